@@ -1,0 +1,468 @@
+// bf16 GEMM for sm_100a on the 5th-generation tensor cores.
+//
+//   C[M,N] (+)= A * B     fp32 accumulation in TMEM, bf16 (or fp32) output
+//
+// One persistent, warp-specialised kernel covers the dense projections (q/k/v/o, router,
+// lm_head, dense MLP), their input/weight gradients, and the three grouped expert GEMMs of
+// the MoE block:
+//   * warp 0   : TMA producer - tiled bulk tensor loads into a 128B-swizzled smem ring
+//   * warp 1   : one elected thread issues tcgen05.mma (UMMA 128 x BLOCK_N x 16) into one of
+//                two TMEM accumulators and commits to mbarriers
+//   * warps 2-5: epilogue - tcgen05.ld the accumulator (each warp owns 32 TMEM lanes),
+//                convert and store / accumulate into C while the next tile's main loop runs
+// Each operand may be K-major (rows of K contiguous) or MN-major (rows of M/N contiguous),
+// which gives NT / NN / TN / TT products without a transpose pass:
+//   forward   Y  = X  W^T    A K-major,  B K-major
+//   dgrad     dX = dY W      A K-major,  B MN-major
+//   wgrad     dW = dY^T X    A MN-major, B MN-major
+// Grouping modes (the per-expert row ranges live on the device, no host sync):
+//   MODE_RAGGED_M : A/C rows are grouped by expert, each group padded to a multiple of 128
+//                   rows; meta[0] = number of 128-row blocks in use, meta[1+i] = expert of
+//                   block i.  B is the merged weight [E, rows_per_expert, ld].
+//   MODE_RAGGED_K : per-expert wgrad, K runs over the expert's (padded) row range
+//                   meta[e] .. meta[e+1]; C is [E, M, N].
+// The reference computes these with torch.matmul per expert or with XPU Triton kernels
+// (optimus/models/common/moe.py:43-215, optimus/kernels/merged_mlp_triton_kernels.py:8-269,
+// optimus/kernels/grouped_linear_*.py).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+
+#include "olb_api.h"
+#include "ptx.cuh"
+
+namespace olb {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;  // 64 bf16 = 128 bytes = one swizzle atom
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int A_STAGE_BYTES = BLOCK_M * BLOCK_K * 2;
+constexpr int MN_BOX_BYTES = 64 * BLOCK_K * 2;  // one [64 k-rows][64 mn] box
+
+struct GemmParams {
+  void* C;
+  long long ldc;
+  int M, N, K;
+  int a_mn_major, b_mn_major;
+  int mode;
+  const int* meta;
+  int num_experts;
+  int b_expert_rows;           // rows of B's 2D view that belong to one expert
+  long long c_expert_stride;   // elements between consecutive experts' C (ragged-K)
+  int accumulate;              // C += A*B instead of C = A*B
+  int out_fp32;
+  int* status;
+};
+
+template <int BLOCK_N>
+struct SmemLayout {
+  static constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 2;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = (BLOCK_N == 256) ? 4 : (BLOCK_N == 128 ? 6 : 8);
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + slack for 1024B alignment
+};
+
+struct TileInfo {
+  int m0, n0;        // element offsets of the tile in C
+  int kb_begin, kb_end;  // K range in units of BLOCK_K
+  int expert;
+};
+
+// Map a linear tile id to its coordinates.  Returns false when `t` is past the last tile.
+template <int BLOCK_N>
+__device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int num_m_blocks, TileInfo& ti) {
+  const int num_n_blocks = (p.N + BLOCK_N - 1) / BLOCK_N;
+  if (p.mode == OLB_GEMM_RAGGED_K) {
+    const int per_expert = num_m_blocks * num_n_blocks;
+    if (t >= per_expert * p.num_experts) return false;
+    const int e = t / per_expert;
+    const int r = t - e * per_expert;
+    ti.expert = e;
+    ti.m0 = (r / num_n_blocks) * BLOCK_M;
+    ti.n0 = (r % num_n_blocks) * BLOCK_N;
+    ti.kb_begin = p.meta[e] / BLOCK_K;
+    ti.kb_end = p.meta[e + 1] / BLOCK_K;
+    return true;
+  }
+  if (t >= num_m_blocks * num_n_blocks) return false;
+  // Walk N fastest inside bands of 8 row blocks so that concurrently resident CTAs share
+  // operand tiles through L2.
+  constexpr int BAND = 8;
+  const int band_tiles = BAND * num_n_blocks;
+  const int band = t / band_tiles;
+  const int first_m = band * BAND;
+  const int rows_in_band = min(BAND, num_m_blocks - first_m);
+  const int r = t - band * band_tiles;
+  const int m_blk = first_m + r % rows_in_band;
+  const int n_blk = r / rows_in_band;
+  ti.m0 = m_blk * BLOCK_M;
+  ti.n0 = n_blk * BLOCK_N;
+  ti.kb_begin = 0;
+  ti.kb_end = (p.K + BLOCK_K - 1) / BLOCK_K;
+  ti.expert = (p.mode == OLB_GEMM_RAGGED_M) ? p.meta[1 + m_blk] : 0;
+  return true;
+}
+
+template <int BLOCK_N>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const GemmParams p) {
+  using L = SmemLayout<BLOCK_N>;
+  constexpr int STAGES = L::STAGES;
+  constexpr uint32_t TMEM_COLS = (2 * BLOCK_N < 32) ? 32 : 2 * BLOCK_N;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + L::BAR_OFFSET;
+  // barrier map: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFFSET + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFFSET + 8 * (2 * STAGES + 4) + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  int num_m_blocks;
+  if (p.mode == OLB_GEMM_RAGGED_M) {
+    num_m_blocks = min(p.meta[0], (p.M + BLOCK_M - 1) / BLOCK_M);
+  } else {
+    num_m_blocks = (p.M + BLOCK_M - 1) / BLOCK_M;
+  }
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      TileInfo ti;
+      for (int t = blockIdx.x; ok && get_tile<BLOCK_N>(p, t, num_m_blocks, ti); t += gridDim.x) {
+        for (int kb = ti.kb_begin; kb < ti.kb_end; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          const uint32_t fb = full_bar(stage);
+          mbar_expect_tx(fb, L::STAGE_BYTES);
+          const int k0 = kb * BLOCK_K;
+          if (!p.a_mn_major) {
+            tma_load_2d(sa, &tma_a, fb, k0, ti.m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d(sa + j * MN_BOX_BYTES, &tma_a, fb, ti.m0 + j * 64, k0);
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d(sb, &tma_b, fb, k0, ti.expert * p.b_expert_rows + ti.n0);
+          } else {
+            const int krow = (p.mode == OLB_GEMM_RAGGED_M ? ti.expert * p.b_expert_rows : 0) + k0;
+#pragma unroll
+            for (int j = 0; j < BLOCK_N / 64; ++j) tma_load_2d(sb + j * MN_BOX_BYTES, &tma_b, fb, ti.n0 + j * 64, krow);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      // Drain: every issued load must have landed before the CTA's shared memory goes away.
+      // The MMA warp consumes all stages in the normal case; after an abort wait (bounded)
+      // for the loads of the current ring pass.
+      if (!ok || *abort_flag) {
+        for (int s = 0; s < STAGES; ++s) {
+          unsigned long long t0 = globaltimer_ns();
+          while (!mbar_try_wait(full_bar(s), (s < stage) ? phase : (phase ^ 1u))) {
+            if (globaltimer_ns() - t0 > 200000000ull) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc_bf16(BLOCK_M, BLOCK_N, p.a_mn_major, p.b_mn_major);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      TileInfo ti;
+      for (int t = blockIdx.x; ok && get_tile<BLOCK_N>(p, t, num_m_blocks, ti); t += gridDim.x) {
+        if (ti.kb_end <= ti.kb_begin) continue;  // empty expert: the epilogue writes zeros
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, p.status, ST_TIMEOUT_ACC_EMPTY, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
+        for (int kb = ti.kb_begin; kb < ti.kb_end; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, p.status, ST_TIMEOUT_FULL, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            const uint64_t da = p.a_mn_major ? make_smem_desc(sa + k * (UMMA_K * 128), MN_BOX_BYTES, 1024)
+                                             : make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t db = p.b_mn_major ? make_smem_desc(sb + k * (UMMA_K * 128), MN_BOX_BYTES, 1024)
+                                             : make_smem_desc(sb + k * (UMMA_K * 2), 16, 1024);
+            umma_ss(tmem_d, da, db, idesc, (kb > ti.kb_begin || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(acc_full_bar(acc));
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, +32) belong to this warp
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    TileInfo ti;
+    for (int t = blockIdx.x; get_tile<BLOCK_N>(p, t, num_m_blocks, ti); t += gridDim.x) {
+      const int row = ti.m0 + lane_group * 32 + lane;
+      const bool row_ok = row < p.M;
+      const bool has_k = ti.kb_end > ti.kb_begin;
+      char* c_row;
+      {
+        long long off = static_cast<long long>(row) * p.ldc + ti.n0;
+        if (p.mode == OLB_GEMM_RAGGED_K) off += static_cast<long long>(ti.expert) * p.c_expert_stride;
+        c_row = static_cast<char*>(p.C) + off * (p.out_fp32 ? 4 : 2);
+      }
+      if (has_k) {
+        if (!mbar_wait(acc_full_bar(acc), acc_phase, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) break;
+        tc_fence_after();
+      } else if (p.accumulate) {
+        continue;  // nothing to add
+      }
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + acc * BLOCK_N;
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        uint32_t r[32];
+        if (has_k) {
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (row_ok) {
+          const int col0 = ti.n0 + c * 32;
+          if (p.out_fp32) {
+            float4* dst = reinterpret_cast<float4*>(c_row + c * 32 * 4);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (col0 + g * 4 < p.N) {
+                float4 v = make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
+                                       __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
+                if (p.accumulate) {
+                  float4 o = dst[g];
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                dst[g] = v;
+              }
+            }
+          } else {
+            uint4* dst = reinterpret_cast<uint4*>(c_row + c * 32 * 2);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (col0 + g * 8 < p.N) {
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[8 * g + i]);
+                if (p.accumulate) {
+                  uint4 o = dst[g];
+                  float2 a;
+                  a = unpack_bf16(o.x); f[0] += a.x; f[1] += a.y;
+                  a = unpack_bf16(o.y); f[2] += a.x; f[3] += a.y;
+                  a = unpack_bf16(o.z); f[4] += a.x; f[5] += a.y;
+                  a = unpack_bf16(o.w); f[6] += a.x; f[7] += a.y;
+                }
+                uint4 v;
+                v.x = pack_bf16(f[0], f[1]);
+                v.y = pack_bf16(f[2], f[3]);
+                v.z = pack_bf16(f[4], f[5]);
+                v.w = pack_bf16(f[6], f[7]);
+                dst[g] = v;
+              }
+            }
+          }
+        }
+      }
+      if (has_k) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+// 2D bf16 tensor map with 128B swizzle.  dims/box are {inner, outer}.
+int make_tmap_2d_bf16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                      uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t elem_strides[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+template <int BLOCK_N>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_sms, cudaStream_t stream) {
+  using L = SmemLayout<BLOCK_N>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return -3;
+    configured = true;
+  }
+  long long tiles;
+  const long long nm = (p.M + BLOCK_M - 1) / BLOCK_M, nn = (p.N + BLOCK_N - 1) / BLOCK_N;
+  tiles = nm * nn * (p.mode == OLB_GEMM_RAGGED_K ? p.num_experts : 1);
+  int grid = static_cast<int>(tiles < num_sms ? tiles : num_sms);
+  if (grid <= 0) return 0;
+  gemm_bf16_kernel<BLOCK_N><<<grid, NUM_THREADS, L::TOTAL, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace olb
+
+extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
+  using namespace olb;
+  if (d->M <= 0 || d->N <= 0) return 0;
+  if ((d->lda % 8) || (d->ldb % 8) || (d->ldc % 8) || (d->N % 8) || (reinterpret_cast<uintptr_t>(d->A) & 15) ||
+      (reinterpret_cast<uintptr_t>(d->B) & 15) || (reinterpret_cast<uintptr_t>(d->C) & 15))
+    return -10;
+  int block_n = d->block_n;
+  if (block_n == 0) {
+    if (d->mode != OLB_GEMM_DENSE) {
+      block_n = (d->N % 256 == 0) ? 256 : (d->N % 128 == 0 ? 128 : 64);
+      if (d->N % 64) return -11;
+    } else {
+      block_n = d->N > 128 ? 256 : (d->N > 64 ? 128 : 64);
+    }
+  }
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+
+  CUtensorMap ta, tb;
+  int rc;
+  // A: K-major -> global [a_rows, K] (inner K); MN-major -> global [K rows, M] (inner M).
+  if (!d->a_mn_major)
+    rc = make_tmap_2d_bf16(&ta, d->A, d->K, d->a_rows, d->lda * 2, BLOCK_K, BLOCK_M);
+  else
+    rc = make_tmap_2d_bf16(&ta, d->A, d->M, d->a_rows, d->lda * 2, 64, BLOCK_K);
+  if (rc) return rc;
+  if (!d->b_mn_major)
+    rc = make_tmap_2d_bf16(&tb, d->B, d->K, d->b_rows, d->ldb * 2, BLOCK_K, block_n);
+  else
+    rc = make_tmap_2d_bf16(&tb, d->B, d->N, d->b_rows, d->ldb * 2, 64, BLOCK_K);
+  if (rc) return rc;
+
+  GemmParams p;
+  p.C = d->C;
+  p.ldc = d->ldc;
+  p.M = d->M;
+  p.N = d->N;
+  p.K = d->K;
+  p.a_mn_major = d->a_mn_major;
+  p.b_mn_major = d->b_mn_major;
+  p.mode = d->mode;
+  p.meta = d->meta;
+  p.num_experts = d->num_experts;
+  p.b_expert_rows = d->b_expert_rows;
+  p.c_expert_stride = d->c_expert_stride;
+  p.accumulate = d->accumulate;
+  p.out_fp32 = d->out_fp32;
+  p.status = d->status;
+  const int sms = d->max_ctas > 0 && d->max_ctas < num_sms ? d->max_ctas : num_sms;
+  switch (block_n) {
+    case 256: return launch<256>(ta, tb, p, sms, stream);
+    case 128: return launch<128>(ta, tb, p, sms, stream);
+    case 64: return launch<64>(ta, tb, p, sms, stream);
+    default: return -12;
+  }
+}

@@ -1,0 +1,272 @@
+// RMSNorm / non-parametric LayerNorm, forward and backward, bf16 data with fp32 statistics.
+// One warp owns one row; 16-byte vector accesses; the row is read twice (second read is an
+// L1/L2 hit).  The weight gradient is reduced deterministically: each warp keeps its own
+// fp32 accumulator row in shared memory, blocks write partial rows to a scratch buffer and
+// a second kernel sums the partials in a fixed order.
+//
+// Reference semantics (optimus/models/olmoe/modeling_olmoe.py:93-104): the normalised value
+// is rounded to the input dtype before it is multiplied by the weight; OLMo's LayerNorm has
+// no affine parameters and eps 1e-5 (optimus/models/olmo/modeling_olmo.py:19-30).
+#include "olb_api.h"
+#include "ptx.cuh"
+
+namespace olb {
+
+constexpr int NORM_WARPS = 4;
+constexpr int NORM_THREADS = NORM_WARPS * 32;
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  uint4 v = *reinterpret_cast<const uint4*>(p);
+  float2 a;
+  a = unpack_bf16(v.x); f[0] = a.x; f[1] = a.y;
+  a = unpack_bf16(v.y); f[2] = a.x; f[3] = a.y;
+  a = unpack_bf16(v.z); f[4] = a.x; f[5] = a.y;
+  a = unpack_bf16(v.w); f[6] = a.x; f[7] = a.y;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 v;
+  v.x = pack_bf16(f[0], f[1]);
+  v.y = pack_bf16(f[2], f[3]);
+  v.z = pack_bf16(f[4], f[5]);
+  v.w = pack_bf16(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = v;
+}
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int cols, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * NORM_WARPS + warp;
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + row * cols;
+  __nv_bfloat16* yr = y + row * cols;
+  float ss = 0.f;
+  for (int c = lane * 8; c < cols; c += 256) {
+    float f[8];
+    load8(xr + c, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / cols + eps);
+  if (lane == 0 && rstd) rstd[row] = r;
+  for (int c = lane * 8; c < cols; c += 256) {
+    float f[8], g[8];
+    load8(xr + c, f);
+    if (w) load8(w + c, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float n = round_bf16(f[i] * r);
+      f[i] = w ? n * g[i] : n;
+    }
+    store8(yr + c, f);
+  }
+}
+
+// dx = r * (dn - n * mean(dn * n)), dn = dy * w, n = x * r.  dw partial = sum_rows dy * n.
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int cols) {
+  extern __shared__ float s_dw[];  // [NORM_WARPS][cols] when dw_partial != NULL
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* my_dw = s_dw + static_cast<size_t>(warp) * cols;
+  if (dw_partial) {
+    for (int c = lane; c < cols; c += 32) my_dw[c] = 0.f;
+  }
+  __syncwarp();
+  for (long long row = static_cast<long long>(blockIdx.x) * NORM_WARPS + warp; row < rows;
+       row += static_cast<long long>(gridDim.x) * NORM_WARPS) {
+    const __nv_bfloat16* xr = x + row * cols;
+    const __nv_bfloat16* dyr = dy + row * cols;
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int c = lane * 8; c < cols; c += 256) {
+      float fx[8], fd[8], fw[8];
+      load8(xr + c, fx);
+      load8(dyr + c, fd);
+      if (w) load8(w + c, fw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float n = fx[i] * r;
+        const float dn = w ? fd[i] * fw[i] : fd[i];
+        dot += dn * n;
+        if (dw_partial) my_dw[c + i] += fd[i] * round_bf16(n);
+      }
+    }
+    dot = warp_sum(dot) / cols;
+    for (int c = lane * 8; c < cols; c += 256) {
+      float fx[8], fd[8], fw[8], o[8];
+      load8(xr + c, fx);
+      load8(dyr + c, fd);
+      if (w) load8(w + c, fw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float n = fx[i] * r;
+        const float dn = w ? fd[i] * fw[i] : fd[i];
+        o[i] = r * (dn - n * dot);
+      }
+      store8(dx + row * cols + c, o);
+    }
+  }
+  if (dw_partial) {
+    __syncthreads();
+    for (int c = threadIdx.x; c < cols; c += NORM_THREADS) {
+      float s = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < NORM_WARPS; ++wi) s += s_dw[static_cast<size_t>(wi) * cols + c];
+      dw_partial[static_cast<size_t>(blockIdx.x) * cols + c] = s;
+    }
+  }
+}
+
+__global__ void colsum_finalize_kernel(const float* __restrict__ partial, int nparts, int cols, void* dw, int dw_fp32,
+                                       int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += partial[static_cast<size_t>(p) * cols + c];
+  if (dw_fp32) {
+    float* o = static_cast<float*>(dw);
+    o[c] = accumulate ? o[c] + s : s;
+  } else {
+    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(dw);
+    o[c] = __float2bfloat16_rn(accumulate ? __bfloat162float(o[c]) + s : s);
+  }
+}
+
+__global__ void __launch_bounds__(NORM_THREADS)
+layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, float* __restrict__ mean,
+                     float* __restrict__ rstd, int rows, int cols, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * NORM_WARPS + warp;
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + row * cols;
+  float s = 0.f;
+  for (int c = lane * 8; c < cols; c += 256) {
+    float f[8];
+    load8(xr + c, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += f[i];
+  }
+  const float mu = warp_sum(s) / cols;
+  float ss = 0.f;
+  for (int c = lane * 8; c < cols; c += 256) {
+    float f[8];
+    load8(xr + c, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += (f[i] - mu) * (f[i] - mu);
+  }
+  const float r = rsqrtf(warp_sum(ss) / cols + eps);
+  if (lane == 0) {
+    mean[row] = mu;
+    rstd[row] = r;
+  }
+  for (int c = lane * 8; c < cols; c += 256) {
+    float f[8];
+    load8(xr + c, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = (f[i] - mu) * r;
+    store8(y + row * cols + c, f);
+  }
+}
+
+// dx = r * (dy - mean(dy) - n * mean(dy * n))
+__global__ void __launch_bounds__(NORM_THREADS)
+layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                     const float* __restrict__ mean, const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx,
+                     int rows, int cols) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * NORM_WARPS + warp;
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + row * cols;
+  const __nv_bfloat16* dyr = dy + row * cols;
+  const float mu = mean[row], r = rstd[row];
+  float s1 = 0.f, s2 = 0.f;
+  for (int c = lane * 8; c < cols; c += 256) {
+    float fx[8], fd[8];
+    load8(xr + c, fx);
+    load8(dyr + c, fd);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      s1 += fd[i];
+      s2 += fd[i] * (fx[i] - mu) * r;
+    }
+  }
+  s1 = warp_sum(s1) / cols;
+  s2 = warp_sum(s2) / cols;
+  for (int c = lane * 8; c < cols; c += 256) {
+    float fx[8], fd[8], o[8];
+    load8(xr + c, fx);
+    load8(dyr + c, fd);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = r * (fd[i] - s1 - (fx[i] - mu) * r * s2);
+    store8(dx + row * cols + c, o);
+  }
+}
+
+}  // namespace olb
+
+using namespace olb;
+
+extern "C" int olb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps,
+                               cudaStream_t stream) {
+  if (cols % 8) return -1;
+  if (rows <= 0) return 0;
+  rmsnorm_fwd_kernel<<<(rows + NORM_WARPS - 1) / NORM_WARPS, NORM_THREADS, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), rstd,
+      rows, cols, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int olb_rmsnorm_bwd_blocks(int rows) {
+  int nb = (rows + NORM_WARPS - 1) / NORM_WARPS;
+  return nb < 296 ? (nb < 1 ? 1 : nb) : 296;
+}
+
+extern "C" int olb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                               float* dw_partial, int rows, int cols, cudaStream_t stream) {
+  if (cols % 8) return -1;
+  if (rows <= 0) return 0;
+  const int nb = olb_rmsnorm_bwd_blocks(rows);
+  const size_t smem = dw_partial ? sizeof(float) * NORM_WARPS * cols : 0;
+  if (smem > 200 * 1024) return -3;
+  if (smem > 48 * 1024) {
+    static size_t configured = 0;
+    if (smem > configured) {
+      if (cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+        return -4;
+      configured = 200 * 1024;
+    }
+  }
+  rmsnorm_bwd_kernel<<<nb, NORM_THREADS, smem, stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+      rstd, static_cast<__nv_bfloat16*>(dx), dw_partial, rows, cols);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int olb_colsum_finalize(const float* partial, int nparts, int cols, void* dw, int dw_fp32, int accumulate,
+                                   cudaStream_t stream) {
+  colsum_finalize_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(partial, nparts, cols, dw, dw_fp32, accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int olb_layernorm_fwd(const void* x, void* y, float* mean, float* rstd, int rows, int cols, float eps,
+                                 cudaStream_t stream) {
+  if (cols % 8) return -1;
+  if (rows <= 0) return 0;
+  layernorm_fwd_kernel<<<(rows + NORM_WARPS - 1) / NORM_WARPS, NORM_THREADS, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), mean, rstd, rows, cols, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int olb_layernorm_bwd(const void* dy, const void* x, const float* mean, const float* rstd, void* dx,
+                                 int rows, int cols, cudaStream_t stream) {
+  if (cols % 8) return -1;
+  if (rows <= 0) return 0;
+  layernorm_bwd_kernel<<<(rows + NORM_WARPS - 1) / NORM_WARPS, NORM_THREADS, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), mean, rstd,
+      static_cast<__nv_bfloat16*>(dx), rows, cols);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

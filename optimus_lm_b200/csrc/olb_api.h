@@ -1,0 +1,190 @@
+// C entry points of the sm_100a kernel library.  Every function enqueues work on `stream`
+// and returns 0 on success or a negative code for a rejected argument / failed launch.
+// Pointers are device pointers unless stated otherwise.  No function allocates memory.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---------------------------------------------------------------- GEMM (gemm_tcgen05.cu)
+enum { OLB_GEMM_DENSE = 0, OLB_GEMM_RAGGED_M = 1, OLB_GEMM_RAGGED_K = 2 };
+
+typedef struct {
+  const void* A;  // bf16. K-major: [a_rows, K] with row stride lda; MN-major: [a_rows (=K extent), M]
+  const void* B;  // bf16. K-major: [b_rows, K] with row stride ldb; MN-major: [b_rows (=K extent), N]
+  void* C;        // bf16 (or fp32 when out_fp32), row-major [M, N], row stride ldc
+  long long lda, ldb, ldc;  // in elements
+  long long a_rows, b_rows; // outer extent of the operand's 2D view (bounds for TMA)
+  int M, N, K;
+  int a_mn_major, b_mn_major;
+  int mode;                  // OLB_GEMM_*
+  const int* meta;           // RAGGED_M: [0]=#row blocks, [1+i]=expert of block i; RAGGED_K: row offsets [E+1]
+  int num_experts;
+  int b_expert_rows;
+  long long c_expert_stride;
+  int accumulate;
+  int out_fp32;
+  int block_n;               // 0 = choose
+  int max_ctas;              // 0 = all SMs
+  int* status;               // device status word (may be NULL)
+} olb_gemm_desc;
+
+int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream);
+
+// ---------------------------------------------------------------- normalisation (norm.cu)
+// y = x * rsqrt(mean(x^2) + eps) * w   (w may be NULL).  rstd [rows] fp32 is saved for backward.
+int olb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps,
+                    cudaStream_t stream);
+// dx and, when dw_partial != NULL, per-block partial sums of dw ([olb_rmsnorm_bwd_blocks(rows), cols] fp32).
+int olb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_partial,
+                    int rows, int cols, cudaStream_t stream);
+int olb_rmsnorm_bwd_blocks(int rows);
+// dw[cols] (bf16 or fp32 by dw_fp32) (+)= sum over `nparts` rows of dw_partial.
+int olb_colsum_finalize(const float* partial, int nparts, int cols, void* dw, int dw_fp32, int accumulate,
+                        cudaStream_t stream);
+// Non-parametric LayerNorm (fp32 statistics), saves mean and rstd.
+int olb_layernorm_fwd(const void* x, void* y, float* mean, float* rstd, int rows, int cols, float eps,
+                      cudaStream_t stream);
+int olb_layernorm_bwd(const void* dy, const void* x, const float* mean, const float* rstd, void* dx, int rows,
+                      int cols, cudaStream_t stream);
+
+// ---------------------------------------------------------------- activation / rope (elementwise.cu)
+// act[r, i] = silu(g[r,i]) * u[r,i];   g, u, act have their own row strides (elements).
+int olb_swiglu_fwd(const void* g, long long ldg, const void* u, long long ldu, void* act, long long ldact,
+                   long long rows, int cols, cudaStream_t stream);
+int olb_swiglu_bwd(const void* dact, long long lddact, const void* g, long long ldg, const void* u, long long ldu,
+                   void* dg, long long lddg, void* du, long long lddu, long long rows, int cols,
+                   cudaStream_t stream);
+// Expert-MLP activation with the routing weight folded in (rows are the expert-grouped rows of
+// olb_moe_build_index): act[row] = weights[src_of[row], k_of[row]] * silu(g) * u; padding rows -> 0.
+int olb_swiglu_rowscale_fwd(const void* g, long long ldg, const void* u, long long ldu, const int* src_of,
+                            const int* k_of, const float* weights, int K, const int* meta, void* act,
+                            long long ldact, int cap, int cols, cudaStream_t stream);
+// Backward of the above; also dweights[t,k] = <dact[row], silu(g)*u> (dweights may be NULL).
+int olb_swiglu_rowscale_bwd(const void* dact, long long lddact, const void* g, long long ldg, const void* u,
+                            long long ldu, const int* src_of, const int* k_of, const float* weights, int K,
+                            const int* meta, void* dg, long long lddg, void* du, long long lddu, float* dweights,
+                            int cap, int cols, cudaStream_t stream);
+// In-place rotary embedding on x [tokens, heads, head_dim] (bf16), token t uses position t % seq_len.
+// cos/sin: fp32 [seq_len, rot_dim].  interleaved: pairs (2i, 2i+1) are de-interleaved first and the
+// result is left in de-interleaved order.  conj != 0 applies the inverse rotation (backward).
+int olb_rope_inplace(void* x, long long token_stride, int tokens, int heads, int head_dim, int rot_dim,
+                     int seq_len, const float* cos_tab, const float* sin_tab, int interleaved, int conj,
+                     cudaStream_t stream);
+
+// ---------------------------------------------------------------- router (router.cu)
+// Softmax over experts in fp32, top-k (ties -> lowest index), optional renormalisation.
+// logits bf16 [T, E]; out: weights fp32 [T, K], indices int32 [T, K];
+// optional per-block partials for the load-balance loss: cnt_partial/prob_partial [blocks, E] and
+// lse_sq_partial [blocks] (sum of logsumexp^2, for the z-loss).
+int olb_router_softmax_topk(const void* logits, int T, int E, int K, int renorm, float* weights, int* indices,
+                            float* cnt_partial, float* prob_partial, float* lse_sq_partial, cudaStream_t stream);
+int olb_router_blocks(int T);
+// dlogits [T,E] (bf16) = softmax-backward of (d_weights scattered to the selected experts, with the
+// renormalisation chain) + aux_scale * p o (f - <f,p>) + z_scale * 2 * lse * p
+int olb_router_bwd(const void* logits, const int* indices, const float* dweights, int T, int E, int K, int renorm,
+                   const float* aux_f, float aux_scale, float z_scale, void* dlogits, cudaStream_t stream);
+// Same, with the aux/z scales additionally multiplied by *aux_scale_dev (a device scalar, e.g. the
+// upstream gradient of the auxiliary loss) when it is not NULL.
+int olb_router_bwd_ex(const void* logits, const int* indices, const float* dweights, int T, int E, int K,
+                      int renorm, const float* aux_f, const float* aux_scale_dev, float aux_scale, float z_scale,
+                      void* dlogits, cudaStream_t stream);
+// DeepSeek-V3 router: sigmoid scores (+bias for selection only), group-limited top-k, renorm, scale.
+int olb_router_sigmoid_group_topk(const float* logits, const float* bias, int T, int E, int K, int n_group,
+                                  int topk_group, int renorm, float scale, float* weights, int* indices,
+                                  cudaStream_t stream);
+int olb_router_sigmoid_bwd(const float* logits, const int* indices, const float* dweights, int T, int E, int K,
+                           int renorm, float scale, float* dlogits, cudaStream_t stream);
+
+// ---------------------------------------------------------------- MoE permutation (moe.cu)
+// Build the expert-grouped row layout for the pairs (t,k) whose expert lies in
+// [e_start, e_start+E_loc).  Each expert's rows start at a multiple of 128.
+//   ws          : int workspace, at least olb_moe_ws_ints(T, E_loc) ints
+//   row_of      : [T, K]   destination row of pair (t,k) or -1
+//   src_of,k_of : [cap]    source token / k slot of each row, -1 for padding rows
+//   meta        : [1 + cap/128] GEMM tile table (see OLB_GEMM_RAGGED_M)
+//   offsets     : [E_loc+1] padded row offsets (see OLB_GEMM_RAGGED_K); counts: [E_loc] true counts
+// If the padded rows exceed `cap`, status receives ST_OVERFLOW and the excess pairs get row -1.
+int olb_moe_build_index(const int* indices, int T, int K, int e_start, int E_loc, int cap, int* ws, int* row_of,
+                        int* src_of, int* k_of, int* meta, int* offsets, int* counts, int* status,
+                        cudaStream_t stream);
+long long olb_moe_ws_ints(int T, int E_loc);
+// out[row,:] = src_of[row] >= 0 ? x[src_of[row],:] : 0   for row < meta[0]*128   (bf16, cols % 8 == 0)
+int olb_moe_gather_rows(const void* x, const int* src_of, const int* meta, void* out, int cap, int cols,
+                        cudaStream_t stream);
+// out[t,:] = sum_k w[t,k] * y[row_of[t,k],:]  (fp32 accumulation; w == NULL means 1)
+int olb_moe_combine(const void* y, const int* row_of, const float* w, void* out, int T, int K, int cols,
+                    cudaStream_t stream);
+// dy[row,:] = w[t,k] * dout[t,:]; dw[t,k] = <y[row,:], dout[t,:]>  (rows < meta[0]*128; padding rows -> 0)
+int olb_moe_combine_bwd(const void* dout, const void* y, const int* src_of, const int* k_of, const int* meta,
+                        const float* w, void* dy, float* dw, int cap, int K, int cols, cudaStream_t stream);
+
+// ---------------------------------------------------------------- loss (loss.cu)
+// Per-row cross entropy on bf16 logits [rows, V] (row stride ldl) with int64 labels (ignore < 0).
+// loss_row [rows] fp32 (0 for ignored rows), lse [rows] fp32.
+int olb_ce_fwd(const void* logits, long long ldl, const long long* labels, float* loss_row, float* lse, int rows,
+               int V, cudaStream_t stream);
+// dlogits = (softmax - onehot) * (*scale_dev); may alias logits.
+int olb_ce_bwd(const void* logits, long long ldl, const long long* labels, const float* lse, const float* scale_dev,
+               void* dlogits, int rows, int V, cudaStream_t stream);
+
+// ---------------------------------------------------------------- optimizer (adamw.cu)
+typedef struct {
+  float lr, beta1, beta2, eps, weight_decay;
+  float bias_correction1, bias_correction2;  // 1 - beta^t
+  float grad_scale;                          // applied to the gradient before everything else
+  int skip_weight_update;
+} olb_adamw_hparams;
+// Sum of squares of (grad * grad_scale) -> partial [olb_sumsq_blocks(n)] fp32 (deterministic).
+int olb_sumsq_partial(const void* grad, int grad_fp32, long long n, float grad_scale, float* partial,
+                      cudaStream_t stream);
+int olb_sumsq_blocks(long long n);
+// out[0] = sum(partial[0..nparts))  (+= when accumulate)
+int olb_sum_finalize(const float* partial, int nparts, float* out, int accumulate, cudaStream_t stream);
+// AdamW of the reference form on one flat shard: g = grad*grad_scale*(*clip_coef_dev or 1);
+// m,v update; master -= lr*mhat/(sqrt(vhat)+eps); master += master*(-lr*wd); param = cast(master).
+int olb_adamw_step(const void* grad, int grad_fp32, float* master, float* m, float* v, void* param,
+                   int param_fp32, long long n, const olb_adamw_hparams* hp, const float* clip_coef_dev,
+                   cudaStream_t stream);
+
+// ---------------------------------------------------------------- attention (attention.cu)
+// Causal flash attention forward, bf16, q/k/v as [B, S, H, D] with arbitrary token/head strides
+// (elements); o [B, S, Hq, Dv]; lse [B, Hq, S] fp32.  D in {64, 128, 192}, Dv in {64, 128}.
+typedef struct {
+  const void *q, *k, *v;
+  void* o;
+  float* lse;
+  long long q_bs, q_ss, q_hs;  // batch / seq / head strides
+  long long k_bs, k_ss, k_hs;
+  long long v_bs, v_ss, v_hs;
+  long long o_bs, o_ss, o_hs;
+  int B, S, Hq, Hkv, D, Dv;
+  float scale;
+  int* status;
+} olb_attn_fwd_desc;
+int olb_attn_fwd(const olb_attn_fwd_desc* d, cudaStream_t stream);
+
+typedef struct {
+  const void *q, *k, *v, *o, *dout;
+  const float* lse;
+  void *dq, *dk, *dv;   // bf16, same layouts as q/k/v
+  float* dq_acc;        // fp32 scratch [B, S, Hq, D]
+  float* delta;         // fp32 scratch [B, Hq, S]
+  long long q_bs, q_ss, q_hs, k_bs, k_ss, k_hs, v_bs, v_ss, v_hs, o_bs, o_ss, o_hs;
+  long long dq_bs, dq_ss, dq_hs, dk_bs, dk_ss, dk_hs, dv_bs, dv_ss, dv_hs, do_bs, do_ss, do_hs;
+  int B, S, Hq, Hkv, D, Dv;
+  float scale;
+  int* status;
+} olb_attn_bwd_desc;
+int olb_attn_bwd(const olb_attn_bwd_desc* d, cudaStream_t stream);
+
+// ---------------------------------------------------------------- timing (event_profiler.cu)
+// Writes %globaltimer (ns) of the moment the kernel runs on `stream` into slot[0].
+int olb_stamp_globaltimer(unsigned long long* slot, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

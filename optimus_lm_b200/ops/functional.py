@@ -1,0 +1,670 @@
+"""Autograd ops of the framework.
+
+Each op has two implementations with identical semantics:
+
+* the sm_100a kernels of ``optimus_lm_b200._C`` (tcgen05 GEMMs, fused norm / rope / SwiGLU /
+  router / MoE permutation / cross-entropy kernels), used for bf16 CUDA tensors;
+* a plain PyTorch version written like the reference's modules, used on CPU (gloo tests)
+  and for fp32 runs, and serving as the oracle of the kernel tests.
+
+GEMM operand conventions (see csrc/gemm_tcgen05.cu): forward ``Y = X W^T`` is K-major x
+K-major; ``dX = dY W`` reads ``W`` MN-major; ``dW = dY^T X`` reads both operands MN-major,
+so no transposed copies are ever materialised.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from ._ext import extension, use_kernels
+
+GEMM_DENSE, GEMM_RAGGED_M, GEMM_RAGGED_K = 0, 1, 2
+
+# Device status word per GPU: kernels record bounded-wait timeouts / capacity overflow here.
+_STATUS = {}
+
+
+def status_word(device) -> torch.Tensor:
+    device = torch.device(device)
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    t = _STATUS.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _STATUS[key] = t
+    return t
+
+
+def check_status(device) -> int:
+    """Read (and clear) the device status word; non-zero means a kernel reported a problem."""
+    t = status_word(device)
+    v = int(t.item())
+    if v:
+        t.zero_()
+    return v
+
+
+def _kernel_ok(*ts) -> bool:
+    return all(t is None or t.dtype == torch.bfloat16 for t in ts) and use_kernels(*[t for t in ts if t is not None])
+
+
+# ------------------------------------------------------------------------------------ GEMM
+def gemm(a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, *, a_mn_major=False, b_mn_major=False,
+         out: Optional[torch.Tensor] = None, accumulate=False, mode=GEMM_DENSE, meta=None, num_experts=1,
+         b_expert_rows=0, c_expert_stride=0, out_dtype=torch.bfloat16, block_n=0, max_ctas=0) -> torch.Tensor:
+    """Raw tcgen05 GEMM on 2D bf16 views (unit inner stride). See csrc/olb_api.h."""
+    if out is None:
+        assert not accumulate
+        shape = (num_experts, M, N) if mode == GEMM_RAGGED_K else (M, N)
+        out = torch.empty(shape, dtype=out_dtype, device=a.device)
+    extension().gemm(a, b, out, M, N, K, a_mn_major, b_mn_major, accumulate, mode, meta, num_experts,
+                     b_expert_rows, c_expert_stride, status_word(a.device), block_n, max_ctas)
+    return out
+
+
+def _as_2d(x: torch.Tensor) -> torch.Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or (x2.stride(0) % 8) or (x2.data_ptr() % 16):
+        x2 = x2.contiguous()
+    return x2
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        x2 = _as_2d(x)
+        M, K = x2.shape
+        N = w.shape[0]
+        y = gemm(x2, w, M, N, K)
+        ctx.save_for_backward(x2, w)
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        M, K = x2.shape
+        N = w.shape[0]
+        dy2 = _as_2d(dy)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, M, K, N, b_mn_major=True).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, N, K, M, a_mn_major=True, b_mn_major=True)
+        return dx, dw
+
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x @ w.T`` for a bias-free projection (reference: nn.Linear -> oneDNN)."""
+    if _kernel_ok(x, w) and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0:
+        return _LinearFn.apply(x, w)
+    return F.linear(x, w)
+
+
+# ------------------------------------------------------------------------------------ norms
+def rms_norm_reference(x, weight, eps):
+    """Reference RMSNorm (optimus/models/olmoe/modeling_olmoe.py:93-104)."""
+    dt = x.dtype
+    h = x.to(torch.float32)
+    h = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps)
+    h = h.to(dt)
+    return weight * h if weight is not None else h
+
+
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        C = extension()
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        rstd = torch.empty(xc.numel() // xc.shape[-1], dtype=torch.float32, device=x.device)
+        C.rmsnorm_fwd(xc, w, y, rstd, eps)
+        ctx.save_for_backward(xc, w, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = extension()
+        x, w, rstd = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        rows, cols = rstd.numel(), x.shape[-1]
+        dw = None
+        if w is not None and ctx.needs_input_grad[1]:
+            nb = C.rmsnorm_bwd_blocks(rows)
+            partial = torch.empty((nb, cols), dtype=torch.float32, device=x.device)
+            C.rmsnorm_bwd(dy, x, w, rstd, dx, partial)
+            dw = torch.empty_like(w)
+            C.colsum_finalize(partial, nb, dw, False)
+        else:
+            C.rmsnorm_bwd(dy, x, w, rstd, dx, None)
+        return dx, dw, None
+
+
+def rms_norm(x, weight, eps=1e-5):
+    if _kernel_ok(x, weight) and x.shape[-1] % 8 == 0:
+        return _RMSNormFn.apply(x, weight, eps)
+    return rms_norm_reference(x, weight, eps)
+
+
+def layer_norm_noaffine_reference(x, eps=1e-5):
+    """OLMo's non-parametric LayerNorm in fp32 (optimus/models/olmo/modeling_olmo.py:19-30)."""
+    dt = x.dtype
+    return F.layer_norm(x.to(torch.float32), (x.shape[-1],), None, None, eps).to(dt)
+
+
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, eps):
+        C = extension()
+        xc = x.contiguous()
+        rows = xc.numel() // xc.shape[-1]
+        y = torch.empty_like(xc)
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty_like(mean)
+        C.layernorm_fwd(xc, y, mean, rstd, eps)
+        ctx.save_for_backward(xc, mean, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, mean, rstd = ctx.saved_tensors
+        dx = torch.empty_like(x)
+        extension().layernorm_bwd(dy.contiguous(), x, mean, rstd, dx)
+        return dx, None
+
+
+def layer_norm_noaffine(x, eps=1e-5):
+    if _kernel_ok(x) and x.shape[-1] % 8 == 0:
+        return _LayerNormFn.apply(x, eps)
+    return layer_norm_noaffine_reference(x, eps)
+
+
+# ------------------------------------------------------------------------------------ SwiGLU
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, g, u):
+        g2, u2 = _as_2d(g), _as_2d(u)
+        act = torch.empty((g2.shape[0], g2.shape[1]), dtype=g.dtype, device=g.device)
+        extension().swiglu_fwd(g2, u2, act)
+        ctx.save_for_backward(g2, u2)
+        ctx.shape = g.shape
+        return act.view(g.shape)
+
+    @staticmethod
+    def backward(ctx, dact):
+        g2, u2 = ctx.saved_tensors
+        d2 = _as_2d(dact)
+        dg = torch.empty((g2.shape[0], g2.shape[1]), dtype=g2.dtype, device=g2.device)
+        du = torch.empty_like(dg)
+        extension().swiglu_bwd(d2, g2, u2, dg, du)
+        return dg.view(ctx.shape), du.view(ctx.shape)
+
+
+def swiglu(g, u):
+    """``silu(g) * u``."""
+    if _kernel_ok(g, u) and g.shape[-1] % 8 == 0:
+        return _SwiGLUFn.apply(g, u)
+    return F.silu(g) * u
+
+
+# ------------------------------------------------------------------------------------ RoPE
+class _RopeFn(torch.autograd.Function):
+    """In-place rotary embedding on ``x[..., rot_offset:rot_offset+rot_dim]`` of a
+    ``[B, S, heads, head_dim]`` tensor."""
+
+    @staticmethod
+    def forward(ctx, x, cos_tab, sin_tab, rot_offset, rot_dim, interleaved):
+        B, S, Hn, D = x.shape
+        assert x.stride(-1) == 1 and x.stride(2) % 8 == 0 and x.stride(1) % 8 == 0 and rot_offset % 8 == 0
+        assert B == 1 or x.stride(0) == S * x.stride(1)
+        view = x[..., rot_offset:]
+        extension().rope_inplace(view, x.stride(1), B * S, Hn, x.stride(2), rot_dim, S, cos_tab, sin_tab,
+                                 interleaved, False)
+        ctx.mark_dirty(x)
+        ctx.save_for_backward(cos_tab, sin_tab)
+        ctx.args = (rot_offset, rot_dim, interleaved)
+        return x
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos_tab, sin_tab = ctx.saved_tensors
+        rot_offset, rot_dim, interleaved = ctx.args
+        dx = dy.contiguous().clone() if not dy.is_contiguous() else dy.clone()
+        B, S, Hn, D = dx.shape
+        view = dx[..., rot_offset:]
+        extension().rope_inplace(view, dx.stride(1), B * S, Hn, dx.stride(2), rot_dim, S, cos_tab, sin_tab,
+                                 interleaved, True)
+        return dx, None, None, None, None, None
+
+
+def rope_reference(x, cos_tab, sin_tab, rot_offset=0, rot_dim=None, interleaved=False):
+    """x: [B, S, heads, head_dim]; cos/sin: [S, rot_dim] fp32."""
+    from ..models.common.modeling_rope_utils import deinterleave_last_dim, rotate_half
+    rot_dim = rot_dim or (x.shape[-1] - rot_offset)
+    xr = x[..., rot_offset:rot_offset + rot_dim]
+    if interleaved:
+        xr = deinterleave_last_dim(xr)
+    cos = cos_tab[None, :, None, :].to(x.dtype)
+    sin = sin_tab[None, :, None, :].to(x.dtype)
+    out = xr * cos + rotate_half(xr) * sin
+    if rot_offset == 0 and rot_dim == x.shape[-1]:
+        return out
+    return torch.cat([x[..., :rot_offset], out, x[..., rot_offset + rot_dim:]], dim=-1)
+
+
+def rope(x, cos_tab, sin_tab, rot_offset=0, rot_dim=None, interleaved=False):
+    """Rotary embedding on a ``[B, S, heads, head_dim]`` tensor (may modify ``x`` in place on
+    the kernel path; use the return value)."""
+    rot_dim = rot_dim or (x.shape[-1] - rot_offset)
+    if _kernel_ok(x) and rot_dim % 16 == 0 and cos_tab.is_cuda:
+        return _RopeFn.apply(x, cos_tab.contiguous(), sin_tab.contiguous(), rot_offset, rot_dim, interleaved)
+    return rope_reference(x, cos_tab, sin_tab, rot_offset, rot_dim, interleaved)
+
+
+# ------------------------------------------------------------------------------------ attention
+def attention_reference(q, k, v, scale=None, causal=True):
+    """q [B,S,Hq,D], k [B,S,Hkv,D], v [B,S,Hkv,Dv] -> [B,S,Hq,Dv]; fp32 softmax, eager."""
+    B, S, Hq, D = q.shape
+    Hkv = k.shape[2]
+    rep = Hq // Hkv
+    scale = scale if scale is not None else D ** -0.5
+    qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    if rep > 1:
+        kh = kh.repeat_interleave(rep, dim=1)
+        vh = vh.repeat_interleave(rep, dim=1)
+    s = torch.matmul(qh, kh.transpose(-1, -2)) * scale
+    if causal:
+        mask = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
+        s = s.masked_fill(~mask, float("-inf"))
+    p = torch.softmax(s, dim=-1, dtype=torch.float32).to(q.dtype)
+    return torch.matmul(p, vh).transpose(1, 2).contiguous()
+
+
+def attention(q, k, v, scale=None, causal=True):
+    """Causal attention on ``[B, S, H, D]`` tensors (GQA when ``k`` has fewer heads)."""
+    from . import attention as _attn
+    return _attn.flash_attention(q, k, v, scale=scale, causal=causal)
+
+
+# ------------------------------------------------------------------------------------ router
+def router_softmax_topk_reference(logits, k, renorm):
+    """Reference routing (optimus/models/olmoe/modeling_olmoe.py:295-299); returns fp32 weights
+    and int64 indices."""
+    p = F.softmax(logits, dim=1, dtype=torch.float)
+    w, idx = torch.topk(p, k, dim=-1)
+    if renorm:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return w, idx
+
+
+class _RouterFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, k, renorm, want_stats):
+        C = extension()
+        T, E = logits.shape
+        logits = logits.contiguous()
+        w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+        idx = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+        if want_stats:
+            nb = C.router_blocks(T)
+            cnt = torch.empty((nb, E), dtype=torch.float32, device=logits.device)
+            prob = torch.empty((nb, E), dtype=torch.float32, device=logits.device)
+            lse2 = torch.empty((nb,), dtype=torch.float32, device=logits.device)
+            C.router_softmax_topk(logits, k, renorm, w, idx, cnt, prob, lse2)
+            stats = torch.cat([cnt.sum(0), prob.sum(0), lse2.sum(0, keepdim=True)])  # [2E+1], fixed order
+        else:
+            C.router_softmax_topk(logits, k, renorm, w, idx, None, None, None)
+            stats = torch.zeros(2 * E + 1, dtype=torch.float32, device=logits.device)
+        ctx.save_for_backward(logits, idx)
+        ctx.renorm = renorm
+        ctx.mark_non_differentiable(idx, stats)
+        return w, idx, stats
+
+    @staticmethod
+    def backward(ctx, dw, _didx, _dstats):
+        logits, idx = ctx.saved_tensors
+        dlogits = torch.empty_like(logits)
+        extension().router_bwd(logits, idx, dw.contiguous().float(), ctx.renorm, None, None, 0.0, 0.0, dlogits)
+        return dlogits, None, None, None
+
+
+def router_softmax_topk(logits, k, renorm=False, want_stats=True):
+    """Returns ``(weights fp32 [T,k], indices [T,k], stats)``.  ``stats`` is a ``[2E+1]`` fp32
+    vector (selection counts per expert, summed probabilities per expert, sum of lse^2) on
+    the kernel path and ``None`` on the PyTorch path."""
+    if _kernel_ok(logits) and logits.shape[1] <= 256 and k <= 16:
+        return _RouterFn.apply(logits, k, renorm, want_stats)
+    w, idx = router_softmax_topk_reference(logits, k, renorm)
+    return w, idx, None
+
+
+def load_balancing_loss_reference(gate_logits: Sequence[torch.Tensor], num_experts: int, top_k: int):
+    """Switch load-balance loss over all layers concatenated
+    (optimus/models/olmoe/modeling_olmoe.py:29-85, attention_mask=None)."""
+    if gate_logits is None or len(gate_logits) == 0:
+        return 0
+    cat = torch.cat(list(gate_logits), dim=0)
+    rw = F.softmax(cat, dim=-1)
+    _, sel = torch.topk(rw, top_k, dim=-1)
+    mask = F.one_hot(sel, num_experts)
+    tokens_per_expert = torch.mean(mask.float(), dim=0)
+    router_prob_per_expert = torch.mean(rw, dim=0)
+    return torch.sum(tokens_per_expert * router_prob_per_expert.unsqueeze(0)) * num_experts
+
+
+def layer_level_load_balancing_loss_reference(gate_logits, num_experts, top_k):
+    """Per-layer load-balance loss averaged over layers
+    (optimus/models/common/ral_functions.py:6-35)."""
+    if gate_logits is None or len(gate_logits) == 0:
+        return 0
+    st = torch.stack(list(gate_logits), dim=0)  # [L, T, E]
+    rw = F.softmax(st, dim=-1)
+    _, sel = torch.topk(rw, top_k, dim=-1)
+    mask = F.one_hot(sel, num_experts)  # [L, T, k, E]
+    tokens_per_expert = torch.mean(mask.float(), dim=1)  # [L, k, E]
+    prob = torch.mean(rw, dim=1)  # [L, E]
+    per_layer = torch.sum(tokens_per_expert * prob.unsqueeze(1), dim=(1, 2)) * num_experts
+    return per_layer.mean()
+
+
+def z_loss_reference(gate_logits):
+    cat = torch.cat(list(gate_logits), dim=0).float()
+    return torch.logsumexp(cat, dim=-1).pow(2).mean()
+
+
+class _AuxLossFn(torch.autograd.Function):
+    """Load-balance (+ optional z) loss from the router kernels' statistics.
+
+    forward inputs: ``num_layers`` logits tensors followed by ``num_layers`` index tensors and
+    ``num_layers`` stats vectors.  The gradient w.r.t. each layer's logits is
+    ``coef*E/N * p o (f - <f,p>)`` (+ z-loss term) computed by the router backward kernel.
+    """
+
+    @staticmethod
+    def forward(ctx, num_experts, top_k, layer_level, aux_coef, z_coef, n_layers, *tensors):
+        logits = tensors[:n_layers]
+        idxs = tensors[n_layers:2 * n_layers]
+        stats = torch.stack(tensors[2 * n_layers:3 * n_layers], dim=0)  # [L, 2E+1]
+        E = num_experts
+        T = logits[0].shape[0]
+        cnt, prob, lse2 = stats[:, :E], stats[:, E:2 * E], stats[:, 2 * E]
+        if layer_level:
+            f = cnt / T  # [L, E]
+            aux = (E * (f * (prob / T)).sum(dim=1)).mean()
+            n_norm = T * n_layers
+        else:
+            n_norm = T * n_layers
+            f = (cnt.sum(0) / n_norm).unsqueeze(0).expand(n_layers, E)
+            aux = E * (f[0] * (prob.sum(0) / n_norm)).sum()
+        z = lse2.sum() / (T * n_layers)
+        ctx.save_for_backward(*logits, *idxs, f.contiguous())
+        ctx.cfg = (E, n_layers, aux_coef, z_coef, n_norm, T)
+        return aux_coef * aux + z_coef * z
+
+    @staticmethod
+    def backward(ctx, g):
+        E, L, aux_coef, z_coef, n_norm, T = ctx.cfg
+        saved = ctx.saved_tensors
+        logits, idxs, f = saved[:L], saved[L:2 * L], saved[2 * L]
+        C = extension()
+        g = g.to(torch.float32).reshape(1).contiguous()
+        grads = []
+        for l in range(L):
+            d = torch.empty_like(logits[l])
+            C.router_bwd(logits[l], idxs[l], None, False, f[l].contiguous(), g, aux_coef * E / n_norm,
+                         z_coef / (T * L), d)
+            grads.append(d)
+        return (None,) * 6 + tuple(grads) + (None,) * (2 * L)
+
+
+def router_aux_loss(logits_list, idx_list, stats_list, num_experts, top_k, *, layer_level=False, aux_coef=1.0,
+                    z_coef=0.0):
+    """``aux_coef * load_balance + z_coef * z_loss`` over the given layers' router logits."""
+    L = len(logits_list)
+    if L == 0:
+        return 0
+    if stats_list is not None and all(s is not None for s in stats_list) and _kernel_ok(*logits_list):
+        return _AuxLossFn.apply(num_experts, top_k, layer_level, aux_coef, z_coef, L, *logits_list, *idx_list,
+                                *stats_list)
+    fn = layer_level_load_balancing_loss_reference if layer_level else load_balancing_loss_reference
+    loss = aux_coef * fn(tuple(logits_list), num_experts, top_k)
+    if z_coef:
+        loss = loss + z_coef * z_loss_reference(logits_list)
+    return loss
+
+
+# ------------------------------------------------------------------------------------ MoE experts
+def moe_experts_reference(x, topk_w, topk_idx, wg, wu, wd, e_start=0):
+    """Loop-over-experts oracle (optimus/models/olmoe/modeling_olmoe.py:310-336).
+
+    x [T,H]; topk_w [T,K] (already in x.dtype or fp32); topk_idx [T,K] global expert ids;
+    wg/wu [E_loc, I, H]; wd [E_loc, H, I].  Returns [T, H] partial output of the local experts.
+    """
+    T, H = x.shape
+    E_loc = wg.shape[0]
+    out = torch.zeros((T, H), dtype=x.dtype, device=x.device)
+    tw = topk_w.to(x.dtype)
+    for le in range(E_loc):
+        tok, kk = torch.where(topk_idx == (e_start + le))
+        if tok.numel() == 0:
+            continue
+        cur = x[tok]
+        h = F.silu(F.linear(cur, wg[le])) * F.linear(cur, wu[le])
+        y = F.linear(h, wd[le]) * tw[tok, kk, None]
+        out.index_add_(0, tok, y)
+    return out
+
+
+def moe_capacity_rows(T: int, K: int, E_loc: int, ep: int = 1, capacity_factor: float = 0.0) -> int:
+    """Row capacity of the expert-grouped buffers: every routed pair plus 127 padding rows per
+    local expert, rounded to 128.  With ``capacity_factor > 0`` (expert parallel receive
+    side) the pair count is ``capacity_factor`` x the balanced share instead of the worst case."""
+    pairs = T * K
+    if capacity_factor and ep > 1:
+        pairs = min(pairs, int(math.ceil(capacity_factor * T * K / ep)))
+    rows = pairs + E_loc * 127
+    return ((rows + 127) // 128) * 128
+
+
+class MoEIndex:
+    """Device-resident permutation of routed (token, k) pairs into expert-grouped rows."""
+
+    __slots__ = ("row_of", "src_of", "k_of", "meta", "offsets", "counts", "cap", "E_loc", "K")
+
+    def __init__(self, topk_idx: torch.Tensor, e_start: int, E_loc: int, cap: int):
+        C = extension()
+        T, K = topk_idx.shape
+        dev = topk_idx.device
+        ws = torch.empty(C.moe_ws_ints(T, E_loc), dtype=torch.int32, device=dev)
+        self.row_of = torch.empty((T, K), dtype=torch.int32, device=dev)
+        self.src_of = torch.empty(cap, dtype=torch.int32, device=dev)
+        self.k_of = torch.empty(cap, dtype=torch.int32, device=dev)
+        self.meta = torch.empty(1 + cap // 128, dtype=torch.int32, device=dev)
+        self.offsets = torch.empty(E_loc + 1, dtype=torch.int32, device=dev)
+        self.counts = torch.empty(E_loc, dtype=torch.int32, device=dev)
+        self.cap, self.E_loc, self.K = cap, E_loc, K
+        C.moe_build_index(topk_idx.contiguous(), e_start, E_loc, cap, ws, self.row_of, self.src_of, self.k_of,
+                          self.meta, self.offsets, self.counts, status_word(dev))
+
+
+def grouped_linear_fwd(xp, w, index: MoEIndex, out=None):
+    """``y[rows of e] = xp[rows of e] @ w[e].T`` for merged weights ``w [E, N, K]``."""
+    E, N, K = w.shape
+    return gemm(xp, w.view(E * N, K), index.cap, N, K, mode=GEMM_RAGGED_M, meta=index.meta, b_expert_rows=N, out=out)
+
+
+def grouped_linear_dgrad(dy, w, index: MoEIndex, out=None, accumulate=False):
+    """``dx[rows of e] (+)= dy[rows of e] @ w[e]``."""
+    E, N, K = w.shape
+    return gemm(dy, w.view(E * N, K), index.cap, K, N, b_mn_major=True, mode=GEMM_RAGGED_M, meta=index.meta,
+                b_expert_rows=N, out=out, accumulate=accumulate)
+
+
+def grouped_linear_wgrad(dy, xp, index: MoEIndex, N: int, K: int):
+    """``dw[e] = dy[rows of e].T @ xp[rows of e]`` -> [E, N, K]."""
+    return gemm(dy, xp, N, K, index.cap, a_mn_major=True, b_mn_major=True, mode=GEMM_RAGGED_K, meta=index.offsets,
+                num_experts=index.E_loc, c_expert_stride=N * K)
+
+
+class _MoEExpertsFn(torch.autograd.Function):
+    """Local expert computation on expert-grouped rows:
+    index build -> gather -> grouped gate/up GEMMs -> weighted SwiGLU -> grouped down GEMM ->
+    unweighted combine.  The routing weight is folded into the activation, so the backward
+    needs neither the expert outputs nor a weighted scatter."""
+
+    @staticmethod
+    def forward(ctx, x, topk_w, topk_idx, wg, wu, wd, e_start, cap):
+        C = extension()
+        T, H = x.shape
+        E_loc, I, _ = wg.shape
+        x = x.contiguous()
+        topk_w = topk_w.contiguous().float()
+        index = MoEIndex(topk_idx, e_start, E_loc, cap)
+        xp = torch.empty((cap, H), dtype=x.dtype, device=x.device)
+        C.moe_gather_rows(x, index.src_of, index.meta, xp)
+        h = torch.empty((cap, 2 * I), dtype=x.dtype, device=x.device)
+        grouped_linear_fwd(xp, wg, index, out=h[:, :I])
+        grouped_linear_fwd(xp, wu, index, out=h[:, I:])
+        act = torch.empty((cap, I), dtype=x.dtype, device=x.device)
+        C.swiglu_rowscale_fwd(h[:, :I], h[:, I:], index.src_of, index.k_of, topk_w, index.meta, act)
+        y = grouped_linear_fwd(act, wd, index)
+        out = torch.empty((T, H), dtype=x.dtype, device=x.device)
+        C.moe_combine(y, index.row_of, None, out)
+        ctx.save_for_backward(xp, h, act, topk_w, wg, wu, wd)
+        ctx.index = index
+        ctx.dims = (T, H, I, E_loc)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        C = extension()
+        xp, h, act, topk_w, wg, wu, wd = ctx.saved_tensors
+        index = ctx.index
+        T, H, I, E_loc = ctx.dims
+        cap = index.cap
+        dout = dout.contiguous()
+        # d(y) = gather of dout (the combine was an unweighted sum)
+        dyp = torch.empty((cap, H), dtype=dout.dtype, device=dout.device)
+        C.moe_gather_rows(dout, index.src_of, index.meta, dyp)
+        dwd = grouped_linear_wgrad(dyp, act, index, H, I) if ctx.needs_input_grad[5] else None
+        dact = grouped_linear_dgrad(dyp, wd, index)
+        del dyp
+        dh = torch.empty_like(h)
+        dtopk = torch.zeros_like(topk_w)
+        C.swiglu_rowscale_bwd(dact, h[:, :I], h[:, I:], index.src_of, index.k_of, topk_w, index.meta, dh[:, :I],
+                              dh[:, I:], dtopk)
+        del dact
+        dwg = grouped_linear_wgrad(dh[:, :I], xp, index, I, H) if ctx.needs_input_grad[3] else None
+        dwu = grouped_linear_wgrad(dh[:, I:], xp, index, I, H) if ctx.needs_input_grad[4] else None
+        dxp = grouped_linear_dgrad(dh[:, :I], wg, index)
+        grouped_linear_dgrad(dh[:, I:], wu, index, out=dxp, accumulate=True)
+        dx = torch.empty((T, H), dtype=dout.dtype, device=dout.device)
+        C.moe_combine(dxp, index.row_of, None, dx)
+        return dx, dtopk, None, dwg, dwu, dwd, None, None
+
+
+def moe_experts(x, topk_w, topk_idx, wg, wu, wd, e_start=0, cap: Optional[int] = None):
+    """Partial MoE output of the local experts for tokens ``x [T,H]``.
+
+    ``topk_idx`` holds global expert ids; pairs routed to other ranks' experts are skipped.
+    ``wg/wu [E_loc, I, H]``, ``wd [E_loc, H, I]`` (the merged-MLP layout of the reference,
+    optimus/models/common/moe.py:379-405)."""
+    E_loc, I, H = wg.shape
+    if _kernel_ok(x, wg, wu, wd) and topk_idx.dtype == torch.int32 and H % 64 == 0 and I % 64 == 0 and E_loc <= 256:
+        if cap is None:
+            cap = moe_capacity_rows(x.shape[0], topk_idx.shape[1], E_loc)
+        return _MoEExpertsFn.apply(x, topk_w, topk_idx, wg, wu, wd, e_start, cap)
+    return moe_experts_reference(x, topk_w, topk_idx.long(), wg, wu, wd, e_start)
+
+
+# ------------------------------------------------------------------------------------ cross entropy
+class _ShiftedCEFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits2d, labels1d, inplace_backward):
+        C = extension()
+        rows = logits2d.shape[0]
+        loss_row = torch.empty(rows, dtype=torch.float32, device=logits2d.device)
+        lse = torch.empty_like(loss_row)
+        C.ce_fwd(logits2d, labels1d, loss_row, lse)
+        n_valid = (labels1d >= 0).sum().to(torch.float32)
+        ctx.save_for_backward(logits2d, labels1d, lse, n_valid)
+        ctx.inplace = inplace_backward
+        return loss_row.sum() / n_valid
+
+    @staticmethod
+    def backward(ctx, g):
+        logits2d, labels1d, lse, n_valid = ctx.saved_tensors
+        scale = (g.to(torch.float32) / n_valid).reshape(1).contiguous()
+        d = logits2d if ctx.inplace else torch.empty_like(logits2d)
+        extension().ce_bwd(logits2d, labels1d, lse, scale, d)
+        return d, None, None
+
+
+def shifted_cross_entropy_reference(logits, labels):
+    """Reference loss (optimus/models/olmoe/modeling_olmoe.py:515-524)."""
+    V = logits.shape[-1]
+    sl = logits[..., :-1, :].contiguous().view(-1, V)
+    tl = labels[..., 1:].contiguous().view(-1)
+    return F.cross_entropy(sl, tl)
+
+
+def shifted_cross_entropy(logits, labels, inplace_backward=False):
+    """Mean CE of ``logits[:, :-1]`` against ``labels[:, 1:]``.  On the kernel path the full
+    ``[B*S, V]`` logits are used with the last position of every sequence ignored, so no
+    shifted copy of the logits is made; with ``inplace_backward`` the gradient overwrites the
+    logits buffer."""
+    if _kernel_ok(logits) and logits.is_contiguous() and logits.shape[-1] % 8 == 0:
+        B, S, V = logits.shape
+        tgt = torch.full((B, S), -100, dtype=torch.long, device=logits.device)
+        tgt[:, :-1] = labels[:, 1:]
+        return _ShiftedCEFn.apply(logits.view(B * S, V), tgt.view(-1), inplace_backward)
+    return shifted_cross_entropy_reference(logits, labels)
+
+
+# ------------------------------------------------------------------------------------ optimizer kernels
+def adamw_step_reference(grad, master, m, v, param, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0,
+                         clip_coef=None, skip_weight_update=False):
+    """The reference update (optimus/optimizers.py:193-205) in plain torch, in place."""
+    g = grad.to(torch.float32) * grad_scale
+    if clip_coef is not None:
+        g = g * clip_coef
+    m.mul_(beta1).add_(g, alpha=1 - beta1)
+    v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+    if not skip_weight_update:
+        mhat = m / (1 - beta1 ** step)
+        vhat = v / (1 - beta2 ** step)
+        master.sub_(lr * mhat / (vhat.sqrt() + eps))
+        master.add_(master, alpha=-lr * weight_decay)
+    if param.data_ptr() != master.data_ptr():
+        param.copy_(master)
+
+
+def adamw_step(grad, master, m, v, param, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0,
+               clip_coef=None, skip_weight_update=False):
+    if master.is_cuda and use_kernels(master) and master.numel() % 4 == 0:
+        extension().adamw_step(grad, master, m, v, param, lr, beta1, beta2, eps, weight_decay, step, grad_scale,
+                               clip_coef, skip_weight_update)
+    else:
+        adamw_step_reference(grad, master, m, v, param, lr, beta1, beta2, eps, weight_decay, step, grad_scale,
+                             clip_coef, skip_weight_update)
+
+
+def sum_of_squares(t: torch.Tensor, scale: float = 1.0, out: Optional[torch.Tensor] = None, accumulate=False):
+    """``sum((t*scale)^2)`` as a 1-element fp32 tensor (deterministic reduction on GPU)."""
+    if out is None:
+        out = torch.zeros(1, dtype=torch.float32, device=t.device)
+        accumulate = False
+    if t.is_cuda and use_kernels(t) and t.dtype in (torch.bfloat16, torch.float32) and t.is_contiguous():
+        C = extension()
+        partial = torch.empty(max(1, C.sumsq_blocks(t.numel())), dtype=torch.float32, device=t.device)
+        C.sumsq(t, scale, partial, out, accumulate)
+    else:
+        s = (t.to(torch.float32) * scale).pow(2).sum().reshape(1)
+        if accumulate:
+            out.add_(s)
+        else:
+            out.copy_(s)
+    return out
