@@ -250,10 +250,12 @@ def test_router_softmax_topk(T, E, K, renorm):
     wr, idxr = OF.router_softmax_topk_reference(lr, K, renorm)
     # same selected sets (order may differ only on exact ties)
     assert torch.equal(idx.long().sort(-1).values, idxr.sort(-1).values)
-    assert rel_err(w, torch.gather(torch.softmax(lr, -1), 1, idx.long()) / (wr.sum(-1, keepdim=True) if renorm else 1)) < 1e-4
+    sel_ref = torch.gather(torch.softmax(lr, -1), 1, idx.long()).detach()
+    if renorm:
+        sel_ref = sel_ref / sel_ref.sum(-1, keepdim=True)
+    assert rel_err(w, sel_ref) < 1e-4
     g = torch.randn(T, K, device="cuda")
     w.backward(g)
-    (torch.gather(wr, 1, torch.argsort(torch.argsort(idxr, -1), -1)) * 0).sum()  # no-op, keeps graph simple
     # reference gradient with matching order
     p = torch.softmax(lr, -1)
     sel = torch.gather(p, 1, idx.long())
