@@ -29,6 +29,7 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "olb_api.h"
@@ -408,6 +409,13 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
 
 extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   using namespace olb;
+  static const bool debug = getenv("OLB_DEBUG_GEMM") != nullptr;
+  if (debug) {
+    fprintf(stderr, "[olb_gemm] M=%d N=%d K=%d a_mn=%d b_mn=%d mode=%d lda=%lld ldb=%lld ldc=%lld a_rows=%lld b_rows=%lld "
+            "acc=%d fp32=%d A=%p B=%p C=%p meta=%p\n", d->M, d->N, d->K, d->a_mn_major, d->b_mn_major, d->mode, d->lda,
+            d->ldb, d->ldc, d->a_rows, d->b_rows, d->accumulate, d->out_fp32, d->A, d->B, d->C, (const void*)d->meta);
+    fflush(stderr);
+  }
   if (d->M <= 0 || d->N <= 0) return 0;
   if ((d->lda % 8) || (d->ldb % 8) || (d->ldc % 8) || (d->N % 8) || (reinterpret_cast<uintptr_t>(d->A) & 15) ||
       (reinterpret_cast<uintptr_t>(d->B) & 15) || (reinterpret_cast<uintptr_t>(d->C) & 15))
@@ -428,6 +436,14 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
 
+  // cuTensorMapEncodeTiled is a driver call and needs a current context in the calling thread.
+  // A thread that has only been handed tensors (an autograd worker whose first CUDA work is this
+  // GEMM) has none yet; one runtime call binds the primary context.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   CUtensorMap ta, tb;
   int rc;
   // A: K-major -> global [a_rows, K] (inner K); MN-major -> global [K rows, M] (inner M).
@@ -442,6 +458,10 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
     rc = make_tmap_2d_bf16(&tb, d->B, d->N, d->b_rows, d->ldb * 2, 64, BLOCK_K);
   if (rc) return rc;
 
+  if (debug) {
+    fprintf(stderr, "[olb_gemm] tensor maps ok, block_n=%d\n", block_n);
+    fflush(stderr);
+  }
   GemmParams p;
   p.C = d->C;
   p.ldc = d->ldc;
