@@ -270,3 +270,93 @@ extern "C" int olb_layernorm_bwd(const void* dy, const void* x, const float* mea
       static_cast<__nv_bfloat16*>(dx), rows, cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the RMSNorm backward (see olb_noalloc.h).  The per-block partial
+// sums of the weight gradient go to a device array that is part of the library image.
+#include <mutex>
+
+#include "olb_noalloc.h"
+
+namespace olb {
+
+static __device__ __align__(256) float g_noalloc_dw_partial[OLB_NOALLOC_MAX_PARTS * OLB_NOALLOC_MAX_COLS];
+
+// Device code may name the array directly; only host code needs its address.
+__global__ void colsum_finalize_static_kernel(int nparts, int cols, void* dw, int dw_fp32) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += g_noalloc_dw_partial[static_cast<size_t>(p) * cols + c];
+  if (dw_fp32)
+    static_cast<float*>(dw)[c] = s;
+  else
+    static_cast<__nv_bfloat16*>(dw)[c] = __float2bfloat16_rn(s);
+}
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+struct NoallocDeviceState {
+  float* scratch = nullptr;  // device address of g_noalloc_dw_partial on this device
+  bool smem_raised = false;
+};
+static NoallocDeviceState g_noalloc_state[NOALLOC_MAX_DEVICES];
+static std::mutex g_noalloc_mutex;
+
+// One-time set-up per device, with that device current.  In host code the array's name is only
+// a handle for the runtime, not a device address, so the address is looked up explicitly.
+static int noalloc_setup(int dev, bool need_big_smem, float** scratch) {
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  NoallocDeviceState& st = g_noalloc_state[dev];
+  if (st.scratch == nullptr) {
+    float* ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_dw_partial) != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return OLB_NOALLOC_ERR_SYMBOL;
+    }
+    st.scratch = ptr;
+  }
+  if (need_big_smem && !st.smem_raised) {
+    if (cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return OLB_NOALLOC_ERR_SYMBOL;
+    }
+    st.smem_raised = true;
+  }
+  *scratch = st.scratch;
+  return OLB_NOALLOC_OK;
+}
+
+}  // namespace olb
+
+extern "C" const char* olb_noalloc_strerror(int code) {
+  switch (code) {
+    case OLB_NOALLOC_OK: return "ok";
+    case OLB_NOALLOC_ERR_BAD_COLS: return "cols must be a multiple of 8";
+    case OLB_NOALLOC_ERR_LAUNCH: return "kernel launch failed";
+    case OLB_NOALLOC_ERR_TOO_LARGE: return "cols exceeds OLB_NOALLOC_MAX_COLS (8192): the built-in scratch array is too small";
+    case OLB_NOALLOC_ERR_SYMBOL: return "could not resolve the device address of the built-in scratch array";
+    case OLB_NOALLOC_ERR_DEVICE: return "no usable current CUDA device";
+    default: return "unknown error";
+  }
+}
+
+extern "C" int olb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                                       void* dw, int dw_fp32, int rows, int cols, cudaStream_t stream) {
+  if (cols % 8) return OLB_NOALLOC_ERR_BAD_COLS;
+  if (cols > OLB_NOALLOC_MAX_COLS) return OLB_NOALLOC_ERR_TOO_LARGE;
+  if (rows <= 0) return OLB_NOALLOC_OK;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return OLB_NOALLOC_ERR_DEVICE;
+  const int nb = olb_rmsnorm_bwd_blocks(rows);  // <= OLB_NOALLOC_MAX_PARTS
+  const size_t smem = sizeof(float) * NORM_WARPS * cols;
+  float* scratch = nullptr;
+  const int rc = noalloc_setup(dev, smem > 48 * 1024, &scratch);
+  if (rc != OLB_NOALLOC_OK) return rc;
+  rmsnorm_bwd_kernel<<<nb, NORM_THREADS, smem, stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+      rstd, static_cast<__nv_bfloat16*>(dx), scratch, rows, cols);
+  if (cudaGetLastError() != cudaSuccess) return OLB_NOALLOC_ERR_LAUNCH;
+  colsum_finalize_static_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(nb, cols, dw, dw_fp32);
+  return cudaGetLastError() == cudaSuccess ? OLB_NOALLOC_OK : OLB_NOALLOC_ERR_LAUNCH;
+}
