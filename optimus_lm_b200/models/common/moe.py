@@ -116,6 +116,7 @@ class SparseMoeBlock(nn.Module):
         self._a2a = None  # lazily built fused dispatcher
         self.last_router_stats = None
         self.last_router_indices = None
+        self.last_router_logits = None
 
     # ------------------------------------------------------------------ routing
     def _route(self, hidden2d, sequence_length):
@@ -132,7 +133,7 @@ class SparseMoeBlock(nn.Module):
                                                want_stats=self.output_router_logits)
         # the reference rounds the routing weights to the activation dtype before using them
         w = w.to(hidden2d.dtype)
-        self.last_router_stats, self.last_router_indices = stats, idx
+        self.last_router_stats, self.last_router_indices, self.last_router_logits = stats, idx, router_logits
         return router_logits, w, idx
 
     # ------------------------------------------------------------------ experts

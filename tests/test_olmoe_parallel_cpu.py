@@ -1,0 +1,94 @@
+"""Tiny OLMoE on CPU/gloo: expert-parallel, pipeline-parallel and sharded-optimizer runs must
+reproduce the serial run's loss curve (fp32)."""
+import pytest
+import torch
+
+MODEL = "allenai/OLMoE-1B-7B-0924--L2-SH0.125-SA0.25-SE0.125-SC0.25-SI0.5"   # 2 layers, d=256, 4 heads, 8 experts top-2, ffn 512
+OVR = {"vocab_size": 1024, "max_position_embeddings": 128, "router_z_loss_coef": 0.001}
+STEPS, MBS, SEQ = 8, 2, 128
+
+
+def _tokens(n_seq):
+    g = torch.Generator().manual_seed(0)
+    return torch.randint(0, 1024, (STEPS, n_seq, SEQ), generator=g)
+
+
+def _engine(**kw):
+    from optimus_lm_b200.engine import EngineArgs, TrainEngine
+    ovr = dict(OVR)
+    ovr.update(kw.pop("config_overrides", {}))
+    args = EngineArgs(model_choice=MODEL, dtype="fp32", context_size=SEQ, lr=4e-4, beta1=0.9, beta2=0.95,
+                      weight_decay=0.1, warmup_steps=0, config_overrides=ovr, use_fused_ep_alltoall=False, **kw)
+    return TrainEngine(args, device=torch.device("cpu"))
+
+
+def _serial_losses(n_seq, merged=True):
+    torch.manual_seed(0)
+    e = _engine(batch_size=n_seq, optimizer="unsharded", use_merged_mlp_in_fast_moe=merged)
+    data = _tokens(n_seq)
+    return [e.train_step(data[s]).loss.item() for s in range(STEPS)]
+
+
+def _ep_worker(rank, world, optimizer, ref):
+    import torch.distributed as dist
+    e = _engine(batch_size=MBS, optimizer=optimizer, expert_parallelism=world)
+    data = _tokens(MBS * world)
+    for s in range(STEPS):
+        out = e.train_step(data[s, rank * MBS:(rank + 1) * MBS])
+        loss = out.loss.detach().clone()
+        dist.all_reduce(loss)
+        loss = loss.item() / world
+        # the aux loss is computed per rank on its local tokens, the serial run sees all tokens:
+        # CE matches exactly, the aux part differs at the 1e-3 level of the aux term itself
+        assert abs(loss - ref[s]) < 2e-3, (s, loss, ref[s])
+
+
+@pytest.mark.parametrize("optimizer", ["pgshard", "shard"])
+def test_ep2_matches_serial(optimizer):
+    from dist_utils import run_distributed
+    ref = _serial_losses(2 * MBS)
+    assert ref[-1] < ref[0]
+    run_distributed(_ep_worker, 2, optimizer, ref)
+
+
+def _pp_worker(rank, world, scheme, ref):
+    e = _engine(batch_size=2 * MBS, micro_batch_size=MBS, optimizer="shard", pipeline_parallelism=world,
+                pp_scheme=scheme)
+    data = _tokens(2 * MBS)
+    for s in range(STEPS):
+        out = e.train_step(data[s])
+        if e.pmap.is_last_stage_rank:
+            assert abs(out.loss.item() - ref[s]) < 2e-3, (s, out.loss.item(), ref[s])
+
+
+@pytest.mark.parametrize("scheme", ["1f1b", "gpipe"])
+def test_pp2_matches_serial(scheme):
+    from dist_utils import run_distributed
+    ref = _serial_losses(2 * MBS)
+    run_distributed(_pp_worker, 2, scheme, ref)
+
+
+def _dp_worker(rank, world, optimizer, ref):
+    import torch.distributed as dist
+    e = _engine(batch_size=MBS, optimizer=optimizer, data_parallelism=world)
+    data = _tokens(MBS * world)
+    for s in range(STEPS):
+        out = e.train_step(data[s, rank * MBS:(rank + 1) * MBS])
+        loss = out.loss.detach().clone()
+        dist.all_reduce(loss)
+        assert abs(loss.item() / world - ref[s]) < 2e-3
+
+
+@pytest.mark.parametrize("optimizer", ["unsharded", "shard", "pgshard", "subshard", "pgsubshard"])
+def test_dp2_matches_serial(optimizer):
+    from dist_utils import run_distributed
+    ref = _serial_losses(2 * MBS)
+    run_distributed(_dp_worker, 2, optimizer, ref)
+
+
+def test_merged_and_per_expert_layouts_agree():
+    a = _serial_losses(MBS, merged=True)
+    b = _serial_losses(MBS, merged=False)
+    # same model (the init is keyed by global expert index), two execution paths
+    for x, y in zip(a, b):
+        assert abs(x - y) < 1e-4
