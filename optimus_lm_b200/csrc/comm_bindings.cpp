@@ -1,8 +1,122 @@
-// Python bindings for the fused compute+collective kernels (comm_*.cu).
+// Python bindings for the peer-memory kernels (comm_p2p.cu).  Peer pointers arrive as Python
+// lists of integers (addresses inside other GPUs' symmetric buffers).
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <vector>
+
 #include "olb_api.h"
 
-void register_comm(pybind11::module& m) { (void)m; }
+namespace {
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+inline void check(int rc, const char* what) { TORCH_CHECK(rc == 0, what, " failed with code ", rc); }
+
+std::vector<const void*> cptrs(const std::vector<int64_t>& v) {
+  std::vector<const void*> out;
+  for (auto p : v) out.push_back(reinterpret_cast<const void*>(static_cast<uintptr_t>(p)));
+  return out;
+}
+std::vector<void*> mptrs(const std::vector<int64_t>& v) {
+  std::vector<void*> out;
+  for (auto p : v) out.push_back(reinterpret_cast<void*>(static_cast<uintptr_t>(p)));
+  return out;
+}
+
+void symm_barrier(const std::vector<int64_t>& pads, int64_t my_rank, int64_t channel, int64_t epoch,
+                  const c10::optional<at::Tensor>& status) {
+  auto p = mptrs(pads);
+  check(olb_symm_barrier(p.data(), static_cast<int>(my_rank), static_cast<int>(p.size()), static_cast<int>(channel),
+                         static_cast<unsigned>(epoch), status.has_value() ? status->data_ptr<int>() : nullptr,
+                         cur_stream()),
+        "olb_symm_barrier");
+}
+
+void ep_gather_rows(const std::vector<int64_t>& peer_x, int64_t T, const at::Tensor& src_of, const at::Tensor& meta,
+                    at::Tensor& out) {
+  c10::cuda::CUDAGuard guard(out.device());
+  auto p = cptrs(peer_x);
+  check(olb_ep_gather_rows(p.data(), static_cast<int>(p.size()), static_cast<int>(T), src_of.data_ptr<int>(),
+                           meta.data_ptr<int>(), out.data_ptr(), static_cast<int>(out.size(0)),
+                           static_cast<int>(out.size(1)), cur_stream()),
+        "olb_ep_gather_rows");
+}
+
+void ep_resolve_rows(const std::vector<int64_t>& peer_row_of, const at::Tensor& idx, int64_t my_rank, int64_t E_loc,
+                     at::Tensor& rows) {
+  c10::cuda::CUDAGuard guard(rows.device());
+  auto p = cptrs(peer_row_of);
+  check(olb_ep_resolve_rows(p.data(), static_cast<int>(p.size()), idx.data_ptr<int>(), static_cast<int>(my_rank),
+                            static_cast<int>(idx.size(0)), static_cast<int>(idx.size(1)), static_cast<int>(E_loc),
+                            rows.data_ptr<int>(), cur_stream()),
+        "olb_ep_resolve_rows");
+}
+
+void ep_combine(const std::vector<int64_t>& peer_y, const at::Tensor& rows, const at::Tensor& idx, int64_t E_loc,
+                at::Tensor& out) {
+  c10::cuda::CUDAGuard guard(out.device());
+  auto py = cptrs(peer_y);
+  check(olb_ep_combine(py.data(), static_cast<int>(py.size()), rows.data_ptr<int>(), idx.data_ptr<int>(),
+                       static_cast<int>(idx.size(0)), static_cast<int>(idx.size(1)), static_cast<int>(E_loc),
+                       out.data_ptr(), static_cast<int>(out.size(1)), cur_stream()),
+        "olb_ep_combine");
+}
+
+void ep_pull_dweights(const std::vector<int64_t>& peer_dw, const at::Tensor& idx, int64_t my_rank, int64_t E_loc,
+                      at::Tensor& dw) {
+  c10::cuda::CUDAGuard guard(dw.device());
+  auto p = cptrs(peer_dw);
+  check(olb_ep_pull_dweights(p.data(), static_cast<int>(p.size()), idx.data_ptr<int>(), static_cast<int>(my_rank),
+                             static_cast<int>(idx.size(0)), static_cast<int>(idx.size(1)), static_cast<int>(E_loc),
+                             dw.data_ptr<float>(), cur_stream()),
+        "olb_ep_pull_dweights");
+}
+
+void pull_reduce_rows(const std::vector<int64_t>& peer_partial, int64_t row0, int64_t ld, at::Tensor& out) {
+  c10::cuda::CUDAGuard guard(out.device());
+  auto p = cptrs(peer_partial);
+  check(olb_pull_reduce_rows(p.data(), static_cast<int>(p.size()), row0, static_cast<int>(out.size(0)),
+                             static_cast<int>(out.size(1)), ld, out.data_ptr(), cur_stream()),
+        "olb_pull_reduce_rows");
+}
+
+int64_t rs_adamw_blocks(int64_t n) { return olb_rs_adamw_blocks(n); }
+
+void rs_adamw(const std::vector<int64_t>& peer_grad, const std::vector<int64_t>& peer_param, int64_t shard_off,
+              at::Tensor& master, at::Tensor& m, at::Tensor& v, double lr, double beta1, double beta2, double eps,
+              double weight_decay, int64_t step, double grad_scale, const c10::optional<at::Tensor>& clip_coef,
+              at::Tensor& norm_partial, int64_t mode, bool skip_weight_update) {
+  c10::cuda::CUDAGuard guard(master.device());
+  olb_adamw_hparams hp;
+  hp.lr = static_cast<float>(lr);
+  hp.beta1 = static_cast<float>(beta1);
+  hp.beta2 = static_cast<float>(beta2);
+  hp.eps = static_cast<float>(eps);
+  hp.weight_decay = static_cast<float>(weight_decay);
+  hp.bias_correction1 = static_cast<float>(1.0 - std::pow(beta1, static_cast<double>(step)));
+  hp.bias_correction2 = static_cast<float>(1.0 - std::pow(beta2, static_cast<double>(step)));
+  hp.grad_scale = static_cast<float>(grad_scale);
+  hp.skip_weight_update = skip_weight_update;
+  auto pg = cptrs(peer_grad);
+  auto pp = mptrs(peer_param);
+  TORCH_CHECK(norm_partial.numel() >= olb_rs_adamw_blocks(master.numel()), "norm_partial too small");
+  check(olb_rs_adamw(pg.data(), pp.data(), static_cast<int>(pg.size()), shard_off, master.numel(),
+                     master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), &hp,
+                     clip_coef.has_value() ? clip_coef->data_ptr<float>() : nullptr, norm_partial.data_ptr<float>(),
+                     static_cast<int>(mode), cur_stream()),
+        "olb_rs_adamw");
+}
+
+}  // namespace
+
+void register_comm(pybind11::module& m) {
+  m.def("symm_barrier", &symm_barrier);
+  m.def("ep_gather_rows", &ep_gather_rows);
+  m.def("ep_resolve_rows", &ep_resolve_rows);
+  m.def("ep_combine", &ep_combine);
+  m.def("ep_pull_dweights", &ep_pull_dweights);
+  m.def("pull_reduce_rows", &pull_reduce_rows);
+  m.def("rs_adamw_blocks", &rs_adamw_blocks);
+  m.def("rs_adamw", &rs_adamw);
+}

@@ -150,6 +150,34 @@ int olb_adamw_step(const void* grad, int grad_fp32, float* master, float* m, flo
                    int param_fp32, long long n, const olb_adamw_hparams* hp, const float* clip_coef_dev,
                    cudaStream_t stream);
 
+// ---------------------------------------------------------------- peer-memory kernels (comm_p2p.cu)
+// Host arrays of n (<= 16) device pointers, one per rank of the group, into symmetric buffers.
+// Rendezvous of all ranks through signal words pads[rank][channel*16 + src]; `epoch` must grow by one
+// per use of a channel.  Bounded wait; a timeout is reported in *status.
+int olb_symm_barrier(void* const* pads, int my_rank, int n, int channel, unsigned epoch, int* status,
+                     cudaStream_t stream);
+// out[row,:] = peer_x[g / T][g % T, :], g = src_of[row] (global token id), rows < meta[0]*128; padding -> 0.
+int olb_ep_gather_rows(const void* const* peer_x, int n, int T, const int* src_of, const int* meta, void* out, int cap,
+                       int cols, cudaStream_t stream);
+// rows[t,k] = peer_row_of[d][(my_rank*T+t)*K+k], d = idx[t,k] / E_loc  (row of each of my pairs on its owner).
+int olb_ep_resolve_rows(const void* const* peer_row_of, int n, const int* idx, int my_rank, int T, int K, int E_loc,
+                        int* rows, cudaStream_t stream);
+// out[t,:] = sum_k peer_y[d][rows[t,k], :] with d = idx[t,k] / E_loc (fp32 accumulation; rows < 0 skipped).
+int olb_ep_combine(const void* const* peer_y, int n, const int* rows, const int* idx, int T, int K, int E_loc,
+                   void* out, int cols, cudaStream_t stream);
+int olb_ep_pull_dweights(const void* const* peer_dw, int n, const int* idx, int my_rank, int T, int K, int E_loc,
+                         float* dw, cudaStream_t stream);
+// out[r,:] = sum_p peer_partial[p][row0 + r, :] (row stride ld), bf16 in/out, fp32 accumulation.
+int olb_pull_reduce_rows(const void* const* peer_partial, int n, long long row0, int rows, int cols, long long ld,
+                         void* out, cudaStream_t stream);
+// Gradient reduce-scatter + AdamW + parameter all-gather on the shard [shard_off, shard_off+n_elems) of the
+// ranks' flat bf16 gradient / parameter buffers.  mode 0: norm partials only; mode 1: update as well.
+// norm_partial: olb_rs_adamw_blocks(n_elems) floats (sum of squares of the reduced, scaled gradient).
+int olb_rs_adamw(const void* const* peer_grad, void* const* peer_param, int n, long long shard_off, long long n_elems,
+                 float* master, float* m, float* v, const olb_adamw_hparams* hp, const float* clip_coef_dev,
+                 float* norm_partial, int mode, cudaStream_t stream);
+int olb_rs_adamw_blocks(long long n_elems);
+
 // ---------------------------------------------------------------- attention (attention.cu)
 // Causal flash attention forward, bf16, q/k/v as [B, S, H, D] with arbitrary token/head strides
 // (elements); o [B, S, Hq, Dv]; lse [B, Hq, S] fp32.  D in {64, 128, 192}, Dv in {64, 128}.

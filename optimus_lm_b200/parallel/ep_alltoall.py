@@ -1,0 +1,124 @@
+"""Expert-parallel MoE with the token exchange fused into the permutation kernels.
+
+The reference all-gathers every token, routing weight and index over the EP group, runs the
+local experts over all gathered tokens and reduce-scatters a ``[EP*T, H]`` buffer
+(optimus/models/olmoe/modeling_olmoe.py:305-341, optimus/models/common/moe.py:477-608).  Here only
+the routing metadata (``[T, K]`` indices and weights, ~1 MB) is all-gathered with NCCL; the token
+rows themselves never go through a collective:
+
+* dispatch  - each rank builds the expert-grouped row layout of *its* experts from the gathered
+  indices and its gather kernel pulls exactly the routed rows from the owners' activation buffers
+  over NVLink, straight into the grouped-GEMM operand (dispatch all-to-all + permutation, one
+  kernel, no staging copy of all tokens);
+* experts   - grouped tcgen05 GEMMs with the routing weight folded into the activation;
+* combine   - each rank's combine kernel pulls the K expert outputs of each of its tokens from the
+  owners' output buffers and reduces them in fp32 (combine all-to-all + weighted sum, one kernel).
+
+The backward pass is the mirror image (gather of output gradients, combine of input gradients,
+pull of the routing-weight gradients).  Two device-side barriers per direction order the buffer
+reuse; all waits are bounded.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as OF
+from ..ops._ext import extension
+from .symm import SymmGroup
+
+
+def _all_gather_rows(t: torch.Tensor, n: int, group) -> torch.Tensor:
+    out = torch.empty((n * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+    dist.all_gather_into_tensor(out, t.contiguous(), group=group)
+    return out
+
+
+class _FusedEPMoEFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, topk_w, topk_idx, wg, wu, wd, sg: SymmGroup, e_start, cap):
+        C = extension()
+        n, rank = sg.size, sg.rank
+        T, H = x.shape
+        E_loc, I, _ = wg.shape
+        K = topk_idx.shape[1]
+        topk_idx = topk_idx.contiguous()
+        topk_w = topk_w.contiguous().float()
+
+        xs = sg.named("ep_rows", (T, H), x.dtype)
+        xs.local.copy_(x)
+        idx_all = _all_gather_rows(topk_idx, n, sg.group)
+        w_all = _all_gather_rows(topk_w, n, sg.group)
+        sg.barrier(0)
+
+        index = OF.MoEIndex(idx_all, e_start, E_loc, cap)
+        xp = torch.empty((cap, H), dtype=x.dtype, device=x.device)
+        C.ep_gather_rows(xs.ptrs, T, index.src_of, index.meta, xp)
+        h = torch.empty((cap, 2 * I), dtype=x.dtype, device=x.device)
+        OF.grouped_linear_fwd(xp, wg, index, out=h[:, :I])
+        OF.grouped_linear_fwd(xp, wu, index, out=h[:, I:])
+        act = torch.empty((cap, I), dtype=x.dtype, device=x.device)
+        C.swiglu_rowscale_fwd(h[:, :I], h[:, I:], index.src_of, index.k_of, w_all, index.meta, act)
+        ys = sg.named("ep_out", (cap, H), x.dtype)
+        OF.grouped_linear_fwd(act, wd, index, out=ys.local)
+        rt = sg.named("ep_rowof", (n * T, K), torch.int32)
+        rt.local.copy_(index.row_of)
+        sg.barrier(1)
+
+        rows = torch.empty((T, K), dtype=torch.int32, device=x.device)
+        C.ep_resolve_rows(rt.ptrs, topk_idx, rank, E_loc, rows)
+        out = torch.empty((T, H), dtype=x.dtype, device=x.device)
+        C.ep_combine(ys.ptrs, rows, topk_idx, E_loc, out)
+
+        ctx.save_for_backward(xp, h, act, w_all, wg, wu, wd, rows, topk_idx)
+        ctx.index, ctx.sg = index, sg
+        ctx.dims = (T, H, I, E_loc, K, cap)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        C = extension()
+        xp, h, act, w_all, wg, wu, wd, rows, topk_idx = ctx.saved_tensors
+        index, sg = ctx.index, ctx.sg
+        T, H, I, E_loc, K, cap = ctx.dims
+        n, rank = sg.size, sg.rank
+
+        ds = sg.named("ep_rows", (T, H), dout.dtype)
+        ds.local.copy_(dout)
+        sg.barrier(2)
+
+        dyp = torch.empty((cap, H), dtype=dout.dtype, device=dout.device)
+        C.ep_gather_rows(ds.ptrs, T, index.src_of, index.meta, dyp)
+        dwd = OF.grouped_linear_wgrad(dyp, act, index, H, I) if ctx.needs_input_grad[5] else None
+        dact = OF.grouped_linear_dgrad(dyp, wd, index)
+        del dyp
+        dh = torch.empty_like(h)
+        dwt = sg.named("ep_dw", (n * T, K), torch.float32)
+        dwt.local.zero_()
+        C.swiglu_rowscale_bwd(dact, h[:, :I], h[:, I:], index.src_of, index.k_of, w_all, index.meta, dh[:, :I],
+                              dh[:, I:], dwt.local)
+        del dact
+        dwg = OF.grouped_linear_wgrad(dh[:, :I], xp, index, I, H) if ctx.needs_input_grad[3] else None
+        dwu = OF.grouped_linear_wgrad(dh[:, I:], xp, index, I, H) if ctx.needs_input_grad[4] else None
+        dxp = sg.named("ep_out", (cap, H), dout.dtype)
+        OF.grouped_linear_dgrad(dh[:, :I], wg, index, out=dxp.local)
+        OF.grouped_linear_dgrad(dh[:, I:], wu, index, out=dxp.local, accumulate=True)
+        sg.barrier(3)
+
+        dx = torch.empty((T, H), dtype=dout.dtype, device=dout.device)
+        C.ep_combine(dxp.ptrs, rows, topk_idx, E_loc, dx)
+        dtopk = torch.empty((T, K), dtype=torch.float32, device=dout.device)
+        C.ep_pull_dweights(dwt.ptrs, topk_idx, rank, E_loc, dtopk)
+        return dx, dtopk, None, dwg, dwu, dwd, None, None, None
+
+
+def fused_ep_moe(block, x, w, idx):
+    """MoE forward of ``block`` (a ``SparseMoeBlock``-like module with merged experts) for the
+    local tokens ``x [T, H]`` with routing weights ``w [T, K]`` and global expert ids ``idx``."""
+    pmap = block.pmap
+    sg = SymmGroup.get(pmap.ep_group)
+    wg, wu, wd = block.experts.weights()
+    T = x.shape[0]
+    cap = OF.moe_capacity_rows(T * pmap.expert_parallelism, block.num_experts_per_tok, block.num_experts_per_rank,
+                               pmap.expert_parallelism, block.capacity_factor)
+    return _FusedEPMoEFn.apply(x.contiguous(), w.float(), idx, wg, wu, wd, sg, block.expert_start_idx, cap)

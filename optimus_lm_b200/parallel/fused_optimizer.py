@@ -1,0 +1,128 @@
+"""Optimizer step with the collectives fused into the update kernel.
+
+For every sharded parameter family of a flat-buffer optimizer (``optimizers.py``) the flat
+gradient and parameter buffers are moved into symmetric memory.  One kernel
+(``csrc/comm_p2p.cu: rs_adamw_kernel``) then does, for the shard this rank owns:
+
+    load the shard of every peer's gradient buffer over NVLink -> sum in fp32 (reduce-scatter)
+    -> scale by 1/N -> norm partial -> AdamW on the fp32 master / moments
+    -> store the updated bf16 parameters into every peer's parameter buffer (all-gather)
+
+which replaces ``reduce_scatter_tensor`` + division + ``get_total_norm`` + ~12 elementwise kernels
++ ``all_gather_into_tensor`` of the reference (optimus/optimizers.py:354-494, 704-928).  Two
+device-side barriers bracket the kernel (gradients complete everywhere / parameters written and
+gradients consumed everywhere).
+
+Clipping needs the global norm before the update.  While clipping is inactive (the default
+"delayed clipping" covers the first ``warmup_steps`` optimizer steps) the norm is a by-product of
+the single fused pass; once it is active a first pass computes only the norm partials and the
+fused pass follows with the coefficient, at the cost of reading the peers' gradients twice.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as OF
+from ..ops._ext import extension
+from .symm import SymmGroup, SymmTensor, peer_access_ok
+
+
+class FusedShardedStep:
+    def __init__(self, opt):
+        self.opt = opt
+        self.device = opt.device
+        self.sym: Dict[int, Dict[str, SymmTensor]] = {}
+        self.groups: Dict[int, SymmGroup] = {}
+        for fi, fam in enumerate(opt.families):
+            if not (fam.spec.sharded and fam.spec.num_shards > 1):
+                continue
+            sg = SymmGroup.get(fam.spec.group)
+            self.groups[fi] = sg
+            gp = sg.empty((fam.flat_size,), fam.dtype)
+            gp.local.copy_(fam.flat_param)
+            gg = sg.empty((fam.flat_size,), fam.dtype, zero=True)
+            gg.local.copy_(fam.flat_grad)
+            fam.flat_param, fam.flat_grad = gp.local, gg.local
+            for p, start, size in zip(fam.spec.params, fam.param_start_inds, fam.param_sizes):
+                p.data = fam.flat_param[start:start + size].view_as(p.data)
+                p.grad = fam.flat_grad[start:start + size].view_as(p.data)
+            self.sym[fi] = {"param": gp, "grad": gg}
+        if len(opt.families) == 1:
+            opt._alias_single()
+        else:
+            opt._alias_pair()
+        torch.cuda.synchronize()
+
+    @staticmethod
+    def try_create(opt) -> Optional["FusedShardedStep"]:
+        if opt.dtype != torch.bfloat16 or opt.skip_optimizer_step:
+            return None
+        if opt.opt_use_allreduce_for_param_gather:
+            return None
+        fams = [f for f in opt.families if f.spec.sharded and f.spec.num_shards > 1]
+        if not fams:
+            return None
+        if any(f.spec.group in (None, -1) for f in fams):
+            return None
+        if hasattr(opt, "_replicated_param_ranges") and (opt.expert_parallelism > 1 or opt.tensor_parallelism > 1):
+            return None  # the "shard" class weights replicated gradients in the norm; keep the NCCL path
+        if any(f.spec.num_shards > 16 for f in fams):
+            return None
+        if not all(peer_access_ok(f.spec.group) for f in fams):
+            return None
+        return FusedShardedStep(opt)
+
+    def usable(self, opt) -> bool:
+        return True
+
+    @torch.no_grad()
+    def step(self, opt):
+        C = extension()
+        beta1, beta2 = opt.defaults["betas"]
+        eps, wd = opt.defaults["eps"], opt.defaults["weight_decay"]
+        lr = opt.param_groups[0]["lr"]
+        step_no = opt.step_id + 1
+        clipping = opt._clipping_active()
+        total_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+
+        for sg in {id(g): g for g in self.groups.values()}.values():
+            sg.barrier(8)  # every rank's gradients are complete
+
+        def run(mode, clip_coef):
+            for fi, fam in enumerate(opt.families):
+                scale = 1.0 / fam.spec.grad_divisor
+                for sl in fam.slices:
+                    s0, s1 = sl.state_start, sl.state_start + sl.part
+                    if fi in self.sym:
+                        lo, _ = fam._part_range(sl)
+                        nb = C.rs_adamw_blocks(sl.part)
+                        partial = torch.empty(nb, dtype=torch.float32, device=self.device)
+                        C.rs_adamw(self.sym[fi]["grad"].ptrs, self.sym[fi]["param"].ptrs, lo, fam.master[s0:s1],
+                                   fam.exp_avg[s0:s1], fam.exp_avg_sq[s0:s1], lr, beta1, beta2, eps, wd, step_no, scale,
+                                   clip_coef, partial, mode, opt.skip_optimizer_step_weight_update)
+                        if clip_coef is None:
+                            total_sq.add_(partial.sum())
+                    else:
+                        if clip_coef is None:
+                            OF.sum_of_squares(fam.grad_part(sl), scale, out=total_sq, accumulate=True)
+                        if mode == 1:
+                            OF.adamw_step(fam.grad_part(sl), fam.master[s0:s1], fam.exp_avg[s0:s1],
+                                          fam.exp_avg_sq[s0:s1], fam.param_part(sl), lr, beta1, beta2, eps, wd, step_no,
+                                          grad_scale=scale, clip_coef=clip_coef,
+                                          skip_weight_update=opt.skip_optimizer_step_weight_update)
+
+        if clipping:
+            run(0, None)
+            grad_norm = opt._global_norm(total_sq).reshape(())
+            clip = torch.clamp(opt.max_grad_norm / (grad_norm + 1e-6), max=1.0).reshape(1).float()
+            run(1, clip)
+        else:
+            run(1, None)
+            grad_norm = opt._global_norm(total_sq).reshape(())
+
+        for sg in {id(g): g for g in self.groups.values()}.values():
+            sg.barrier(9)  # parameters written everywhere, gradients consumed everywhere
+        return grad_norm

@@ -1,0 +1,147 @@
+"""Symmetric (peer-accessible) device memory for the fused compute+collective kernels.
+
+``SymmGroup`` wraps one process group whose ranks sit on GPUs with NVLink peer access.  It
+hands out *symmetric tensors*: the same shape on every rank, with the device addresses of all
+ranks' copies known everywhere, so that a kernel can load from / store to a peer's copy.
+
+Two providers, tried in order:
+
+1. ``torch.distributed._symmetric_memory`` (CUDA VMM handles exchanged by PyTorch, also gives
+   an NVLS multicast address when the fabric supports it);
+2. CUDA IPC handles of ordinary allocations, exchanged with ``all_gather_object``.
+
+The group's barrier is a kernel (``csrc/comm_p2p.cu: symm_barrier_kernel``) that signals through
+words in the peers' memory; its wait is bounded and reports ``ST_TIMEOUT_PEER`` in the device
+status word instead of hanging.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as OF
+from ..ops._ext import extension
+
+_SIGNAL_WORDS = 16 * 64  # 64 channels x 16 peers
+
+
+class SymmTensor:
+    """Local tensor + the addresses of every rank's copy."""
+
+    __slots__ = ("local", "ptrs", "multicast_ptr", "_keep")
+
+    def __init__(self, local: torch.Tensor, ptrs: List[int], multicast_ptr: int = 0, keep=None):
+        self.local = local
+        self.ptrs = ptrs
+        self.multicast_ptr = multicast_ptr
+        self._keep = keep
+
+    def offset_ptrs(self, elem_offset: int) -> List[int]:
+        b = elem_offset * self.local.element_size()
+        return [p + b for p in self.ptrs]
+
+
+class SymmGroup:
+    _instances: Dict[int, "SymmGroup"] = {}
+
+    def __init__(self, group):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.size = dist.get_world_size(group)
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.provider = os.environ.get("OLB_SYMM_PROVIDER", "auto")
+        self._epochs: Dict[int, int] = {}
+        self._named: Dict[str, SymmTensor] = {}
+        self.pads = self.empty((_SIGNAL_WORDS,), torch.int32, zero=True)
+        # every rank must have zeroed its signal words before anyone signals
+        dist.barrier(group=group)
+        torch.cuda.synchronize()
+
+    @classmethod
+    def get(cls, group) -> "SymmGroup":
+        key = id(group)
+        inst = cls._instances.get(key)
+        if inst is None:
+            inst = cls._instances[key] = SymmGroup(group)
+        return inst
+
+    # ------------------------------------------------------------------ allocation
+    def _alloc_symm_mem(self, shape, dtype) -> SymmTensor:
+        import torch.distributed._symmetric_memory as symm_mem
+        t = symm_mem.empty(*shape, dtype=dtype, device=self.device)
+        hdl = symm_mem.rendezvous(t, self.group)
+        delta = t.data_ptr() - int(hdl.buffer_ptrs[hdl.rank])
+        ptrs = [int(p) + delta for p in hdl.buffer_ptrs]
+        mc = 0
+        try:
+            mc = int(hdl.multicast_ptr or 0)
+            if mc:
+                mc += delta
+        except Exception:
+            mc = 0
+        return SymmTensor(t, ptrs, mc, keep=hdl)
+
+    def _alloc_ipc(self, shape, dtype) -> SymmTensor:
+        t = torch.empty(shape, dtype=dtype, device=self.device)
+        storage = t.untyped_storage()
+        handle = storage._share_cuda_()
+        gathered = [None] * self.size
+        dist.all_gather_object(gathered, (handle, t.storage_offset() * t.element_size()), group=self.group)
+        ptrs, keep = [], []
+        for r, (h, byte_off) in enumerate(gathered):
+            if r == self.rank:
+                ptrs.append(t.data_ptr())
+                continue
+            st = torch.UntypedStorage._new_shared_cuda(*h)
+            keep.append(st)
+            ptrs.append(st.data_ptr() + byte_off)
+        return SymmTensor(t, ptrs, 0, keep=keep)
+
+    def empty(self, shape, dtype, zero=False) -> SymmTensor:
+        st = None
+        if self.provider in ("auto", "symm_mem"):
+            try:
+                st = self._alloc_symm_mem(tuple(shape), dtype)
+            except Exception as exc:  # noqa: BLE001 - provider fallback
+                if self.provider == "symm_mem":
+                    raise
+                self._symm_mem_error = exc
+                self.provider = "ipc"
+        if st is None:
+            st = self._alloc_ipc(tuple(shape), dtype)
+        if zero:
+            st.local.zero_()
+        return st
+
+    def named(self, name: str, shape, dtype, zero=False) -> SymmTensor:
+        """Cached symmetric tensor (all ranks must request the same names in the same order)."""
+        st = self._named.get(name)
+        if st is None or tuple(st.local.shape) != tuple(shape) or st.local.dtype != dtype:
+            st = self._named[name] = self.empty(shape, dtype, zero=zero)
+        return st
+
+    # ------------------------------------------------------------------ synchronisation
+    def barrier(self, channel: int = 0):
+        """All ranks' preceding work on the current stream is complete and visible to peers when
+        the kernels enqueued after this call start."""
+        e = self._epochs.get(channel, 0) + 1
+        self._epochs[channel] = e
+        extension().symm_barrier(self.pads.ptrs, self.rank, channel, e, OF.status_word(self.device))
+
+
+def peer_access_ok(group) -> bool:
+    """True if every pair of GPUs of this node-local group can address each other's memory."""
+    if not torch.cuda.is_available() or not dist.is_initialized():
+        return False
+    try:
+        n = torch.cuda.device_count()
+        me = torch.cuda.current_device()
+        ok = all(torch.cuda.can_device_access_peer(me, d) for d in range(n) if d != me)
+    except Exception:
+        ok = False
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    return bool(flag.item())

@@ -1,0 +1,155 @@
+"""Multi-GPU tests (2 ranks, one process per GPU, NCCL): the fused peer-memory paths against the
+NCCL-only paths of the same computation.  Skipped when fewer than 2 GPUs are visible."""
+import os
+import socket
+import traceback
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fn_name, args, errq):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    try:
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        globals()[fn_name](rank, world, *args)
+        dist.barrier()
+        torch.cuda.synchronize()
+    except Exception:
+        errq.put((rank, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def _run(fn_name, world, *args, timeout=600):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fn_name, args, errq)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout)
+    errors = []
+    while not errq.empty():
+        errors.append(errq.get())
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+            errors.append((-1, "timeout"))
+        elif p.exitcode != 0 and not errors:
+            errors.append((-1, f"exit code {p.exitcode}"))
+    assert not errors, "\n".join(f"[rank {r}]\n{tb}" for r, tb in errors)
+
+
+def _rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+# ----------------------------------------------------------------------------- workers
+def w_symm_barrier_and_pull(rank, world):
+    import torch.distributed as dist
+    from optimus_lm_b200.ops import functional as OF
+    from optimus_lm_b200.ops import extension
+    from optimus_lm_b200.parallel.symm import SymmGroup
+    sg = SymmGroup.get(dist.group.WORLD)
+    st = sg.empty((world * 64, 256), torch.bfloat16)
+    st.local.fill_(float(rank + 1))
+    for _ in range(5):
+        sg.barrier(0)
+    out = torch.empty(64, 256, dtype=torch.bfloat16, device="cuda")
+    extension().pull_reduce_rows(st.ptrs, rank * 64, 256, out)
+    torch.cuda.synchronize()
+    assert torch.all(out.float() == sum(range(1, world + 1)))
+    assert OF.check_status("cuda") == 0
+
+
+def w_fused_ep_vs_allgather(rank, world):
+    import torch.distributed as dist
+    from optimus_lm_b200.mapper import ParallelDpPpEpTpMapper
+    from optimus_lm_b200.models.olmoe.configuration_olmoe import OlmoeParallelConfig
+    from optimus_lm_b200.models.common.moe import FastOlmoeParallelSparseMoeBlock
+    from optimus_lm_b200.ops import functional as OF
+    pmap = ParallelDpPpEpTpMapper(1, 1, world, 1, rank=rank, create_groups=True)
+    cfg = OlmoeParallelConfig(hidden_size=256, intermediate_size=512, num_experts=8, num_experts_per_tok=2,
+                              expert_parallelism=world, use_fast_moe=True, use_merged_mlp_in_fast_moe=True,
+                              output_router_logits=True, moe_capacity_factor=0.0)
+    torch.manual_seed(0)
+    blk = FastOlmoeParallelSparseMoeBlock(cfg, pmap).cuda().to(torch.bfloat16)
+    with torch.no_grad():
+        for name, p in blk.named_parameters():
+            g = torch.Generator(device="cuda").manual_seed(hash(name) % 1000 + (rank if "experts" in name else 0))
+            p.copy_(torch.randn(p.shape, device="cuda", generator=g) * 0.05)
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    x0 = torch.randn(2, 96, 256, device="cuda", generator=g).to(torch.bfloat16)
+    go = torch.randn(2, 96, 256, device="cuda", generator=g).to(torch.bfloat16)
+    res = {}
+    for transport in ("allgather", "alltoall"):
+        blk.ep_transport = transport
+        blk.zero_grad()
+        x = x0.clone().requires_grad_()
+        y, _ = blk(x)
+        y.backward(go)
+        res[transport] = (y.detach().clone(), x.grad.clone(), {n: p.grad.clone() for n, p in blk.named_parameters()})
+    ya, xa, ga = res["allgather"]
+    yb, xb, gb = res["alltoall"]
+    assert _rel(yb, ya) < 2e-2, _rel(yb, ya)
+    assert _rel(xb, xa) < 2e-2, _rel(xb, xa)
+    for n in ga:
+        assert _rel(gb[n], ga[n]) < 3e-2, (n, _rel(gb[n], ga[n]))
+    assert OF.check_status("cuda") == 0
+
+
+def w_fused_optimizer_vs_nccl(rank, world):
+    import copy
+    import torch.distributed as dist
+    from optimus_lm_b200.engine import EngineArgs, TrainEngine
+    from optimus_lm_b200.ops import functional as OF
+    losses = {}
+    for fused in (False, True):
+        args = EngineArgs(model_choice="allenai/OLMoE-1B-7B-0924--L2-SH0.125-SA0.25-SE0.125-SC0.25-SI0.5",
+                          batch_size=2, context_size=128, optimizer="pgshard", warmup_steps=2, expert_parallelism=world,
+                          use_fused_ep_alltoall=fused, use_fused_optimizer=fused,
+                          config_overrides={"vocab_size": 1024, "max_position_embeddings": 128,
+                                            "output_router_logits": True})
+        eng = TrainEngine(args)
+        g = torch.Generator().manual_seed(5 + rank)
+        out = []
+        for s in range(5):
+            tok = torch.randint(0, 1024, (2, 128), generator=g)
+            o = eng.train_step(tok.cuda())
+            out.append((o.loss.item(), o.grad_norm.item()))
+        losses[fused] = out
+        assert eng.check_device_status() == 0
+    for (la, na), (lb, nb) in zip(losses[False], losses[True]):
+        assert abs(la - lb) < 3e-2 * abs(la), (losses)
+        assert abs(na - nb) < 5e-2 * abs(na) + 1e-3, (losses)
+
+
+# ----------------------------------------------------------------------------- tests
+def test_symm_barrier_and_pull_reduce():
+    _run("w_symm_barrier_and_pull", 2)
+
+
+def test_fused_ep_moe_matches_allgather_transport():
+    _run("w_fused_ep_vs_allgather", 2)
+
+
+def test_fused_engine_matches_nccl_engine():
+    _run("w_fused_optimizer_vs_nccl", 2)
