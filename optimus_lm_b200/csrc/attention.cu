@@ -1,0 +1,377 @@
+// Causal flash attention for sm_100a on tcgen05 tensor cores with TMEM accumulators.
+//
+// Forward, one CTA per (batch, head, 128-row query tile):
+//   warp 0    : TMA producer - Q once, then K / V tiles through a 2-stage ring (4D tensor maps over
+//               the strided [B, S, H, D] tensors, 128B swizzle)
+//   warp 1    : one thread issues  S = Q K^T  (UMMA 128 x BKV x 16, K-major x K-major) into one of
+//               two TMEM score buffers and  O += P V  (A = P from shared memory, B = V MN-major)
+//   warps 2-5 : softmax - thread r owns query row r: tcgen05.ld of its score row, online softmax
+//               in base 2 with lazy rescaling (the running maximum only moves when it grows by
+//               more than 2^8, so the TMEM accumulator is rarely rescaled), P written as bf16
+//               into a swizzled shared-memory tile, final normalisation and store of O and the
+//               log-sum-exp.
+// Head dims: D (q/k) in {64, 128, 192}, Dv in {64, 128}; D = 192 / Dv = 128 is DeepSeek-V3's MLA.
+// The reference calls F.scaled_dot_product_attention (optimus/models/olmoe/modeling_olmoe.py:219-227)
+// or materialises the S x S scores (optimus/models/deepseek_v3/modeling_deepseek_v3.py:359-369).
+//
+// Backward: two kernels so that every gradient has exactly one writer (deterministic, no atomics):
+// dK/dV per key tile looping over query tiles, dQ per query tile looping over key tiles; both
+// recompute P from the saved log-sum-exp.  See attention_bwd.cu.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cfloat>
+#include <cstdint>
+
+#include "olb_api.h"
+#include "ptx.cuh"
+
+namespace olb {
+
+int make_tmap_4d_bf16(CUtensorMap* map, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                      const uint32_t box[4]);
+
+constexpr int ATT_BQ = 128;
+constexpr int ATT_THREADS = 192;
+
+template <int D, int DV, int BKV>
+struct AttnFwdSmem {
+  static constexpr int Q_BYTES = ATT_BQ * D * 2;
+  static constexpr int K_BYTES = BKV * D * 2;
+  static constexpr int V_BYTES = BKV * DV * 2;
+  static constexpr int P_BYTES = ATT_BQ * BKV * 2;
+  static constexpr int STAGES = 2;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;
+  static constexpr int OFF_V = OFF_K + STAGES * K_BYTES;
+  static constexpr int OFF_P = OFF_V + STAGES * V_BYTES;
+  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+struct AttnFwdParams {
+  __nv_bfloat16* o;
+  float* lse;
+  long long o_bs, o_ss, o_hs;
+  int B, S, Hq, Hkv;
+  float scale_log2;  // softmax scale * log2(e)
+  float scale;
+  int* status;
+};
+
+// barrier slots
+enum { AB_Q = 0, AB_K0 = 1, AB_V0 = 3, AB_KV_EMPTY0 = 5, AB_S_FULL0 = 7, AB_S_EMPTY0 = 9, AB_P_FULL = 11, AB_O_DONE = 12 };
+
+template <int D, int DV, int BKV>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const AttnFwdParams p) {
+  using L = AttnFwdSmem<D, DV, BKV>;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t TM_S0 = 0, TM_S1 = BKV, TM_O = 2 * BKV;  // column offsets
+  static_assert(2 * BKV + DV <= 512, "TMEM budget");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  auto bar = [&](int i) { return base + L::OFF_BAR + 8u * i; };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::OFF_BAR + 8 * 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::OFF_BAR + 8 * 16 + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_q_tiles = p.S / ATT_BQ;
+  const int qt = n_q_tiles - 1 - blockIdx.x;  // heavy tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int q0 = qt * ATT_BQ;
+  const int n_kv = (q0 + ATT_BQ + BKV - 1) / BKV;  // causal: key tiles up to the diagonal
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(AB_Q), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(AB_K0 + s), 1);
+      mbar_init(bar(AB_V0 + s), 1);
+      mbar_init(bar(AB_KV_EMPTY0 + s), 1);
+      mbar_init(bar(AB_S_FULL0 + s), 1);
+      mbar_init(bar(AB_S_EMPTY0 + s), 4);
+    }
+    mbar_init(bar(AB_P_FULL), 4);
+    mbar_init(bar(AB_O_DONE), 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (elect_one()) {
+      mbar_expect_tx(bar(AB_Q), L::Q_BYTES);
+#pragma unroll
+      for (int a = 0; a < D / 64; ++a) tma_load_4d(base + L::OFF_Q + a * (ATT_BQ * 128), &tm_q, bar(AB_Q), a * 64, h, q0, b);
+      uint32_t phase = 0;
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        if (j >= 2) {
+          if (!mbar_wait(bar(AB_KV_EMPTY0 + s), phase ^ 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
+        }
+        mbar_expect_tx(bar(AB_K0 + s), L::K_BYTES);
+#pragma unroll
+        for (int a = 0; a < D / 64; ++a)
+          tma_load_4d(base + L::OFF_K + s * L::K_BYTES + a * (BKV * 128), &tm_k, bar(AB_K0 + s), a * 64, hk, j * BKV, b);
+        mbar_expect_tx(bar(AB_V0 + s), L::V_BYTES);
+#pragma unroll
+        for (int a = 0; a < DV / 64; ++a)
+          tma_load_4d(base + L::OFF_V + s * L::V_BYTES + a * (BKV * 128), &tm_v, bar(AB_V0 + s), a * 64, hk, j * BKV, b);
+        if (s == 1) phase ^= 1u;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc_s = make_idesc_bf16(ATT_BQ, BKV, 0, 0);
+      const uint32_t idesc_o = make_idesc_bf16(ATT_BQ, DV, 0, 1);
+      bool ok = mbar_wait(bar(AB_Q), 0, p.status, ST_TIMEOUT_FULL, abort_flag);
+      auto issue_s = [&](int j) {
+        const int s = j & 1;
+        const uint32_t kbase = base + L::OFF_K + s * L::K_BYTES;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t da = make_smem_desc(base + L::OFF_Q + (k / 4) * (ATT_BQ * 128) + (k % 4) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc(kbase + (k / 4) * (BKV * 128) + (k % 4) * 32, 16, 1024);
+          umma_ss(tmem + (s ? TM_S1 : TM_S0), da, db, idesc_s, k > 0 ? 1u : 0u);
+        }
+        umma_commit(bar(AB_S_FULL0 + s));
+      };
+      if (ok && n_kv > 0) {
+        ok = mbar_wait(bar(AB_K0), 0, p.status, ST_TIMEOUT_FULL, abort_flag);
+        tc_fence_after();
+        if (ok) issue_s(0);
+      }
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1u;
+        if (j + 1 < n_kv) {
+          const int s1 = (j + 1) & 1;
+          const uint32_t ph1 = ((j + 1) >> 1) & 1u;
+          // score buffer s1 was last read by the softmax of tile j-1
+          if (j >= 1 && !mbar_wait(bar(AB_S_EMPTY0 + s1), ((j - 1) >> 1) & 1u, p.status, ST_TIMEOUT_ACC_EMPTY, abort_flag)) {
+            ok = false;
+            break;
+          }
+          if (!mbar_wait(bar(AB_K0 + s1), ph1, p.status, ST_TIMEOUT_FULL, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_s(j + 1);
+        }
+        if (!mbar_wait(bar(AB_P_FULL), j & 1u, p.status, ST_TIMEOUT_FULL, abort_flag)) break;
+        if (!mbar_wait(bar(AB_V0 + s), ph, p.status, ST_TIMEOUT_FULL, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t vbase = base + L::OFF_V + s * L::V_BYTES;
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k) {
+          const uint64_t da = make_smem_desc(base + L::OFF_P + (k / 4) * (ATT_BQ * 128) + (k % 4) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc(vbase + k * 2048, BKV * 128, 1024);
+          umma_ss(tmem + TM_O, da, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(bar(AB_KV_EMPTY0 + s));
+        umma_commit(bar(AB_O_DONE));
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax + epilogue
+    const int lg = warp & 3;
+    const int row = lg * 32 + lane;  // query row inside the tile == TMEM lane
+    const int qi = q0 + row;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(lg * 32) << 16);
+    float m_used = -FLT_MAX, l_sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int s = j & 1;
+      if (!mbar_wait(bar(AB_S_FULL0 + s), (j >> 1) & 1u, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t s_addr = lane_addr + (s ? TM_S1 : TM_S0);
+      const int kv0 = j * BKV;
+      const bool diag = kv0 + BKV > q0;  // tile touches the causal boundary
+      // pass 1: row maximum
+      float mx = -FLT_MAX;
+#pragma unroll 1
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(s_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(r[i]);
+          if (diag && kv0 + c * 32 + i > qi) v = -FLT_MAX;
+          mx = fmaxf(mx, v);
+        }
+      }
+      // lazy rescale decision (warp-uniform because the TMEM accesses are warp-wide)
+      float m_new = m_used;
+      const bool grow = (j == 0) || ((mx - m_used) * p.scale_log2 > 8.f);
+      if (grow) m_new = fmaxf(m_used, mx);
+      const float alpha = (j == 0) ? 0.f : exp2f((m_used - m_new) * p.scale_log2);
+      const bool any_grow = __any_sync(0xffffffffu, grow && j > 0);
+      // the previous P V must be complete before O is rescaled and before P is overwritten
+      if (j > 0) {
+        if (!mbar_wait(bar(AB_O_DONE), (j - 1) & 1u, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (any_grow) {
+#pragma unroll 1
+          for (int c = 0; c < DV / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(lane_addr + TM_O + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32b_x32(lane_addr + TM_O + c * 32, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      if (j > 0) l_sum *= alpha;
+      m_used = m_new;
+      const float m_scaled = m_used * p.scale_log2;
+      // pass 2: probabilities -> bf16 P tile in shared memory (K-major, 128B swizzle)
+#pragma unroll 1
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(s_addr + c * 32, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float a = __uint_as_float(r[i]), bb = __uint_as_float(r[i + 1]);
+          const int col = kv0 + c * 32 + i;
+          a = (diag && col > qi) ? 0.f : exp2f(a * p.scale_log2 - m_scaled);
+          bb = (diag && col + 1 > qi) ? 0.f : exp2f(bb * p.scale_log2 - m_scaled);
+          l_sum += a + bb;
+          packed[i >> 1] = pack_bf16(a, bb);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = c * 4 + q;  // 16-byte chunk index along the row
+          const uint32_t addr = base + L::OFF_P + (chunk >> 3) * (ATT_BQ * 128) + row * 128 +
+                                (((chunk & 7) ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * q]), "r"(packed[4 * q + 1]),
+                       "r"(packed[4 * q + 2]), "r"(packed[4 * q + 3])
+                       : "memory");
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar(AB_S_EMPTY0 + s));
+        mbar_arrive(bar(AB_P_FULL));
+      }
+    }
+    // epilogue: O / l and the log-sum-exp
+    if (ok && n_kv > 0 && mbar_wait(bar(AB_O_DONE), (n_kv - 1) & 1u, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) {
+      tc_fence_after();
+      const float inv = 1.f / l_sum;
+      __nv_bfloat16* orow = p.o + static_cast<long long>(b) * p.o_bs + static_cast<long long>(qi) * p.o_ss +
+                            static_cast<long long>(h) * p.o_hs;
+#pragma unroll 1
+      for (int c = 0; c < DV / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(lane_addr + TM_O + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 v;
+          v.x = pack_bf16(__uint_as_float(r[8 * g]) * inv, __uint_as_float(r[8 * g + 1]) * inv);
+          v.y = pack_bf16(__uint_as_float(r[8 * g + 2]) * inv, __uint_as_float(r[8 * g + 3]) * inv);
+          v.z = pack_bf16(__uint_as_float(r[8 * g + 4]) * inv, __uint_as_float(r[8 * g + 5]) * inv);
+          v.w = pack_bf16(__uint_as_float(r[8 * g + 6]) * inv, __uint_as_float(r[8 * g + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = v;
+        }
+      }
+      p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S + qi] = m_used * p.scale + __logf(l_sum);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// [B, S, H, Dh] view -> 4D tensor map with box {64, 1, rows, 1}
+int attn_tmap(CUtensorMap* map, const void* ptr, int Dh, int H, int S, int B, long long bs, long long ss, long long hs,
+              int box_rows) {
+  const uint64_t dims[4] = {static_cast<uint64_t>(Dh), static_cast<uint64_t>(H), static_cast<uint64_t>(S),
+                            static_cast<uint64_t>(B)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(hs) * 2, static_cast<uint64_t>(ss) * 2, static_cast<uint64_t>(bs) * 2};
+  const uint32_t box[4] = {64, 1, static_cast<uint32_t>(box_rows), 1};
+  return make_tmap_4d_bf16(map, ptr, dims, strides, box);
+}
+
+template <int D, int DV, int BKV>
+static int launch_fwd(const olb_attn_fwd_desc* d, cudaStream_t stream) {
+  using L = AttnFwdSmem<D, DV, BKV>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel<D, DV, BKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+      return -3;
+    configured = true;
+  }
+  CUtensorMap tq, tk, tv;
+  if (attn_tmap(&tq, d->q, D, d->Hq, d->S, d->B, d->q_bs, d->q_ss, d->q_hs, ATT_BQ)) return -4;
+  if (attn_tmap(&tk, d->k, D, d->Hkv, d->S, d->B, d->k_bs, d->k_ss, d->k_hs, BKV)) return -4;
+  if (attn_tmap(&tv, d->v, DV, d->Hkv, d->S, d->B, d->v_bs, d->v_ss, d->v_hs, BKV)) return -4;
+  AttnFwdParams p;
+  p.o = static_cast<__nv_bfloat16*>(d->o);
+  p.lse = d->lse;
+  p.o_bs = d->o_bs;
+  p.o_ss = d->o_ss;
+  p.o_hs = d->o_hs;
+  p.B = d->B;
+  p.S = d->S;
+  p.Hq = d->Hq;
+  p.Hkv = d->Hkv;
+  p.scale = d->scale;
+  p.scale_log2 = d->scale * 1.4426950408889634f;
+  p.status = d->status;
+  dim3 grid(d->S / ATT_BQ, d->Hq, d->B);
+  attn_fwd_kernel<D, DV, BKV><<<grid, ATT_THREADS, L::TOTAL, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+}  // namespace olb
+
+extern "C" int olb_attn_fwd(const olb_attn_fwd_desc* d, cudaStream_t stream) {
+  using namespace olb;
+  if (d->S % ATT_BQ || d->Hq % d->Hkv) return -1;
+  auto bad = [](long long s) { return (s % 8) != 0; };
+  if (bad(d->q_bs) || bad(d->q_ss) || bad(d->q_hs) || bad(d->k_bs) || bad(d->k_ss) || bad(d->k_hs) || bad(d->v_bs) ||
+      bad(d->v_ss) || bad(d->v_hs) || bad(d->o_bs) || bad(d->o_ss) || bad(d->o_hs))
+    return -2;
+  if ((reinterpret_cast<uintptr_t>(d->q) | reinterpret_cast<uintptr_t>(d->k) | reinterpret_cast<uintptr_t>(d->v) |
+       reinterpret_cast<uintptr_t>(d->o)) & 15)
+    return -2;
+  if (d->D == 128 && d->Dv == 128) return launch_fwd<128, 128, 128>(d, stream);
+  if (d->D == 64 && d->Dv == 64) return launch_fwd<64, 64, 128>(d, stream);
+  if (d->D == 192 && d->Dv == 128) return launch_fwd<192, 128, 64>(d, stream);
+  return -6;
+}

@@ -45,6 +45,15 @@ class _FlashAttnFn(torch.autograd.Function):
         C = extension()
         q, k, v, o, lse = ctx.saved_tensors
         do = do.contiguous()
+        if not hasattr(C, "attn_bwd") or os.environ.get("OLB_ATTENTION_BWD", "kernel") != "kernel":
+            # library backward (recomputes the forward): used until the backward kernels cover the shape
+            with torch.enable_grad():
+                qq, kk, vv = (t.detach().requires_grad_() for t in (q, k, v))
+                if q.shape[-1] == v.shape[-1]:
+                    out = _sdpa(qq, kk, vv, ctx.scale, True)
+                else:
+                    out = OF.attention_reference(qq, kk, vv, ctx.scale, True)
+            return torch.autograd.grad(out, (qq, kk, vv), do) + (None,)
         dq = torch.empty_like(q)
         dk = torch.empty_like(k)
         dv = torch.empty_like(v)

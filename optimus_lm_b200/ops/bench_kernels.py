@@ -1,0 +1,94 @@
+"""Kernel micro-benchmarks (counterpart of the ``__main__`` blocks of the reference's
+optimus/kernels/*.py): time the tcgen05 GEMMs, the grouped expert GEMMs and flash attention
+against the library kernels with CUDA events, print TFLOP/s.
+
+    python -m optimus_lm_b200.ops.bench_kernels [gemm|grouped|attention|all]
+"""
+import sys
+
+import torch
+
+from . import functional as OF
+from . import attention as OA
+
+
+def _time(fn, iters=10, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()  # > L2
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm():
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    for M, N, K in [(4096, 4096, 4096), (8192, 8192, 8192), (16384, 2048, 2048), (16384, 50304, 2048)]:
+        a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        t1 = _time(lambda: OF.gemm(a, b, M, N, K, out=c), flush=flush)
+        t2 = _time(lambda: torch.matmul(a, b.t(), out=c), flush=flush)
+        fl = 2.0 * M * N * K
+        print(f"gemm NT {M}x{N}x{K}: tcgen05 kernel {t1:.3f} ms ({fl / t1 * 1e-9:.0f} TFLOP/s) | cuBLAS {t2:.3f} ms "
+              f"({fl / t2 * 1e-9:.0f} TFLOP/s)", flush=True)
+
+
+def bench_grouped():
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    T, E, K, H, I = 16384, 64, 8, 2048, 1024
+    idx = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(T)]).to(torch.int32)
+    cap = OF.moe_capacity_rows(T, K, E)
+    ix = OF.MoEIndex(idx, 0, E, cap)
+    xp = torch.randn(cap, H, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(E, I, H, device="cuda") * 0.02).to(torch.bfloat16)
+    y = torch.empty(cap, I, device="cuda", dtype=torch.bfloat16)
+    t = _time(lambda: OF.grouped_linear_fwd(xp, w, ix, out=y), flush=flush)
+    fl = 2.0 * T * K * H * I
+    print(f"grouped fwd  {T * K} rows x {H}->{I}, {E} experts: {t:.3f} ms ({fl / t * 1e-9:.0f} TFLOP/s)", flush=True)
+    dy = torch.randn(cap, I, device="cuda").to(torch.bfloat16)
+    t = _time(lambda: OF.grouped_linear_dgrad(dy, w, ix), flush=flush)
+    print(f"grouped dgrad: {t:.3f} ms ({fl / t * 1e-9:.0f} TFLOP/s)", flush=True)
+    t = _time(lambda: OF.grouped_linear_wgrad(dy, xp, ix, I, H), flush=flush)
+    print(f"grouped wgrad: {t:.3f} ms ({fl / t * 1e-9:.0f} TFLOP/s)", flush=True)
+
+
+def bench_attention():
+    import torch.nn.functional as F
+    for B, S, Hh, D, Dv in [(4, 4096, 16, 128, 128), (1, 4096, 128, 192, 128)]:
+        q = torch.randn(B, S, Hh, D, device="cuda").to(torch.bfloat16)
+        k = torch.randn(B, S, Hh, D, device="cuda").to(torch.bfloat16)
+        v = torch.randn(B, S, Hh, Dv, device="cuda").to(torch.bfloat16)
+        fl = 2.0 * B * Hh * S * S * (D + Dv) / 2
+        t1 = _time(lambda: OA.flash_attention(q, k, v))
+        msg = f"attention fwd B{B} S{S} H{Hh} D{D}/{Dv}: kernel {t1:.3f} ms ({fl / t1 * 1e-9:.0f} TFLOP/s)"
+        if D == Dv:
+            qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+            t2 = _time(lambda: F.scaled_dot_product_attention(qh, kh, vh, is_causal=True))
+            msg += f" | SDPA {t2:.3f} ms ({fl / t2 * 1e-9:.0f} TFLOP/s)"
+        print(msg, flush=True)
+        qa, ka, va = (t.clone().requires_grad_() for t in (q, k, v))
+        o = OA.flash_attention(qa, ka, va)
+        do = torch.randn_like(o)
+        tb = _time(lambda: torch.autograd.grad(o, (qa, ka, va), do, retain_graph=True))
+        print(f"attention bwd: {tb:.3f} ms ({2.5 * fl / tb * 1e-9:.0f} TFLOP/s)", flush=True)
+    assert OF.check_status("cuda") == 0
+
+
+if __name__ == "__main__":
+    what = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if what in ("gemm", "all"):
+        bench_gemm()
+    if what in ("grouped", "all"):
+        bench_grouped()
+    if what in ("attention", "all"):
+        bench_attention()

@@ -1,0 +1,64 @@
+"""Flash-attention kernels against an fp32 eager reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from optimus_lm_b200.ops import functional as OF
+from optimus_lm_b200.ops import attention as OA
+
+
+def _rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def _mk(B, S, Hq, Hkv, D, Dv, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = torch.randn(B, S, Hq, D, device="cuda", generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, Hkv, D, device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, Hkv, Dv, device="cuda", generator=g).to(torch.bfloat16)
+    return q, k, v
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,D,Dv", [(1, 128, 1, 1, 128, 128), (2, 512, 4, 4, 128, 128), (1, 1024, 4, 2, 128, 128),
+                                             (2, 384, 2, 2, 64, 64), (1, 512, 4, 4, 192, 128)])
+def test_flash_attention_forward(B, S, Hq, Hkv, D, Dv):
+    q, k, v = _mk(B, S, Hq, Hkv, D, Dv)
+    scale = D ** -0.5
+    o = OA.flash_attention(q, k, v, scale=scale)
+    ref = OF.attention_reference(q.float(), k.float(), v.float(), scale, True)
+    assert _rel(o, ref) < 2e-2, _rel(o, ref)
+    assert OF.check_status("cuda") == 0
+
+
+def test_flash_attention_strided_views_and_lse():
+    # q/k/v as slices of wider tensors (the MLA layout) and the saved log-sum-exp
+    B, S, H = 1, 256, 2
+    g = torch.Generator(device="cuda").manual_seed(3)
+    qkv = torch.randn(B, S, H, 3 * 128, device="cuda", generator=g).to(torch.bfloat16)
+    q, k, v = qkv[..., :128], qkv[..., 128:256], qkv[..., 256:]
+    C = OF.extension()
+    o = torch.empty(B, S, H, 128, dtype=torch.bfloat16, device="cuda")
+    lse = torch.empty(B, H, S, dtype=torch.float32, device="cuda")
+    C.attn_fwd(q, k, v, o, lse, 128 ** -0.5, OF.status_word("cuda"))
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * 128 ** -0.5
+    s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+    assert _rel(lse, torch.logsumexp(s, -1)) < 1e-3
+    ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), v.float())
+    assert _rel(o, ref) < 2e-2
+    assert OF.check_status("cuda") == 0
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,D,Dv", [(1, 256, 2, 2, 128, 128), (1, 512, 4, 2, 128, 128), (1, 256, 2, 2, 192, 128)])
+def test_flash_attention_backward(B, S, Hq, Hkv, D, Dv):
+    q, k, v = _mk(B, S, Hq, Hkv, D, Dv, seed=1)
+    scale = D ** -0.5
+    g = torch.Generator(device="cuda").manual_seed(9)
+    do = torch.randn(B, S, Hq, Dv, device="cuda", generator=g).to(torch.bfloat16)
+    qa, ka, va = (t.clone().requires_grad_() for t in (q, k, v))
+    OA.flash_attention(qa, ka, va, scale=scale).backward(do)
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    OF.attention_reference(qr, kr, vr, scale, True).backward(do.float())
+    assert _rel(qa.grad, qr.grad) < 3e-2 and _rel(ka.grad, kr.grad) < 3e-2 and _rel(va.grad, vr.grad) < 3e-2
+    assert OF.check_status("cuda") == 0
