@@ -120,97 +120,21 @@ def init_weights(model: nn.Module, std: float, seed: int = 0):
     (generate_serial_model.py:118-158): Linear / Embedding / merged expert weights ~ N(0, std),
     padding row of the embedding zeroed, norm weights = 1.  The generator is seeded per
     parameter name, so a parameter gets the same values whatever rank builds it."""
-    import re
-    import zlib
+    from . import model_io
 
-    inner = getattr(model, "model", model)
-    pmap = getattr(model, "pmap", None)
-    tp = pmap.tensor_parallelism if pmap is not None else 1
-    tp_ind = pmap.tp_ind if pmap is not None else 0
+    device = next(model.parameters()).device
 
-    def global_layer(l: int) -> int:
-        if hasattr(inner, "global_layer_index"):
-            return inner.global_layer_index(l)
-        if hasattr(inner, "layer_ids"):
-            return inner.layer_ids[l]
-        return getattr(inner, "layer_start_idx", 0) + l
+    def draw(serial_name, serial_shape):
+        return model_io.seeded_serial_tensor(serial_name, serial_shape, std, seed, device=device)
 
-    def fill(t, key, shape=None):
-        """N(0, std) values determined by ``key`` alone (independent of the rank that draws them)."""
-        g = torch.Generator(device=t.device)
-        g.manual_seed((seed * 1000003 + zlib.crc32(key.encode())) % (2 ** 63))
-        shape = tuple(t.shape) if shape is None else shape
-        n = 1
-        for d in shape:
-            n *= d
-        if shape == tuple(t.shape) and n > (1 << 28):
-            flat = t.view(-1)  # big tensors: fp32 pieces bound the temporary
-            step = 1 << 26
-            for s in range(0, n, step):
-                e = min(s + step, n)
-                flat[s:e].copy_(torch.randn(e - s, device=t.device, dtype=torch.float32, generator=g) * std)
-            return None
-        full = torch.randn(shape, device=t.device, dtype=torch.float32, generator=g) * std
-        if shape == tuple(t.shape):
-            t.copy_(full)
-            return None
-        return full
-
-    modules = dict(model.named_modules())
-    for name, p in model.named_parameters():
-        if p.dim() == 1 and ("norm" in name or "layernorm" in name):
-            p.fill_(1.0)
-            continue
-        # the seed key uses global layer / expert indices so that every parallel layout draws the
-        # same model
-        key = name
-        m = re.match(r"^(.*layers\.)(\d+)(\..*)$", key)
-        if m:
-            key = f"{m.group(1)}{global_layer(int(m.group(2)))}{m.group(3)}"
-        owner = modules.get(name.rsplit(".", 1)[0])
-        m = re.match(r"^(.*\.experts\.)(\d+)(\..*)$", key)
-        if m:
-            block = modules.get(name.split(".experts.")[0])
-            e0 = getattr(block, "expert_start_idx", 0)
-            key = f"{m.group(1)}{e0 + int(m.group(2))}{m.group(3)}"
-            fill(p, key)
-        elif name.endswith("_merged_weight"):
-            block = modules.get(name.split(".experts.")[0])
-            e0 = getattr(block, "expert_start_idx", 0)
-            proj = name.rsplit(".", 1)[1].replace("_merged_weight", "")
-            base = key.rsplit(".", 1)[0]
-            for le in range(p.shape[0]):
-                fill(p[le], f"{base}.{e0 + le}.{proj}.weight")
-        elif tp > 1 and owner is not None and hasattr(owner, "intermediate_size_per_rank") is False and \
-                type(owner).__name__ in ("ParallelEmbedding", "ParallelLMHead"):
-            if type(owner).__name__ == "ParallelEmbedding":
-                full = fill(p, key, (owner.vocab_size_padded, p.shape[1]))
-                full[owner.vocab_size:].zero_()
-                p.copy_(full[owner.start_embedding_id:owner.end_embedding_id])
-            else:
-                full = fill(p, key, (p.shape[0], p.shape[1] * tp))
-                p.copy_(full[:, tp_ind * p.shape[1]:(tp_ind + 1) * p.shape[1]])
-        elif tp > 1 and p.dim() == 2 and re.search(r"\.(q|k|v|gate|up)_proj\.weight$", name):
-            full = fill(p, key, (p.shape[0] * tp, p.shape[1]))
-            p.copy_(full[tp_ind * p.shape[0]:(tp_ind + 1) * p.shape[0]])
-        elif tp > 1 and p.dim() == 2 and re.search(r"\.(o|down)_proj\.weight$", name):
-            full = fill(p, key, (p.shape[0], p.shape[1] * tp))
-            p.copy_(full[:, tp_ind * p.shape[1]:(tp_ind + 1) * p.shape[1]])
-        elif owner is not None and getattr(owner, "pmap", None) is not None and hasattr(owner, "intermediate_size_per_rank") \
-                and owner.intermediate_size_per_rank != owner.intermediate_size and tp == 1:
-            # DeepSeek-V3 dense MLP: intermediate dimension sharded over the EP group
-            ep, ei = owner.pmap.expert_parallelism, owner.pmap.ep_ind
-            if name.endswith("down_proj.weight"):
-                full = fill(p, key, (p.shape[0], p.shape[1] * ep))
-                p.copy_(full[:, ei * p.shape[1]:(ei + 1) * p.shape[1]])
-            else:
-                full = fill(p, key, (p.shape[0] * ep, p.shape[1]))
-                p.copy_(full[ei * p.shape[0]:(ei + 1) * p.shape[0]])
-        else:
-            fill(p, key)
+    # every local parameter is cut out of its serial tensor, which is drawn from the serial name:
+    # all parallel layouts (PP/VPP/EP/TP, merged or per-expert) therefore hold the same model
+    model_io.fill_shard(model, draw)
     for mod in model.modules():
         if isinstance(mod, nn.Embedding) and mod.padding_idx is not None:
             mod.weight[mod.padding_idx].zero_()
+        elif getattr(mod, "local_padding_idx", None) is not None:
+            mod.weight[mod.local_padding_idx].zero_()
     for name, b in model.named_buffers():
         if name.endswith("e_score_correction_bias"):
             b.zero_()
