@@ -136,9 +136,15 @@ def run_ours(opts):
             dist.barrier()
         torch.cuda.synchronize()
 
+    from optimus_lm_b200.engine import get_learning_rate
+
+    def step(batch):
+        # the training recipe's schedule: linear warm-up from min_lr over 2500 optimizer steps
+        engine.set_lr(get_learning_rate(engine.step_id, 1 << 20, args))
+        return engine.train_step(batch)
+
     for i in range(opts.warmup):
-        engine.set_lr(4e-4)
-        out = engine.train_step(dev_batches[i])
+        out = step(dev_batches[i])
     barrier()
     status = engine.check_device_status()
 
@@ -152,7 +158,7 @@ def run_ours(opts):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for i in range(opts.steps):
-        out = engine.train_step(dev_batches[opts.warmup + i])
+        out = step(dev_batches[opts.warmup + i])
     ev1.record()
     barrier()
     dev_ms = ev0.elapsed_time(ev1)
@@ -163,17 +169,27 @@ def run_ours(opts):
     barrier()
     t0 = time.perf_counter()
     for i in range(opts.steps):
-        out = engine.train_step(host_batches[opts.warmup + opts.steps + i])
+        out = step(host_batches[opts.warmup + opts.steps + i])
         e2e_loss = out.loss.item()
     barrier()
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else None
     status = status or engine.check_device_status()
 
-    t = torch.tensor([dev_ms, e2e_s], dtype=torch.float64, device=dev)
+    t = torch.tensor([dev_ms, e2e_s, float(status)], dtype=torch.float64, device=dev)
     if dist.is_initialized():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_s = t[0].item(), t[1].item()
+    dev_ms, e2e_s, status = t[0].item(), t[1].item(), int(t[2].item())
+    if status != 0:
+        # a kernel reported a timeout or a buffer overflow (e.g. more routed rows than the expert-parallel
+        # receive buffers hold): the step did not do all of its work, so there is no number to report
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "error": f"device status word = {status} on some rank; run invalid",
+                              "n_gpus": n, "impl": "optimus_lm_b200"}), flush=True)
+        if dist.is_initialized():
+            dist.barrier()
+            dist.destroy_process_group()
+        sys.exit(3)
     if rank == 0:
         value = tokens_per_step * opts.steps / (dev_ms / 1e3)
         e2e_value = tokens_per_step * opts.steps / e2e_s

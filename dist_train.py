@@ -139,6 +139,12 @@ def build_parser():
     p.add_argument("--disable_fused_ep_alltoall", action="store_true", help="Use the NCCL all-gather/reduce-scatter EP transport")
     p.add_argument("--disable_fused_optimizer", action="store_true", help="Use NCCL collectives in the optimizer step")
     p.add_argument("--router_z_loss_coef", type=float, default=0.0)
+    p.add_argument("--moe_capacity_factor", type=float, default=None,
+                   help="Rows of the expert-parallel receive buffers as a multiple of the balanced share "
+                        "(0 = worst case, can never overflow); a rank that receives more raises an error")
+    p.add_argument("--enable_tb_logging", action="store_true",
+                   help="Write loss / grad norm / lr / throughput scalars to <exp_dir>/scalars.jsonl and, when "
+                        "tensorboard is installed, to <exp_dir>/tb")
     p.add_argument("--dist_timeout_s", type=float, default=1800.0)
     p.add_argument("--chrome_trace", type=str, default=None, help="Write a Chrome trace of the profiled regions here")
     return p
@@ -201,6 +207,28 @@ def local_grad_norm(engine) -> torch.Tensor:
     return acc.sqrt().reshape(())
 
 
+class ScalarLog:
+    """Per-step scalars of the logging rank: one JSON object per line in ``scalars.jsonl`` and, when the
+    ``tensorboard`` package is importable, the same values under ``<exp_dir>/tb``."""
+
+    def __init__(self, exp_dir):
+        os.makedirs(exp_dir, exist_ok=True)
+        self.fh = open(os.path.join(exp_dir, "scalars.jsonl"), "a")
+        try:
+            from torch.utils.tensorboard import SummaryWriter
+            self.tb = SummaryWriter(os.path.join(exp_dir, "tb"))
+        except Exception:
+            self.tb = None
+
+    def write(self, step, scalars):
+        import json
+        self.fh.write(json.dumps({"step": int(step), **{k: float(v) for k, v in scalars.items()}}) + "\n")
+        self.fh.flush()
+        if self.tb is not None:
+            for k, v in scalars.items():
+                self.tb.add_scalar(k, float(v), int(step))
+
+
 def report_soft_failures(flags, pmap, rank, world_size):
     """Append the nodes of the flagged ranks to launch_info/<job>/failed_soft_nodes.txt."""
     if rank != 0:
@@ -259,6 +287,8 @@ def main(argv=None):
     # ------------------------------------------------------------------ model + optimizer
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
     overrides = {"router_z_loss_coef": args.router_z_loss_coef} if args.router_z_loss_coef else {}
+    if args.moe_capacity_factor is not None:
+        overrides["moe_capacity_factor"] = args.moe_capacity_factor
     config, model = build_model(
         args.model_choice, pmap, dtype=dtype, device=device, memory_tracker=memory_tracker, config_overrides=overrides,
         pipeline_parallelism=args.pipeline_parallelism, expert_parallelism=args.expert_parallelism,
@@ -325,6 +355,7 @@ def main(argv=None):
 
     # ------------------------------------------------------------------ loop
     is_logger = (pmap.is_last_stage_rank and pmap.dp_ind == 0 and pmap.tp_ind == 0 and pmap.ep_ind == 0)
+    scalar_log = ScalarLog(args.exp_dir) if (args.enable_tb_logging and is_logger and args.exp_dir) else None
     flops_per_seq = model.get_flops(args.context_size) if hasattr(model, "get_flops") else 0
     last_log_time = time.time()
     while train_step_id < train_steps:
@@ -401,6 +432,10 @@ def main(argv=None):
             s += f", Local Loss : {(out.loss.item() if out.loss is not None else 0):9.6f}"
             s += f", Local Grad norm : {float(lgn):9.6f}"
             s += f", Rank : {rank} ({pmap.dp_ind},{pmap.pp_ind},{pmap.ep_ind},{pmap.tp_ind})"
+            if is_logger and scalar_log is not None:
+                scalar_log.write(train_step_id, {"loss": global_loss.item(), "grad_norm": float(gn), "lr": lr,
+                                                 "iter_time_s": iter_time,
+                                                 "tokens_per_sec_per_gpu": (args.batch_size * args.context_size) / iter_time})
             if is_logger or args.log_all_ranks:
                 print(s, flush=True)
                 if profiler is not None:

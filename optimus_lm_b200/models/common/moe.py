@@ -111,7 +111,7 @@ class SparseMoeBlock(nn.Module):
         self.force_uniform_routing = getattr(config, "force_uniform_routing", False)
         self.mask = None
         self.use_allreduce_for_reducescatter = False
-        self.capacity_factor = float(getattr(config, "moe_capacity_factor", 2.0))
+        self.capacity_factor = float(getattr(config, "moe_capacity_factor", 4.0))
         self.ep_transport = "alltoall" if getattr(config, "use_fused_ep_alltoall", True) else "allgather"
         self._a2a = None  # lazily built fused dispatcher
         self.last_router_stats = None
