@@ -84,8 +84,48 @@ def bench_attention():
     assert OF.check_status("cuda") == 0
 
 
+def profile_case(name: str, launches: int = 4):
+    """A few launches of ONE kernel on operands larger than L2 and well under a GB each: the case to
+    put under a hardware profiler (``profile-gemm``, ``profile-grouped``, ``profile-attention``,
+    ``profile-rmsnorm-bwd``)."""
+    torch.manual_seed(0)
+    if name == "gemm":
+        M = N = K = 8192
+        a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        fn = lambda: OF.gemm(a, b, M, N, K, out=c)
+    elif name == "grouped":
+        T, E, K, H, I = 16384, 64, 8, 2048, 1024
+        idx = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(T)]).to(torch.int32)
+        ix = OF.MoEIndex(idx, 0, E, OF.moe_capacity_rows(T, K, E))
+        xp = torch.randn(ix.cap, H, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(E, I, H, device="cuda") * 0.02).to(torch.bfloat16)
+        y = torch.empty(ix.cap, I, device="cuda", dtype=torch.bfloat16)
+        fn = lambda: OF.grouped_linear_fwd(xp, w, ix, out=y)
+    elif name == "attention":
+        q, k, v = (torch.randn(4, 4096, 16, 128, device="cuda").to(torch.bfloat16) for _ in range(3))
+        fn = lambda: OA.flash_attention(q, k, v)
+    elif name == "rmsnorm-bwd":
+        x = torch.randn(16384, 2048, device="cuda").to(torch.bfloat16).requires_grad_()
+        w = torch.ones(2048, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        y = OF.rms_norm(x, w, 1e-5)
+        dy = torch.randn_like(y)
+        fn = lambda: torch.autograd.grad(y, (x, w), dy, retain_graph=True)
+    else:
+        raise SystemExit(f"unknown profile case {name}")
+    for _ in range(launches):
+        fn()
+    torch.cuda.synchronize()
+    assert OF.check_status("cuda") == 0
+    print(f"profile case {name}: {launches} launches done", flush=True)
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if what.startswith("profile-"):
+        profile_case(what[len("profile-"):])
+        sys.exit(0)
     if what in ("gemm", "all"):
         bench_gemm()
     if what in ("grouped", "all"):

@@ -50,8 +50,12 @@ def test_flash_attention_strided_views_and_lse():
     assert OF.check_status("cuda") == 0
 
 
-@pytest.mark.parametrize("B,S,Hq,Hkv,D,Dv", [(1, 256, 2, 2, 128, 128), (1, 512, 4, 2, 128, 128), (1, 256, 2, 2, 192, 128)])
+@pytest.mark.parametrize("B,S,Hq,Hkv,D,Dv", [(1, 128, 1, 1, 128, 128), (1, 256, 2, 2, 128, 128), (1, 512, 4, 2, 128, 128),
+                                             (2, 1024, 2, 2, 128, 128), (1, 384, 2, 2, 64, 64), (1, 256, 2, 2, 192, 128),
+                                             (1, 640, 3, 3, 192, 128)])
 def test_flash_attention_backward(B, S, Hq, Hkv, D, Dv):
+    from optimus_lm_b200.ops._ext import extension
+    assert hasattr(extension(), "attn_bwd"), "backward kernels are not in the built extension"
     q, k, v = _mk(B, S, Hq, Hkv, D, Dv, seed=1)
     scale = D ** -0.5
     g = torch.Generator(device="cuda").manual_seed(9)
@@ -61,4 +65,27 @@ def test_flash_attention_backward(B, S, Hq, Hkv, D, Dv):
     qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
     OF.attention_reference(qr, kr, vr, scale, True).backward(do.float())
     assert _rel(qa.grad, qr.grad) < 3e-2 and _rel(ka.grad, kr.grad) < 3e-2 and _rel(va.grad, vr.grad) < 3e-2
+    assert OF.check_status("cuda") == 0
+
+
+def test_flash_attention_backward_strided_and_deterministic():
+    # q / k / v / dO as slices of wider tensors; two runs must agree bit for bit (single writer per element)
+    B, S, H, D = 1, 512, 2, 128
+    g = torch.Generator(device="cuda").manual_seed(5)
+    big = torch.randn(B, S, H, 3 * D + 64, device="cuda", generator=g).to(torch.bfloat16)
+    q, k, v = big[..., :D], big[..., D:2 * D], big[..., 2 * D + 64:3 * D + 64]
+    do_big = torch.randn(B, S, H, 2 * D, device="cuda", generator=g).to(torch.bfloat16)
+    do = do_big[..., D:]
+    grads = []
+    for _ in range(2):
+        qa, ka, va = (t.detach().clone().requires_grad_() for t in (q, k, v))
+        # keep the strided layout: operate on views of a leaf
+        leaf = big.detach().clone().requires_grad_()
+        o = OA.flash_attention(leaf[..., :D], leaf[..., D:2 * D], leaf[..., 2 * D + 64:3 * D + 64])
+        o.backward(do)
+        grads.append(leaf.grad.clone())
+    assert torch.equal(grads[0], grads[1])
+    ref = big.float().detach().requires_grad_()
+    OF.attention_reference(ref[..., :D], ref[..., D:2 * D], ref[..., 2 * D + 64:3 * D + 64], D ** -0.5, True).backward(do.float())
+    assert _rel(grads[0], ref.grad) < 3e-2
     assert OF.check_status("cuda") == 0
