@@ -5,7 +5,8 @@
 //               the strided [B, S, H, D] tensors, 128B swizzle)
 //   warp 1    : one thread issues  S = Q K^T  (UMMA 128 x BKV x 16, K-major x K-major) into one of
 //               two TMEM score buffers and  O += P V  (A = P from shared memory, B = V MN-major)
-//   warps 2-5 : softmax - thread r owns query row r: tcgen05.ld of its score row, online softmax
+//   warps 2-9 : softmax - two threads own query row r (half of the columns each): one tcgen05.ld pass of
+//               the score row into registers, row maxima exchanged between the pair, online softmax
 //               in base 2 with lazy rescaling (the running maximum only moves when it grows by
 //               more than 2^8, so the TMEM accumulator is rarely rescaled), P written as bf16
 //               into a swizzled shared-memory tile, final normalisation and store of O and the
@@ -32,7 +33,7 @@ int make_tmap_4d_bf16(CUtensorMap* map, const void* base, const uint64_t dims[4]
                       const uint32_t box[4]);
 
 constexpr int ATT_BQ = 128;
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 320;  // TMA warp, MMA warp, 8 softmax warps
 
 template <int D, int DV, int BKV>
 struct AttnFwdSmem {
@@ -45,7 +46,8 @@ struct AttnFwdSmem {
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + STAGES * K_BYTES;
   static constexpr int OFF_P = OFF_V + STAGES * V_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int OFF_PAIR = OFF_P + P_BYTES;           // row statistics exchanged between warp pairs
+  static constexpr int OFF_BAR = OFF_PAIR + 2 * 2 * ATT_BQ * 4;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
 
@@ -60,7 +62,7 @@ struct AttnFwdParams {
 };
 
 // barrier slots
-enum { AB_Q = 0, AB_K0 = 1, AB_V0 = 3, AB_KV_EMPTY0 = 5, AB_S_FULL0 = 7, AB_S_EMPTY0 = 9, AB_P_FULL = 11, AB_O_DONE = 12 };
+enum { AB_Q = 0, AB_K0 = 1, AB_V0 = 3, AB_KV_EMPTY0 = 5, AB_S_FULL0 = 7, AB_S_EMPTY0 = 9, AB_P_FULL = 11, AB_O_DONE = 12, AB_PAIR0 = 13 };
 
 template <int D, int DV, int BKV>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
@@ -75,8 +77,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   auto bar = [&](int i) { return base + L::OFF_BAR + 8u * i; };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::OFF_BAR + 8 * 16);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::OFF_BAR + 8 * 16 + 8);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::OFF_BAR + 8 * 20);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::OFF_BAR + 8 * 20 + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_q_tiles = p.S / ATT_BQ;
@@ -93,10 +95,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(bar(AB_V0 + s), 1);
       mbar_init(bar(AB_KV_EMPTY0 + s), 1);
       mbar_init(bar(AB_S_FULL0 + s), 1);
-      mbar_init(bar(AB_S_EMPTY0 + s), 4);
+      mbar_init(bar(AB_S_EMPTY0 + s), 8);
     }
-    mbar_init(bar(AB_P_FULL), 4);
+    mbar_init(bar(AB_P_FULL), 8);
     mbar_init(bar(AB_O_DONE), 1);
+    for (int g = 0; g < 4; ++g) mbar_init(bar(AB_PAIR0 + g), 2);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_q);
@@ -191,10 +194,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else {
     // ---------------------------------------------------------------- softmax + epilogue
+    // Eight warps: warps w and w+4 share the 32 query rows (TMEM lanes) of lane group w % 4 and split the
+    // columns of the score tile.  Each reads its half row from TMEM once, keeps it in registers, and the two
+    // exchange their row maxima through shared memory so that both use the same running maximum.
+    constexpr int CW = BKV / 2;        // score columns per thread
+    constexpr int OW = DV / 2;         // output columns per thread
     const int lg = warp & 3;
-    const int row = lg * 32 + lane;  // query row inside the tile == TMEM lane
+    const int ch = (warp - 2) >> 2;    // column half
+    const int row = lg * 32 + lane;    // query row inside the tile == TMEM lane
     const int qi = q0 + row;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(lg * 32) << 16);
+    float* pair = reinterpret_cast<float*>(gen + L::OFF_PAIR);  // [2 buffers][2 halves][128 rows]
     float m_used = -FLT_MAX, l_sum = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
@@ -204,24 +214,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         break;
       }
       tc_fence_after();
-      const uint32_t s_addr = lane_addr + (s ? TM_S1 : TM_S0);
-      const int kv0 = j * BKV;
-      const bool diag = kv0 + BKV > q0;  // tile touches the causal boundary
-      // pass 1: row maximum
-      float mx = -FLT_MAX;
-#pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
+      const uint32_t s_addr = lane_addr + (s ? TM_S1 : TM_S0) + ch * CW;
+      const int kv0 = j * BKV + ch * CW;
+      const bool diag = kv0 + CW > q0;  // this half tile touches the causal boundary
+      float x[CW];
+#pragma unroll
+      for (int c = 0; c < CW / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(s_addr + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[i]);
-          if (diag && kv0 + c * 32 + i > qi) v = -FLT_MAX;
-          mx = fmaxf(mx, v);
-        }
+        for (int i = 0; i < 32; ++i) x[c * 32 + i] = __uint_as_float(r[i]);
       }
-      // lazy rescale decision (warp-uniform because the TMEM accesses are warp-wide)
+      // the score buffer can be overwritten by the next Q K^T as soon as both halves are in registers
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(AB_S_EMPTY0 + s));
+      float mx = -FLT_MAX;
+#pragma unroll
+      for (int i = 0; i < CW; ++i) {
+        if (diag && kv0 + i > qi) x[i] = -FLT_MAX;
+        mx = fmaxf(mx, x[i]);
+      }
+      float* pb = pair + (j & 1) * 256;
+      pb[ch * 128 + row] = mx;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(AB_PAIR0 + lg));
+      if (!mbar_wait(bar(AB_PAIR0 + lg), j & 1u, p.status, ST_TIMEOUT_PEER, abort_flag)) {
+        ok = false;
+        break;
+      }
+      mx = fmaxf(mx, pb[(ch ^ 1) * 128 + row]);
+      // lazy rescale decision (identical in both warps of a pair: same rows, same maxima)
       float m_new = m_used;
       const bool grow = (j == 0) || ((mx - m_used) * p.scale_log2 > 8.f);
       if (grow) m_new = fmaxf(m_used, mx);
@@ -236,13 +260,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tc_fence_after();
         if (any_grow) {
 #pragma unroll 1
-          for (int c = 0; c < DV / 32; ++c) {
+          for (int c = 0; c < OW / 32; ++c) {
             uint32_t r[32];
-            tmem_ld_32x32b_x32(lane_addr + TM_O + c * 32, r);
+            tmem_ld_32x32b_x32(lane_addr + TM_O + ch * OW + c * 32, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x32(lane_addr + TM_O + c * 32, r);
+            tmem_st_32x32b_x32(lane_addr + TM_O + ch * OW + c * 32, r);
           }
           tmem_st_wait();
         }
@@ -250,50 +274,44 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (j > 0) l_sum *= alpha;
       m_used = m_new;
       const float m_scaled = m_used * p.scale_log2;
-      // pass 2: probabilities -> bf16 P tile in shared memory (K-major, 128B swizzle)
-#pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_ld_wait();
-        uint32_t packed[16];
+      // probabilities -> bf16 P tile in shared memory (K-major, 128B swizzle)
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float a = __uint_as_float(r[i]), bb = __uint_as_float(r[i + 1]);
-          const int col = kv0 + c * 32 + i;
-          a = (diag && col > qi) ? 0.f : exp2f(a * p.scale_log2 - m_scaled);
-          bb = (diag && col + 1 > qi) ? 0.f : exp2f(bb * p.scale_log2 - m_scaled);
+      for (int c8 = 0; c8 < CW / 8; ++c8) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float a = exp2f(x[c8 * 8 + 2 * e] * p.scale_log2 - m_scaled);       // masked entries: exp2(-inf) = 0
+          const float bb = exp2f(x[c8 * 8 + 2 * e + 1] * p.scale_log2 - m_scaled);
           l_sum += a + bb;
-          packed[i >> 1] = pack_bf16(a, bb);
+          packed[e] = pack_bf16(a, bb);
         }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int chunk = c * 4 + q;  // 16-byte chunk index along the row
-          const uint32_t addr = base + L::OFF_P + (chunk >> 3) * (ATT_BQ * 128) + row * 128 +
-                                (((chunk & 7) ^ (row & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * q]), "r"(packed[4 * q + 1]),
-                       "r"(packed[4 * q + 2]), "r"(packed[4 * q + 3])
-                       : "memory");
-        }
+        const int chunk = ch * (CW / 8) + c8;  // 16-byte chunk index along the row
+        const uint32_t addr = base + L::OFF_P + (chunk >> 3) * (ATT_BQ * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[0]), "r"(packed[1]), "r"(packed[2]),
+                     "r"(packed[3])
+                     : "memory");
       }
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar(AB_S_EMPTY0 + s));
-        mbar_arrive(bar(AB_P_FULL));
-      }
+      if (lane == 0) mbar_arrive(bar(AB_P_FULL));
     }
-    // epilogue: O / l and the log-sum-exp
+    // epilogue: O / l and the log-sum-exp; each warp of a pair stores half of the output columns
     if (ok && n_kv > 0 && mbar_wait(bar(AB_O_DONE), (n_kv - 1) & 1u, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) {
       tc_fence_after();
+      float* pb = pair + (n_kv & 1) * 256;
+      pb[ch * 128 + row] = l_sum;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(AB_PAIR0 + lg));
+      const bool paired = mbar_wait(bar(AB_PAIR0 + lg), n_kv & 1u, p.status, ST_TIMEOUT_PEER, abort_flag);
+      l_sum += paired ? pb[(ch ^ 1) * 128 + row] : 0.f;
       const float inv = 1.f / l_sum;
       __nv_bfloat16* orow = p.o + static_cast<long long>(b) * p.o_bs + static_cast<long long>(qi) * p.o_ss +
-                            static_cast<long long>(h) * p.o_hs;
+                            static_cast<long long>(h) * p.o_hs + ch * OW;
 #pragma unroll 1
-      for (int c = 0; c < DV / 32; ++c) {
+      for (int c = 0; c < OW / 32; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(lane_addr + TM_O + c * 32, r);
+        tmem_ld_32x32b_x32(lane_addr + TM_O + ch * OW + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -305,7 +323,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = v;
         }
       }
-      p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S + qi] = m_used * p.scale + __logf(l_sum);
+      if (ch == 0) p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S + qi] = m_used * p.scale + __logf(l_sum);
     }
   }
 

@@ -5,7 +5,7 @@
 //   dK/dV kernel : one CTA per (batch, kv head, 128-row key tile); K and V tiles stay in shared memory,
 //                  64-row Q / dO tiles of every query head of the group stream through a TMA ring:
 //                    S^T = K Q^T, dP^T = V dO^T            (UMMA 128x64x16 into TMEM)
-//                    P^T = exp2(S^T*c - lse2[q]),  dS^T = P^T o (dP^T - delta[q])   (4 warps, thread = key row)
+//                    P^T = exp2(S^T*c - lse2[q]),  dS^T = P^T o (dP^T - delta[q])   (8 warps, two threads per key row)
 //                    dV += P^T dO,  dK += dS^T Q          (A = bf16 tiles written to swizzled shared memory,
 //                                                          B = the streamed tile read MN-major)
 //   dQ kernel    : one CTA per (batch, head, 128-row query tile); Q and dO stay, 64-row K / V tiles stream:
@@ -28,7 +28,7 @@ namespace olb {
 int attn_tmap(CUtensorMap* map, const void* ptr, int Dh, int H, int S, int B, long long bs, long long ss, long long hs,
               int box_rows);
 
-constexpr int BW_THREADS = 192;
+constexpr int BW_THREADS = 320;  // TMA warp, MMA warp, 8 recompute warps
 constexpr int BW_R = 128;  // resident rows per CTA
 constexpr int BW_T = 64;   // streamed rows per step
 
@@ -101,8 +101,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(BB_XY_FULL0 + s), 1);
-      mbar_init(bar(BB_XY_EMPTY0 + s), 4);
-      mbar_init(bar(BB_DS_FULL0 + s), 4);
+      mbar_init(bar(BB_XY_EMPTY0 + s), 8);
+      mbar_init(bar(BB_DS_FULL0 + s), 8);
       mbar_init(bar(BB_DS_EMPTY0 + s), 1);
     }
     mbar_init(bar(BB_ACC), 1);
@@ -204,7 +204,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
     }
   } else {
     // ---------------------------------------------------------------- softmax recompute, dS, epilogue
+    // warps w and w+4 share the 32 rows (TMEM lanes) of lane group w % 4; each takes 32 of the 64 columns
     const int lg = warp & 3;
+    const int c = (warp - 2) >> 2;
     const int row = lg * 32 + lane;  // resident row == TMEM lane
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(lg * 32) << 16);
     bool ok = true;
@@ -232,8 +234,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
         lse_col = p.lse2 + o;
         dl_col = p.delta + o;
       }
-#pragma unroll 1
-      for (int c = 0; c < BW_T / 32; ++c) {
+      {
         uint32_t x[32], y[32];
         tmem_ld_32x32b_x32(lane_addr + L::TM_X + s * BW_T + c * 32, x);
         tmem_ld_32x32b_x32(lane_addr + L::TM_Y + s * BW_T + c * 32, y);
@@ -291,13 +292,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
     }
     if (ok && n_iter > 0 && mbar_wait(bar(BB_ACC), 0, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) {
       tc_fence_after();
+      // each warp of a pair stores half of the columns
       auto store_rows = [&](uint32_t tm_col, int width, __nv_bfloat16* out, long long bs, long long ss, long long hs, float mul) {
+        const int half = width / 2;
         __nv_bfloat16* orow = out + static_cast<long long>(b) * bs + static_cast<long long>(r0 + row) * ss +
-                              static_cast<long long>(head_r) * hs;
+                              static_cast<long long>(head_r) * hs + c * half;
 #pragma unroll 1
-        for (int c = 0; c < width / 32; ++c) {
+        for (int cc = 0; cc < half / 32; ++cc) {
           uint32_t r[32];
-          tmem_ld_32x32b_x32(lane_addr + tm_col + c * 32, r);
+          tmem_ld_32x32b_x32(lane_addr + tm_col + c * half + cc * 32, r);
           tmem_ld_wait();
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
@@ -306,7 +309,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
             v.y = pack_bf16(__uint_as_float(r[8 * g + 2]) * mul, __uint_as_float(r[8 * g + 3]) * mul);
             v.z = pack_bf16(__uint_as_float(r[8 * g + 4]) * mul, __uint_as_float(r[8 * g + 5]) * mul);
             v.w = pack_bf16(__uint_as_float(r[8 * g + 6]) * mul, __uint_as_float(r[8 * g + 7]) * mul);
-            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = v;
+            *reinterpret_cast<uint4*>(orow + cc * 32 + g * 8) = v;
           }
         }
       };
