@@ -4,12 +4,12 @@
 //   warp 0    : TMA producer - Q once, then K / V tiles through a 2-stage ring (4D tensor maps over
 //               the strided [B, S, H, D] tensors, 128B swizzle)
 //   warp 1    : one thread issues  S = Q K^T  (UMMA 128 x BKV x 16, K-major x K-major) into one of
-//               two TMEM score buffers and  O += P V  (A = P from shared memory, B = V MN-major)
+//               two TMEM score buffers and  O += P V  (A = P read from TMEM, B = V MN-major)
 //   warps 2-9 : softmax - two threads own query row r (half of the columns each): one tcgen05.ld pass of
 //               the score row into registers, row maxima exchanged between the pair, online softmax
 //               in base 2 with lazy rescaling (the running maximum only moves when it grows by
-//               more than 2^8, so the TMEM accumulator is rarely rescaled), P written as bf16
-//               into a swizzled shared-memory tile, final normalisation and store of O and the
+//               more than 2^8, so the TMEM accumulator is rarely rescaled), P written as packed
+//               bf16 over the scores in TMEM, final normalisation and store of O and the
 //               log-sum-exp.
 // Head dims: D (q/k) in {64, 128, 192}, Dv in {64, 128}; D = 192 / Dv = 128 is DeepSeek-V3's MLA.
 // The reference calls F.scaled_dot_product_attention (optimus/models/olmoe/modeling_olmoe.py:219-227)
@@ -40,13 +40,11 @@ struct AttnFwdSmem {
   static constexpr int Q_BYTES = ATT_BQ * D * 2;
   static constexpr int K_BYTES = BKV * D * 2;
   static constexpr int V_BYTES = BKV * DV * 2;
-  static constexpr int P_BYTES = ATT_BQ * BKV * 2;
   static constexpr int STAGES = 2;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
   static constexpr int OFF_V = OFF_K + STAGES * K_BYTES;
-  static constexpr int OFF_P = OFF_V + STAGES * V_BYTES;
-  static constexpr int OFF_PAIR = OFF_P + P_BYTES;           // row statistics exchanged between warp pairs
+  static constexpr int OFF_PAIR = OFF_V + STAGES * V_BYTES;  // row statistics exchanged between warp pairs
   static constexpr int OFF_BAR = OFF_PAIR + 2 * 2 * ATT_BQ * 4;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
@@ -95,7 +93,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(bar(AB_V0 + s), 1);
       mbar_init(bar(AB_KV_EMPTY0 + s), 1);
       mbar_init(bar(AB_S_FULL0 + s), 1);
-      mbar_init(bar(AB_S_EMPTY0 + s), 8);
     }
     mbar_init(bar(AB_P_FULL), 8);
     mbar_init(bar(AB_O_DONE), 1);
@@ -166,11 +163,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (j + 1 < n_kv) {
           const int s1 = (j + 1) & 1;
           const uint32_t ph1 = ((j + 1) >> 1) & 1u;
-          // score buffer s1 was last read by the softmax of tile j-1
-          if (j >= 1 && !mbar_wait(bar(AB_S_EMPTY0 + s1), ((j - 1) >> 1) & 1u, p.status, ST_TIMEOUT_ACC_EMPTY, abort_flag)) {
-            ok = false;
-            break;
-          }
+          // score buffer s1 held P of tile j-1, whose P V was issued before this MMA: tcgen05.mma of one
+          // thread execute in issue order, so no barrier is needed before overwriting it
           if (!mbar_wait(bar(AB_K0 + s1), ph1, p.status, ST_TIMEOUT_FULL, abort_flag)) {
             ok = false;
             break;
@@ -184,9 +178,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const uint32_t vbase = base + L::OFF_V + s * L::V_BYTES;
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
-          const uint64_t da = make_smem_desc(base + L::OFF_P + (k / 4) * (ATT_BQ * 128) + (k % 4) * 32, 16, 1024);
+          // A = P read from TMEM: bf16 pairs packed in the first BKV/2 columns of the score buffer,
+          // 8 columns per K = 16 step
           const uint64_t db = make_smem_desc(vbase + k * 2048, BKV * 128, 1024);
-          umma_ss(tmem + TM_O, da, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+          umma_ts(tmem + TM_O, tmem + (s ? TM_S1 : TM_S0) + k * 8, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         }
         umma_commit(bar(AB_KV_EMPTY0 + s));
         umma_commit(bar(AB_O_DONE));
@@ -226,10 +221,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 32; ++i) x[c * 32 + i] = __uint_as_float(r[i]);
       }
-      // the score buffer can be overwritten by the next Q K^T as soon as both halves are in registers
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(AB_S_EMPTY0 + s));
       float mx = -FLT_MAX;
 #pragma unroll
       for (int i = 0; i < CW; ++i) {
@@ -251,14 +242,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (grow) m_new = fmaxf(m_used, mx);
       const float alpha = (j == 0) ? 0.f : exp2f((m_used - m_new) * p.scale_log2);
       const bool any_grow = __any_sync(0xffffffffu, grow && j > 0);
-      // the previous P V must be complete before O is rescaled and before P is overwritten
-      if (j > 0) {
+      // the previous P V must be complete before O is rescaled (rare: only when a row maximum jumped)
+      if (any_grow) {
         if (!mbar_wait(bar(AB_O_DONE), (j - 1) & 1u, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        if (any_grow) {
+        {
 #pragma unroll 1
           for (int c = 0; c < OW / 32; ++c) {
             uint32_t r[32];
@@ -274,24 +265,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (j > 0) l_sum *= alpha;
       m_used = m_new;
       const float m_scaled = m_used * p.scale_log2;
-      // probabilities -> bf16 P tile in shared memory (K-major, 128B swizzle)
+      // probabilities -> bf16 pairs written back into the score buffer (first BKV/2 columns), from where the
+      // P V MMA reads them as its A operand.  Both halves of the scores are in registers by now (the pair
+      // exchange above comes after the loads), so the overwrite is safe.
+      const uint32_t p_addr = lane_addr + (s ? TM_S1 : TM_S0) + ch * (CW / 2);
 #pragma unroll
-      for (int c8 = 0; c8 < CW / 8; ++c8) {
-        uint32_t packed[4];
+      for (int c16 = 0; c16 < CW / 32; ++c16) {
+        uint32_t packed[16];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float a = exp2f(x[c8 * 8 + 2 * e] * p.scale_log2 - m_scaled);       // masked entries: exp2(-inf) = 0
-          const float bb = exp2f(x[c8 * 8 + 2 * e + 1] * p.scale_log2 - m_scaled);
+        for (int e = 0; e < 16; ++e) {
+          const float a = ex2_approx(x[c16 * 32 + 2 * e] * p.scale_log2 - m_scaled);  // masked entries give 0
+          const float bb = ex2_approx(x[c16 * 32 + 2 * e + 1] * p.scale_log2 - m_scaled);
           l_sum += a + bb;
           packed[e] = pack_bf16(a, bb);
         }
-        const int chunk = ch * (CW / 8) + c8;  // 16-byte chunk index along the row
-        const uint32_t addr = base + L::OFF_P + (chunk >> 3) * (ATT_BQ * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[0]), "r"(packed[1]), "r"(packed[2]),
-                     "r"(packed[3])
-                     : "memory");
+        tmem_st_32x32b_x16(p_addr + c16 * 16, packed);
       }
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(AB_P_FULL));
