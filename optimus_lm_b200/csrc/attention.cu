@@ -1,7 +1,7 @@
 // Causal flash attention for sm_100a on tcgen05 tensor cores with TMEM accumulators.
 //
 // Forward, one CTA per (batch, head, 128-row query tile):
-//   warp 0    : TMA producer - Q once, then K / V tiles through a 2-stage ring (4D tensor maps over
+//   warp 0    : TMA producer - Q once, then K tiles and V tiles through two 3- or 4-stage rings (4D tensor maps over
 //               the strided [B, S, H, D] tensors, 128B swizzle)
 //   warp 1    : one thread issues  S = Q K^T  (UMMA 128 x BKV x 16, K-major x K-major) into one of
 //               two TMEM score buffers and  O += P V  (A = P read from TMEM, B = V MN-major)
@@ -40,13 +40,16 @@ struct AttnFwdSmem {
   static constexpr int Q_BYTES = ATT_BQ * D * 2;
   static constexpr int K_BYTES = BKV * D * 2;
   static constexpr int V_BYTES = BKV * DV * 2;
-  static constexpr int STAGES = 2;
+  // K tiles are released as soon as their Q K^T has run, V tiles only after P V: separate rings.  Their depth
+  // has to cover the TMA latency at one tile pair per ~1000 cycles, so all of shared memory is used.
+  static constexpr int KS = (D == 128) ? 3 : 4, VS = KS;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;
-  static constexpr int OFF_V = OFF_K + STAGES * K_BYTES;
-  static constexpr int OFF_PAIR = OFF_V + STAGES * V_BYTES;  // row statistics exchanged between warp pairs
+  static constexpr int OFF_V = OFF_K + KS * K_BYTES;
+  static constexpr int OFF_PAIR = OFF_V + VS * V_BYTES;  // row statistics exchanged between warp pairs
   static constexpr int OFF_BAR = OFF_PAIR + 2 * 2 * ATT_BQ * 4;
-  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+  static constexpr int TOTAL = OFF_BAR + 256;  // no alignment slack: the kernel checks that the window is 1024-aligned
+  static_assert(TOTAL <= 232448, "shared memory budget");
 };
 
 struct AttnFwdParams {
@@ -60,7 +63,7 @@ struct AttnFwdParams {
 };
 
 // barrier slots
-enum { AB_Q = 0, AB_K0 = 1, AB_V0 = 3, AB_KV_EMPTY0 = 5, AB_S_FULL0 = 7, AB_S_EMPTY0 = 9, AB_P_FULL = 11, AB_O_DONE = 12, AB_PAIR0 = 13 };
+enum { AB_Q = 0, AB_K0 = 1, AB_KE0 = 5, AB_V0 = 9, AB_VE0 = 13, AB_S_FULL0 = 17, AB_P_FULL = 19, AB_O_DONE = 20, AB_PAIR0 = 21 };
 
 template <int D, int DV, int BKV>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
@@ -72,11 +75,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   static_assert(2 * BKV + DV <= 512, "TMEM budget");
 
   extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {  // swizzled tiles need a 1024-byte aligned window (uniform exit, nothing allocated yet)
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_ARG);
+    return;
+  }
+  uint8_t* gen = smem_raw;
   auto bar = [&](int i) { return base + L::OFF_BAR + 8u * i; };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::OFF_BAR + 8 * 20);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::OFF_BAR + 8 * 20 + 8);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::OFF_BAR + 8 * 26);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::OFF_BAR + 8 * 26 + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_q_tiles = p.S / ATT_BQ;
@@ -88,12 +95,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(bar(AB_Q), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < L::KS; ++s) {
       mbar_init(bar(AB_K0 + s), 1);
-      mbar_init(bar(AB_V0 + s), 1);
-      mbar_init(bar(AB_KV_EMPTY0 + s), 1);
-      mbar_init(bar(AB_S_FULL0 + s), 1);
+      mbar_init(bar(AB_KE0 + s), 1);
     }
+    for (int s = 0; s < L::VS; ++s) {
+      mbar_init(bar(AB_V0 + s), 1);
+      mbar_init(bar(AB_VE0 + s), 1);
+    }
+    for (int s = 0; s < 2; ++s) mbar_init(bar(AB_S_FULL0 + s), 1);
     mbar_init(bar(AB_P_FULL), 8);
     mbar_init(bar(AB_O_DONE), 1);
     for (int g = 0; g < 4; ++g) mbar_init(bar(AB_PAIR0 + g), 2);
@@ -118,21 +128,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_expect_tx(bar(AB_Q), L::Q_BYTES);
 #pragma unroll
       for (int a = 0; a < D / 64; ++a) tma_load_4d(base + L::OFF_Q + a * (ATT_BQ * 128), &tm_q, bar(AB_Q), a * 64, h, q0, b);
-      uint32_t phase = 0;
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        if (j >= 2) {
-          if (!mbar_wait(bar(AB_KV_EMPTY0 + s), phase ^ 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
+      // K runs two tiles ahead of V
+      for (int i = 0; i < n_kv + 2; ++i) {
+        if (i < n_kv) {
+          const int s = i % L::KS;
+          if (i >= L::KS && !mbar_wait(bar(AB_KE0 + s), ((i / L::KS) - 1) & 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
+          mbar_expect_tx(bar(AB_K0 + s), L::K_BYTES);
+#pragma unroll
+          for (int a = 0; a < D / 64; ++a)
+            tma_load_4d(base + L::OFF_K + s * L::K_BYTES + a * (BKV * 128), &tm_k, bar(AB_K0 + s), a * 64, hk, i * BKV, b);
         }
-        mbar_expect_tx(bar(AB_K0 + s), L::K_BYTES);
+        const int j = i - 2;
+        if (j >= 0) {
+          const int s = j % L::VS;
+          if (j >= L::VS && !mbar_wait(bar(AB_VE0 + s), ((j / L::VS) - 1) & 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) break;
+          mbar_expect_tx(bar(AB_V0 + s), L::V_BYTES);
 #pragma unroll
-        for (int a = 0; a < D / 64; ++a)
-          tma_load_4d(base + L::OFF_K + s * L::K_BYTES + a * (BKV * 128), &tm_k, bar(AB_K0 + s), a * 64, hk, j * BKV, b);
-        mbar_expect_tx(bar(AB_V0 + s), L::V_BYTES);
-#pragma unroll
-        for (int a = 0; a < DV / 64; ++a)
-          tma_load_4d(base + L::OFF_V + s * L::V_BYTES + a * (BKV * 128), &tm_v, bar(AB_V0 + s), a * 64, hk, j * BKV, b);
-        if (s == 1) phase ^= 1u;
+          for (int a = 0; a < DV / 64; ++a)
+            tma_load_4d(base + L::OFF_V + s * L::V_BYTES + a * (BKV * 128), &tm_v, bar(AB_V0 + s), a * 64, hk, j * BKV, b);
+        }
       }
     }
   } else if (warp == 1) {
@@ -143,7 +157,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       bool ok = mbar_wait(bar(AB_Q), 0, p.status, ST_TIMEOUT_FULL, abort_flag);
       auto issue_s = [&](int j) {
         const int s = j & 1;
-        const uint32_t kbase = base + L::OFF_K + s * L::K_BYTES;
+        const uint32_t kbase = base + L::OFF_K + (j % L::KS) * L::K_BYTES;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t da = make_smem_desc(base + L::OFF_Q + (k / 4) * (ATT_BQ * 128) + (k % 4) * 32, 16, 1024);
@@ -151,6 +165,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           umma_ss(tmem + (s ? TM_S1 : TM_S0), da, db, idesc_s, k > 0 ? 1u : 0u);
         }
         umma_commit(bar(AB_S_FULL0 + s));
+        umma_commit(bar(AB_KE0 + j % L::KS));
       };
       if (ok && n_kv > 0) {
         ok = mbar_wait(bar(AB_K0), 0, p.status, ST_TIMEOUT_FULL, abort_flag);
@@ -159,10 +174,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       for (int j = 0; ok && j < n_kv; ++j) {
         const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1u;
         if (j + 1 < n_kv) {
-          const int s1 = (j + 1) & 1;
-          const uint32_t ph1 = ((j + 1) >> 1) & 1u;
+          const int s1 = (j + 1) % L::KS;
+          const uint32_t ph1 = ((j + 1) / L::KS) & 1u;
           // score buffer s1 held P of tile j-1, whose P V was issued before this MMA: tcgen05.mma of one
           // thread execute in issue order, so no barrier is needed before overwriting it
           if (!mbar_wait(bar(AB_K0 + s1), ph1, p.status, ST_TIMEOUT_FULL, abort_flag)) {
@@ -173,9 +187,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           issue_s(j + 1);
         }
         if (!mbar_wait(bar(AB_P_FULL), j & 1u, p.status, ST_TIMEOUT_FULL, abort_flag)) break;
-        if (!mbar_wait(bar(AB_V0 + s), ph, p.status, ST_TIMEOUT_FULL, abort_flag)) break;
+        const int sv = j % L::VS;
+        if (!mbar_wait(bar(AB_V0 + sv), (j / L::VS) & 1u, p.status, ST_TIMEOUT_FULL, abort_flag)) break;
         tc_fence_after();
-        const uint32_t vbase = base + L::OFF_V + s * L::V_BYTES;
+        const uint32_t vbase = base + L::OFF_V + sv * L::V_BYTES;
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
           // A = P read from TMEM: bf16 pairs packed in the first BKV/2 columns of the score buffer,
@@ -183,7 +198,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           const uint64_t db = make_smem_desc(vbase + k * 2048, BKV * 128, 1024);
           umma_ts(tmem + TM_O, tmem + (s ? TM_S1 : TM_S0) + k * 8, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
         }
-        umma_commit(bar(AB_KV_EMPTY0 + s));
+        umma_commit(bar(AB_VE0 + sv));
         umma_commit(bar(AB_O_DONE));
       }
     }
@@ -212,44 +227,57 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t s_addr = lane_addr + (s ? TM_S1 : TM_S0) + ch * CW;
       const int kv0 = j * BKV + ch * CW;
       const bool diag = kv0 + CW > q0;  // this half tile touches the causal boundary
+      uint32_t xr[CW / 32][32];
+#pragma unroll
+      for (int c = 0; c < CW / 32; ++c) tmem_ld_32x32b_x32(s_addr + c * 32, xr[c]);
+      tmem_ld_wait();
       float x[CW];
 #pragma unroll
-      for (int c = 0; c < CW / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_ld_wait();
+      for (int i = 0; i < CW; ++i) x[i] = __uint_as_float(xr[i / 32][i % 32]);
+      if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) x[c * 32 + i] = __uint_as_float(r[i]);
+        for (int i = 0; i < CW; ++i)
+          if (kv0 + i > qi) x[i] = -FLT_MAX;
       }
-      float mx = -FLT_MAX;
+      float mx4[4] = {-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX};  // four independent chains
 #pragma unroll
-      for (int i = 0; i < CW; ++i) {
-        if (diag && kv0 + i > qi) x[i] = -FLT_MAX;
-        mx = fmaxf(mx, x[i]);
-      }
+      for (int i = 0; i < CW; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], x[i]);
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       float* pb = pair + (j & 1) * 256;
       pb[ch * 128 + row] = mx;
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(AB_PAIR0 + lg));
+      // probabilities as packed bf16 pairs and their sum, for a given (scaled) running maximum
+      uint32_t packed[CW / 2];
+      auto probabilities = [&](float m_scaled) {
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int e = 0; e < CW / 2; ++e) {
+          const float a = ex2_approx(x[2 * e] * p.scale_log2 - m_scaled);  // masked entries give 0
+          const float bb = ex2_approx(x[2 * e + 1] * p.scale_log2 - m_scaled);
+          s4[e & 3] += a + bb;
+          packed[e] = pack_bf16(a, bb);
+        }
+        return (s4[0] + s4[1]) + (s4[2] + s4[3]);
+      };
       if (!mbar_wait(bar(AB_PAIR0 + lg), j & 1u, p.status, ST_TIMEOUT_PEER, abort_flag)) {
         ok = false;
         break;
       }
       mx = fmaxf(mx, pb[(ch ^ 1) * 128 + row]);
-      // lazy rescale decision (identical in both warps of a pair: same rows, same maxima)
-      float m_new = m_used;
+      // rescale decision (identical in both warps of a pair: same rows, same maxima)
       const bool grow = (j == 0) || ((mx - m_used) * p.scale_log2 > 8.f);
-      if (grow) m_new = fmaxf(m_used, mx);
-      const float alpha = (j == 0) ? 0.f : exp2f((m_used - m_new) * p.scale_log2);
-      const bool any_grow = __any_sync(0xffffffffu, grow && j > 0);
-      // the previous P V must be complete before O is rescaled (rare: only when a row maximum jumped)
+      const bool any_grow = __any_sync(0xffffffffu, grow);
       if (any_grow) {
-        if (!mbar_wait(bar(AB_O_DONE), (j - 1) & 1u, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        {
+        const float m_new = grow ? fmaxf(m_used, mx) : m_used;
+        const float alpha = (j == 0) ? 0.f : ex2_approx((m_used - m_new) * p.scale_log2);
+        if (j > 0) {
+          // the previous P V must be complete before O is rescaled
+          if (!mbar_wait(bar(AB_O_DONE), (j - 1) & 1u, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < OW / 32; ++c) {
             uint32_t r[32];
@@ -261,25 +289,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
           tmem_st_wait();
         }
+        l_sum *= alpha;
+        m_used = m_new;
       }
-      if (j > 0) l_sum *= alpha;
-      m_used = m_new;
-      const float m_scaled = m_used * p.scale_log2;
-      // probabilities -> bf16 pairs written back into the score buffer (first BKV/2 columns), from where the
-      // P V MMA reads them as its A operand.  Both halves of the scores are in registers by now (the pair
-      // exchange above comes after the loads), so the overwrite is safe.
+      l_sum += probabilities(m_used * p.scale_log2);
+      // P goes back into the score buffer (first BKV/2 columns), from where the P V MMA reads it as its A
+      // operand.  Both halves of the scores are in registers by now (the pair barrier came after the loads).
       const uint32_t p_addr = lane_addr + (s ? TM_S1 : TM_S0) + ch * (CW / 2);
 #pragma unroll
       for (int c16 = 0; c16 < CW / 32; ++c16) {
-        uint32_t packed[16];
+        uint32_t part[16];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const float a = ex2_approx(x[c16 * 32 + 2 * e] * p.scale_log2 - m_scaled);  // masked entries give 0
-          const float bb = ex2_approx(x[c16 * 32 + 2 * e + 1] * p.scale_log2 - m_scaled);
-          l_sum += a + bb;
-          packed[e] = pack_bf16(a, bb);
-        }
-        tmem_st_32x32b_x16(p_addr + c16 * 16, packed);
+        for (int e = 0; e < 16; ++e) part[e] = packed[c16 * 16 + e];
+        tmem_st_32x32b_x16(p_addr + c16 * 16, part);
       }
       tmem_st_wait();
       tc_fence_before();
