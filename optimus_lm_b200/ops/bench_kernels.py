@@ -106,6 +106,11 @@ def profile_case(name: str, launches: int = 4):
     elif name == "attention":
         q, k, v = (torch.randn(4, 4096, 16, 128, device="cuda").to(torch.bfloat16) for _ in range(3))
         fn = lambda: OA.flash_attention(q, k, v)
+    elif name == "attention-bwd":
+        q, k, v = (torch.randn(4, 4096, 16, 128, device="cuda").to(torch.bfloat16).requires_grad_() for _ in range(3))
+        o = OA.flash_attention(q, k, v)
+        do = torch.randn_like(o)
+        fn = lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True)
     elif name == "rmsnorm-bwd":
         x = torch.randn(16384, 2048, device="cuda").to(torch.bfloat16).requires_grad_()
         w = torch.ones(2048, device="cuda", dtype=torch.bfloat16, requires_grad=True)
