@@ -28,7 +28,7 @@ T* opt_ptr(const c10::optional<at::Tensor>& t) {
 void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, int64_t M, int64_t N, int64_t K, bool a_mn_major,
           bool b_mn_major, bool accumulate, int64_t mode, const c10::optional<at::Tensor>& meta, int64_t num_experts,
           int64_t b_expert_rows, int64_t c_expert_stride, const c10::optional<at::Tensor>& status, int64_t block_n,
-          int64_t max_ctas) {
+          int64_t max_ctas, const c10::optional<at::Tensor>& b2, int64_t k_split) {
   CHECK_CUDA_BF16(a);
   CHECK_CUDA_BF16(b);
   TORCH_CHECK(c.is_cuda() && (c.scalar_type() == at::kBFloat16 || c.scalar_type() == at::kFloat), "c must be bf16/fp32");
@@ -59,6 +59,12 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, int64_t M, in
   d.block_n = static_cast<int>(block_n);
   d.max_ctas = static_cast<int>(max_ctas);
   d.status = opt_ptr<int>(status);
+  if (b2.has_value()) {
+    TORCH_CHECK(b2->is_cuda() && b2->scalar_type() == at::kBFloat16 && b2->sizes() == b.sizes() && b2->strides() == b.strides(),
+                "b2 must have the layout of b");
+    d.B2 = b2->data_ptr();
+    d.k_split = static_cast<int>(k_split);
+  }
   check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16");
 }
 

@@ -56,6 +56,7 @@ struct GemmParams {
   long long c_expert_stride;   // elements between consecutive experts' C (ragged-K)
   int accumulate;              // C += A*B instead of C = A*B
   int out_fp32;
+  int kb_split;                // > 0: k-blocks from this one on read B from the second tensor map (K-concatenated B)
   int* status;
 };
 
@@ -112,7 +113,7 @@ __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int num_m_b
 template <int BLOCK_N>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tma_b2, const GemmParams p) {
   using L = SmemLayout<BLOCK_N>;
   constexpr int STAGES = L::STAGES;
   constexpr uint32_t TMEM_COLS = (2 * BLOCK_N < 32) ? 32 : 2 * BLOCK_N;
@@ -186,12 +187,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
             for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d(sa + j * MN_BOX_BYTES, &tma_a, fb, ti.m0 + j * 64, k0);
           }
+          // K-concatenated B: the second half of the K range comes from a second tensor of the same layout
+          const bool second = p.kb_split > 0 && kb >= p.kb_split;
+          const CUtensorMap* tmb = second ? &tma_b2 : &tma_b;
+          const int kB = second ? k0 - p.kb_split * BLOCK_K : k0;
           if (!p.b_mn_major) {
-            tma_load_2d(sb, &tma_b, fb, k0, ti.expert * p.b_expert_rows + ti.n0);
+            tma_load_2d(sb, tmb, fb, kB, ti.expert * p.b_expert_rows + ti.n0);
           } else {
-            const int krow = (p.mode == OLB_GEMM_RAGGED_M ? ti.expert * p.b_expert_rows : 0) + k0;
+            const int krow = (p.mode == OLB_GEMM_RAGGED_M ? ti.expert * p.b_expert_rows : 0) + kB;
 #pragma unroll
-            for (int j = 0; j < BLOCK_N / 64; ++j) tma_load_2d(sb + j * MN_BOX_BYTES, &tma_b, fb, ti.n0 + j * 64, krow);
+            for (int j = 0; j < BLOCK_N / 64; ++j) tma_load_2d(sb + j * MN_BOX_BYTES, tmb, fb, ti.n0 + j * 64, krow);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -408,7 +413,8 @@ int make_tmap_4d_bf16(CUtensorMap* map, const void* base, const uint64_t dims[4]
 }
 
 template <int BLOCK_N>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_sms, cudaStream_t stream) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p, int num_sms,
+                  cudaStream_t stream) {
   using L = SmemLayout<BLOCK_N>;
   static bool configured = false;
   if (!configured) {
@@ -421,7 +427,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   tiles = nm * nn * (p.mode == OLB_GEMM_RAGGED_K ? p.num_experts : 1);
   int grid = static_cast<int>(tiles < num_sms ? tiles : num_sms);
   if (grid <= 0) return 0;
-  gemm_bf16_kernel<BLOCK_N><<<grid, NUM_THREADS, L::TOTAL, stream>>>(ta, tb, p);
+  gemm_bf16_kernel<BLOCK_N><<<grid, NUM_THREADS, L::TOTAL, stream>>>(ta, tb, tb2, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -477,6 +483,23 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   else
     rc = make_tmap_2d_bf16(&tb, d->B, d->N, d->b_rows, d->ldb * 2, 64, BLOCK_K);
   if (rc) return rc;
+  // optional second B (same layout) for the K range [k_split, K)
+  CUtensorMap tb2 = tb;
+  int kb_split = 0;
+  if (d->B2 != nullptr && d->k_split > 0) {
+    if (d->k_split % BLOCK_K || d->k_split >= d->K || d->mode == OLB_GEMM_RAGGED_K || (reinterpret_cast<uintptr_t>(d->B2) & 15))
+      return -13;
+    const int k1 = d->k_split, k2 = d->K - d->k_split;
+    // each map covers only its own K extent, so that reads past it are zero-filled as usual
+    if (!d->b_mn_major) {
+      rc = make_tmap_2d_bf16(&tb, d->B, k1, d->b_rows, d->ldb * 2, BLOCK_K, block_n);
+      if (!rc) rc = make_tmap_2d_bf16(&tb2, d->B2, k2, d->b_rows, d->ldb * 2, BLOCK_K, block_n);
+    } else {
+      rc = make_tmap_2d_bf16(&tb2, d->B2, d->N, d->b_rows, d->ldb * 2, 64, BLOCK_K);
+    }
+    if (rc) return rc;
+    kb_split = d->k_split / BLOCK_K;
+  }
 
   if (debug) {
     fprintf(stderr, "[olb_gemm] tensor maps ok, block_n=%d\n", block_n);
@@ -497,12 +520,13 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   p.c_expert_stride = d->c_expert_stride;
   p.accumulate = d->accumulate;
   p.out_fp32 = d->out_fp32;
+  p.kb_split = kb_split;
   p.status = d->status;
   const int sms = d->max_ctas > 0 && d->max_ctas < num_sms ? d->max_ctas : num_sms;
   switch (block_n) {
-    case 256: return launch<256>(ta, tb, p, sms, stream);
-    case 128: return launch<128>(ta, tb, p, sms, stream);
-    case 64: return launch<64>(ta, tb, p, sms, stream);
+    case 256: return launch<256>(ta, tb, tb2, p, sms, stream);
+    case 128: return launch<128>(ta, tb, tb2, p, sms, stream);
+    case 64: return launch<64>(ta, tb, tb2, p, sms, stream);
     default: return -12;
   }
 }

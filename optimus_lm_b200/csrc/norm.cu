@@ -121,6 +121,87 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
+// Same math for cols = NCH * 256 <= 2048 with the row held in registers: x and dy are read from global memory
+// once, and each lane keeps the weight-gradient sums of its own columns in registers over all rows of its warp
+// (no shared-memory read-modify-write per element); the warps' sums meet in shared memory once at the end.
+template <int NCH>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                       const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                       __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows) {
+  constexpr int cols = NCH * 256;
+  __shared__ __align__(16) __nv_bfloat16 s_w[cols];
+  __shared__ float s_dw[NORM_WARPS][cols + 8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (w) {
+    for (int c = threadIdx.x * 8; c < cols; c += NORM_THREADS * 8)
+      *reinterpret_cast<uint4*>(s_w + c) = *reinterpret_cast<const uint4*>(w + c);
+  }
+  __syncthreads();
+  float dw_acc[NCH][8];
+#pragma unroll
+  for (int k = 0; k < NCH; ++k)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dw_acc[k][i] = 0.f;
+  const float inv_cols = 1.f / cols;
+  for (long long row = static_cast<long long>(blockIdx.x) * NORM_WARPS + warp; row < rows;
+       row += static_cast<long long>(gridDim.x) * NORM_WARPS) {
+    uint4 vx[NCH], vd[NCH];
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      vx[k] = *reinterpret_cast<const uint4*>(x + row * cols + k * 256 + lane * 8);
+      vd[k] = *reinterpret_cast<const uint4*>(dy + row * cols + k * 256 + lane * 8);
+    }
+    const float r = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const uint32_t ux[4] = {vx[k].x, vx[k].y, vx[k].z, vx[k].w}, ud[4] = {vd[k].x, vd[k].y, vd[k].z, vd[k].w};
+      uint4 vw = make_uint4(0, 0, 0, 0);
+      if (w) vw = *reinterpret_cast<const uint4*>(s_w + k * 256 + lane * 8);
+      const uint32_t uw[4] = {vw.x, vw.y, vw.z, vw.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 fx = unpack_bf16(ux[i]), fd = unpack_bf16(ud[i]), fw = unpack_bf16(uw[i]);
+        const float n0 = fx.x * r, n1 = fx.y * r;
+        dot += (w ? fd.x * fw.x : fd.x) * n0 + (w ? fd.y * fw.y : fd.y) * n1;
+        dw_acc[k][2 * i] += fd.x * round_bf16(n0);
+        dw_acc[k][2 * i + 1] += fd.y * round_bf16(n1);
+      }
+    }
+    dot = warp_sum(dot) * inv_cols;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const uint32_t ux[4] = {vx[k].x, vx[k].y, vx[k].z, vx[k].w}, ud[4] = {vd[k].x, vd[k].y, vd[k].z, vd[k].w};
+      uint4 vw = make_uint4(0, 0, 0, 0);
+      if (w) vw = *reinterpret_cast<const uint4*>(s_w + k * 256 + lane * 8);
+      const uint32_t uw[4] = {vw.x, vw.y, vw.z, vw.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 fx = unpack_bf16(ux[i]), fd = unpack_bf16(ud[i]), fw = unpack_bf16(uw[i]);
+        const float n0 = fx.x * r, n1 = fx.y * r;
+        const float d0 = w ? fd.x * fw.x : fd.x, d1 = w ? fd.y * fw.y : fd.y;
+        o[i] = pack_bf16(r * (d0 - n0 * dot), r * (d1 - n1 * dot));
+      }
+      *reinterpret_cast<uint4*>(dx + row * cols + k * 256 + lane * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+  if (dw_partial) {
+#pragma unroll
+    for (int k = 0; k < NCH; ++k)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s_dw[warp][k * 256 + lane * 8 + i] = dw_acc[k][i];
+    __syncthreads();
+    for (int c = threadIdx.x; c < cols; c += NORM_THREADS) {
+      float s = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < NORM_WARPS; ++wi) s += s_dw[wi][c];
+      dw_partial[static_cast<size_t>(blockIdx.x) * cols + c] = s;
+    }
+  }
+}
+
 __global__ void colsum_finalize_kernel(const float* __restrict__ partial, int nparts, int cols, void* dw, int dw_fp32,
                                        int accumulate) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -230,6 +311,21 @@ extern "C" int olb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
   if (cols % 8) return -1;
   if (rows <= 0) return 0;
   const int nb = olb_rmsnorm_bwd_blocks(rows);
+  {
+    const __nv_bfloat16* pdy = static_cast<const __nv_bfloat16*>(dy);
+    const __nv_bfloat16* px = static_cast<const __nv_bfloat16*>(x);
+    const __nv_bfloat16* pw = static_cast<const __nv_bfloat16*>(w);
+    __nv_bfloat16* pdx = static_cast<__nv_bfloat16*>(dx);
+    bool launched = true;
+    switch (cols) {  // register-resident rows
+      case 256: rmsnorm_bwd_reg_kernel<1><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); break;
+      case 512: rmsnorm_bwd_reg_kernel<2><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); break;
+      case 1024: rmsnorm_bwd_reg_kernel<4><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); break;
+      case 2048: rmsnorm_bwd_reg_kernel<8><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); break;
+      default: launched = false;
+    }
+    if (launched) return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   const size_t smem = dw_partial ? sizeof(float) * NORM_WARPS * cols : 0;
   if (smem > 200 * 1024) return -3;
   if (smem > 48 * 1024) {

@@ -30,6 +30,8 @@ typedef struct {
   int block_n;               // 0 = choose
   int max_ctas;              // 0 = all SMs
   int* status;               // device status word (may be NULL)
+  const void* B2;            // optional second B of the same layout: K range [k_split, K) is read from it
+  int k_split;               // multiple of 64; 0 = single B
 } olb_gemm_desc;
 
 int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream);

@@ -53,14 +53,17 @@ def _kernel_ok(*ts) -> bool:
 # ------------------------------------------------------------------------------------ GEMM
 def gemm(a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, *, a_mn_major=False, b_mn_major=False,
          out: Optional[torch.Tensor] = None, accumulate=False, mode=GEMM_DENSE, meta=None, num_experts=1,
-         b_expert_rows=0, c_expert_stride=0, out_dtype=torch.bfloat16, block_n=0, max_ctas=0) -> torch.Tensor:
-    """Raw tcgen05 GEMM on 2D bf16 views (unit inner stride). See csrc/olb_api.h."""
+         b_expert_rows=0, c_expert_stride=0, out_dtype=torch.bfloat16, block_n=0, max_ctas=0,
+         b2: Optional[torch.Tensor] = None, k_split=0) -> torch.Tensor:
+    """Raw tcgen05 GEMM on 2D bf16 views (unit inner stride). See csrc/olb_api.h.  With ``b2`` (same
+    layout as ``b``) the K range ``[k_split, K)`` is read from ``b2``: one launch for
+    ``a[:, :k_split] @ b + a[:, k_split:] @ b2``."""
     if out is None:
         assert not accumulate
         shape = (num_experts, M, N) if mode == GEMM_RAGGED_K else (M, N)
         out = torch.empty(shape, dtype=out_dtype, device=a.device)
     extension().gemm(a, b, out, M, N, K, a_mn_major, b_mn_major, accumulate, mode, meta, num_experts,
-                     b_expert_rows, c_expert_stride, status_word(a.device), block_n, max_ctas)
+                     b_expert_rows, c_expert_stride, status_word(a.device), block_n, max_ctas, b2, k_split)
     return out
 
 
@@ -503,6 +506,15 @@ def grouped_linear_dgrad(dy, w, index: MoEIndex, out=None, accumulate=False):
                 b_expert_rows=N, out=out, accumulate=accumulate)
 
 
+def grouped_linear_dgrad_pair(dh, w1, w2, index: MoEIndex, out=None):
+    """``dx[rows of e] = dh[rows of e, :I] @ w1[e] + dh[rows of e, I:] @ w2[e]`` in one launch (the input
+    gradient of the gate and up projections, whose output gradients sit side by side in ``dh``)."""
+    E, N, K = w1.shape
+    assert w2.shape == w1.shape and dh.shape[1] == 2 * N
+    return gemm(dh, w1.view(E * N, K), index.cap, K, 2 * N, b_mn_major=True, mode=GEMM_RAGGED_M, meta=index.meta,
+                b_expert_rows=N, out=out, b2=w2.view(E * N, K), k_split=N)
+
+
 def grouped_linear_wgrad(dy, xp, index: MoEIndex, N: int, K: int):
     """``dw[e] = dy[rows of e].T @ xp[rows of e]`` -> [E, N, K]."""
     return gemm(dy, xp, N, K, index.cap, a_mn_major=True, b_mn_major=True, mode=GEMM_RAGGED_K, meta=index.offsets,
@@ -559,8 +571,11 @@ class _MoEExpertsFn(torch.autograd.Function):
         del dact
         dwg = grouped_linear_wgrad(dh[:, :I], xp, index, I, H) if ctx.needs_input_grad[3] else None
         dwu = grouped_linear_wgrad(dh[:, I:], xp, index, I, H) if ctx.needs_input_grad[4] else None
-        dxp = grouped_linear_dgrad(dh[:, :I], wg, index)
-        grouped_linear_dgrad(dh[:, I:], wu, index, out=dxp, accumulate=True)
+        if I % 64 == 0:
+            dxp = grouped_linear_dgrad_pair(dh, wg, wu, index)
+        else:
+            dxp = grouped_linear_dgrad(dh[:, :I], wg, index)
+            grouped_linear_dgrad(dh[:, I:], wu, index, out=dxp, accumulate=True)
         dx = torch.empty((T, H), dtype=dout.dtype, device=dout.device)
         C.moe_combine(dxp, index.row_of, None, dx)
         return dx, dtopk, None, dwg, dwu, dwd, None, None

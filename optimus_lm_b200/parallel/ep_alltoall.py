@@ -101,8 +101,11 @@ class _FusedEPMoEFn(torch.autograd.Function):
         dwg = OF.grouped_linear_wgrad(dh[:, :I], xp, index, I, H) if ctx.needs_input_grad[3] else None
         dwu = OF.grouped_linear_wgrad(dh[:, I:], xp, index, I, H) if ctx.needs_input_grad[4] else None
         dxp = sg.named("ep_out", (cap, H), dout.dtype)
-        OF.grouped_linear_dgrad(dh[:, :I], wg, index, out=dxp.local)
-        OF.grouped_linear_dgrad(dh[:, I:], wu, index, out=dxp.local, accumulate=True)
+        if I % 64 == 0:
+            OF.grouped_linear_dgrad_pair(dh, wg, wu, index, out=dxp.local)
+        else:
+            OF.grouped_linear_dgrad(dh[:, :I], wg, index, out=dxp.local)
+            OF.grouped_linear_dgrad(dh[:, I:], wu, index, out=dxp.local, accumulate=True)
         sg.barrier(3)
 
         dx = torch.empty((T, H), dtype=dout.dtype, device=dout.device)

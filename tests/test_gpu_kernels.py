@@ -162,6 +162,32 @@ def test_grouped_gemms():
             assert rel_err(dw[e], dy[a:b].float().t() @ xp[a:b].float()) < 1e-2
         else:
             assert dw[e].abs().max().item() == 0
+    # gate and up input gradients in one launch: K-concatenated B operand
+    w2 = bf(E, I, H, seed=4, scale=0.05)
+    dh = torch.cat([dy, bf(cap, I, seed=5)], dim=1).contiguous()
+    dh[nrows:] = 0
+    dh[:nrows][src < 0] = 0
+    dx2 = OF.grouped_linear_dgrad_pair(dh, w, w2, ix)
+    for e in range(E):
+        a, b = offs[e], offs[e + 1]
+        if b > a:
+            want = dh[a:b, :I].float() @ w[e].float() + dh[a:b, I:].float() @ w2[e].float()
+            assert rel_err(dx2[a:b], want) < 1e-2
+
+
+def test_gemm_k_concatenated_b():
+    M, N, K1, K2 = 384, 320, 192, 128
+    a = bf(M, K1 + K2, seed=1)
+    b1, b2 = bf(N, K1, seed=2), bf(N, K1, seed=3)   # K-major B: [N, K]; both halves must share a layout
+    # K-major operands: second half of K comes from b2 (only its first K2 columns are read)
+    y = OF.gemm(a, b1, M, N, K1 + K2, b2=b2, k_split=K1)
+    want = a[:, :K1].float() @ b1.float().t() + a[:, K1:].float() @ b2[:, :K2].float().t()
+    assert rel_err(y, want) < 1e-2
+    # MN-major B ([K, N]) as in an input-gradient GEMM
+    c1, c2 = bf(K1, N, seed=4), bf(K1, N, seed=5)
+    y = OF.gemm(a, c1, M, N, K1 + K2, b_mn_major=True, b2=c2, k_split=K1)
+    want = a[:, :K1].float() @ c1.float() + a[:, K1:].float() @ c2[:K2].float()
+    assert rel_err(y, want) < 1e-2
 
 
 @pytest.mark.parametrize("T,E,K,H,I,e_start,E_loc", [(512, 8, 2, 256, 512, 0, 8), (1000, 16, 4, 128, 256, 4, 8),
