@@ -202,6 +202,8 @@ def load_initial_weights(args, model, pmap, rank):
 
 def local_grad_norm(engine) -> torch.Tensor:
     acc = torch.zeros(1, dtype=torch.float32, device=engine.device)
+    if hasattr(engine.optimizer, "_finish_direct_grads"):
+        engine.optimizer._finish_direct_grads()  # buffers no GEMM has written in this step yet count as zero
     for fam in engine.optimizer.families:
         OF.sum_of_squares(fam.flat_grad, 1.0, out=acc, accumulate=True)
     return acc.sqrt().reshape(())

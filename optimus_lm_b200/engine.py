@@ -62,6 +62,7 @@ class EngineArgs:
     opt_use_allreduce_for_param_gather: bool = False
     opt_use_chunked_allreduce: bool = False
     use_fused_optimizer: bool = True
+    use_direct_grads: bool = True         # weight-gradient GEMMs store into the flat gradient buffer themselves
     use_activation_checkpointing: bool = False
     activation_checkpointing_level: int = 0
     use_fast_moe: bool = True
@@ -228,6 +229,9 @@ class TrainEngine:
                 opt._fused = FusedShardedStep.try_create(opt)
             except ImportError:
                 opt._fused = None
+        if a.use_direct_grads and self.device.type == "cuda" and self.dtype == torch.bfloat16 \
+                and hasattr(opt, "enable_direct_grads"):
+            opt.enable_direct_grads()
         return opt
 
     def _build_trainer(self):

@@ -74,15 +74,65 @@ def _as_2d(x: torch.Tensor) -> torch.Tensor:
     return x2
 
 
+class DirectGrad:
+    """Gradient buffer of one weight that the weight-gradient GEMMs write (or accumulate into) themselves.
+
+    Autograd's own route - materialise ``dW``, then ``AccumulateGrad`` adds it into a zeroed ``.grad`` - moves
+    the weight gradient through memory four times (memset, GEMM store, read-add-write).  With a ``DirectGrad``
+    attached to a parameter (``enable_direct_grads``) the GEMM epilogue stores straight into the ``.grad`` view
+    of the optimizer's flat buffer: the first gradient of an optimizer step overwrites, later ones (gradient
+    accumulation, pipeline micro-batches) accumulate, and the autograd function returns no gradient."""
+
+    __slots__ = ("buf", "ready")
+
+    def __init__(self, buf: torch.Tensor):
+        self.buf = buf
+        self.ready = False   # False: buffer content is stale, the next gradient overwrites it
+
+
+def enable_direct_grads(params):
+    """Attach a ``DirectGrad`` to every bf16 CUDA weight matrix whose ``.grad`` is preallocated (a view of a flat
+    buffer).  Returns (holders, other_grads): the caller resets the holders and zeroes ``other_grads`` at the
+    start of an optimizer step instead of zeroing everything."""
+    holders, others = [], []
+    for p in params:
+        if p.grad is None:
+            continue
+        if p.is_cuda and p.dtype == torch.bfloat16 and p.dim() >= 2 and p.grad.dtype == torch.bfloat16 \
+                and p.grad.is_contiguous() and p.grad.data_ptr() % 16 == 0 and getattr(p, "_olb_direct_ok", True):
+            h = DirectGrad(p.grad)
+            p._olb_direct = h
+            holders.append(h)
+
+            # A gradient that still arrives through autograd (a torch op used the weight: embedding lookup,
+            # fp32 fall-back, per-expert modules) is added into the buffer by AccumulateGrad; make sure it
+            # is added onto zeros, not onto the previous step's data.
+            def _guard(grad, h=h):
+                if not h.ready:
+                    h.buf.zero_()
+                    h.ready = True
+                return grad
+
+            p.register_hook(_guard)
+        else:
+            others.append(p.grad)
+    return holders, others
+
+
+def _holder(w):
+    return getattr(w, "_olb_direct", None) if torch.is_grad_enabled() else None
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w):
+    def forward(ctx, x, w, holder):
         x2 = _as_2d(x)
         M, K = x2.shape
         N = w.shape[0]
         y = gemm(x2, w, M, N, K)
         ctx.save_for_backward(x2, w)
         ctx.x_shape = x.shape
+        ctx.holder = holder
         return y.view(*x.shape[:-1], N)
 
     @staticmethod
@@ -95,14 +145,19 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, M, K, N, b_mn_major=True).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm(dy2, x2, N, K, M, a_mn_major=True, b_mn_major=True)
-        return dx, dw
+            h = ctx.holder
+            if h is not None:
+                gemm(dy2, x2, N, K, M, a_mn_major=True, b_mn_major=True, out=h.buf, accumulate=h.ready)
+                h.ready = True
+            else:
+                dw = gemm(dy2, x2, N, K, M, a_mn_major=True, b_mn_major=True)
+        return dx, dw, None
 
 
 def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """``x @ w.T`` for a bias-free projection (reference: nn.Linear -> oneDNN)."""
     if _kernel_ok(x, w) and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0:
-        return _LinearFn.apply(x, w)
+        return _LinearFn.apply(x, w, _holder(w))
     return F.linear(x, w)
 
 
@@ -515,8 +570,14 @@ def grouped_linear_dgrad_pair(dh, w1, w2, index: MoEIndex, out=None):
                 b_expert_rows=N, out=out, b2=w2.view(E * N, K), k_split=N)
 
 
-def grouped_linear_wgrad(dy, xp, index: MoEIndex, N: int, K: int):
-    """``dw[e] = dy[rows of e].T @ xp[rows of e]`` -> [E, N, K]."""
+def grouped_linear_wgrad(dy, xp, index: MoEIndex, N: int, K: int, holder: Optional["DirectGrad"] = None):
+    """``dw[e] = dy[rows of e].T @ xp[rows of e]`` -> [E, N, K].  With a ``DirectGrad`` holder the result goes
+    (or is added) into the holder's buffer and ``None`` is returned."""
+    if holder is not None:
+        gemm(dy, xp, N, K, index.cap, a_mn_major=True, b_mn_major=True, mode=GEMM_RAGGED_K, meta=index.offsets,
+             num_experts=index.E_loc, c_expert_stride=N * K, out=holder.buf, accumulate=holder.ready)
+        holder.ready = True
+        return None
     return gemm(dy, xp, N, K, index.cap, a_mn_major=True, b_mn_major=True, mode=GEMM_RAGGED_K, meta=index.offsets,
                 num_experts=index.E_loc, c_expert_stride=N * K)
 
@@ -528,10 +589,11 @@ class _MoEExpertsFn(torch.autograd.Function):
     needs neither the expert outputs nor a weighted scatter."""
 
     @staticmethod
-    def forward(ctx, x, topk_w, topk_idx, wg, wu, wd, e_start, cap):
+    def forward(ctx, x, topk_w, topk_idx, wg, wu, wd, e_start, cap, holders=(None, None, None)):
         C = extension()
         T, H = x.shape
         E_loc, I, _ = wg.shape
+        ctx.holders = holders
         x = x.contiguous()
         topk_w = topk_w.contiguous().float()
         index = MoEIndex(topk_idx, e_start, E_loc, cap)
@@ -561,7 +623,8 @@ class _MoEExpertsFn(torch.autograd.Function):
         # d(y) = gather of dout (the combine was an unweighted sum)
         dyp = torch.empty((cap, H), dtype=dout.dtype, device=dout.device)
         C.moe_gather_rows(dout, index.src_of, index.meta, dyp)
-        dwd = grouped_linear_wgrad(dyp, act, index, H, I) if ctx.needs_input_grad[5] else None
+        hg, hu, hd = ctx.holders
+        dwd = grouped_linear_wgrad(dyp, act, index, H, I, hd) if ctx.needs_input_grad[5] else None
         dact = grouped_linear_dgrad(dyp, wd, index)
         del dyp
         dh = torch.empty_like(h)
@@ -569,8 +632,8 @@ class _MoEExpertsFn(torch.autograd.Function):
         C.swiglu_rowscale_bwd(dact, h[:, :I], h[:, I:], index.src_of, index.k_of, topk_w, index.meta, dh[:, :I],
                               dh[:, I:], dtopk)
         del dact
-        dwg = grouped_linear_wgrad(dh[:, :I], xp, index, I, H) if ctx.needs_input_grad[3] else None
-        dwu = grouped_linear_wgrad(dh[:, I:], xp, index, I, H) if ctx.needs_input_grad[4] else None
+        dwg = grouped_linear_wgrad(dh[:, :I], xp, index, I, H, hg) if ctx.needs_input_grad[3] else None
+        dwu = grouped_linear_wgrad(dh[:, I:], xp, index, I, H, hu) if ctx.needs_input_grad[4] else None
         if I % 64 == 0:
             dxp = grouped_linear_dgrad_pair(dh, wg, wu, index)
         else:
@@ -578,7 +641,7 @@ class _MoEExpertsFn(torch.autograd.Function):
             grouped_linear_dgrad(dh[:, I:], wu, index, out=dxp, accumulate=True)
         dx = torch.empty((T, H), dtype=dout.dtype, device=dout.device)
         C.moe_combine(dxp, index.row_of, None, dx)
-        return dx, dtopk, None, dwg, dwu, dwd, None, None
+        return dx, dtopk, None, dwg, dwu, dwd, None, None, None
 
 
 def moe_experts(x, topk_w, topk_idx, wg, wu, wd, e_start=0, cap: Optional[int] = None):
@@ -591,7 +654,7 @@ def moe_experts(x, topk_w, topk_idx, wg, wu, wd, e_start=0, cap: Optional[int] =
     if _kernel_ok(x, wg, wu, wd) and topk_idx.dtype == torch.int32 and H % 64 == 0 and I % 64 == 0 and E_loc <= 256:
         if cap is None:
             cap = moe_capacity_rows(x.shape[0], topk_idx.shape[1], E_loc)
-        return _MoEExpertsFn.apply(x, topk_w, topk_idx, wg, wu, wd, e_start, cap)
+        return _MoEExpertsFn.apply(x, topk_w, topk_idx, wg, wu, wd, e_start, cap, (_holder(wg), _holder(wu), _holder(wd)))
     return moe_experts_reference(x, topk_w, topk_idx.long(), wg, wu, wd, e_start)
 
 

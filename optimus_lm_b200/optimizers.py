@@ -236,7 +236,29 @@ class _FlatAdamWEngine(Optimizer):
         print("\n".join(lines), flush=True)
 
     # ------------------------------------------------------------------ public API
+    def enable_direct_grads(self):
+        """Let the weight-gradient GEMMs store into the ``.grad`` views of the flat buffers themselves
+        (``ops.functional.DirectGrad``): ``zero_grad`` then only zeroes the few gradients that still go through
+        autograd's accumulation (norm weights, embeddings) instead of the whole flat buffer."""
+        params = [p for fam in self.families for p in fam.spec.params]
+        self._direct, self._other_grads = OF.enable_direct_grads(params)
+        return len(self._direct)
+
+    def _finish_direct_grads(self):
+        # a weight that received no gradient in this optimizer step keeps stale data: zero it
+        for h in getattr(self, "_direct", ()):
+            if not h.ready:
+                h.buf.zero_()
+                h.ready = True
+
     def zero_grad(self, set_to_none: bool = False):
+        direct = getattr(self, "_direct", None)
+        if direct:
+            for h in direct:
+                h.ready = False
+            if self._other_grads:
+                torch._foreach_zero_(self._other_grads)
+            return
         for fam in self.families:
             fam.flat_grad.zero_()
 
@@ -302,11 +324,12 @@ class _FlatAdamWEngine(Optimizer):
 
     @torch.no_grad()
     def step(self, closure=None):
+        self._finish_direct_grads()
         if self.dump_weight_gradients and self.pmap is not None:
             from .utils import dump_weight_gradients
             dump_weight_gradients(self.model, self.config, self.pmap, self.opt_key, "beforegradacc")
 
-        fused = self._fused if (self._fused is not None and self._fused.usable(self)) else None
+        fused =self._fused if (self._fused is not None and self._fused.usable(self)) else None
         with record_pcl_function("3dp-comms-1grad_acc-block"):
             self._pre_reduce()
             if fused is None:

@@ -36,8 +36,9 @@ def _all_gather_rows(t: torch.Tensor, n: int, group) -> torch.Tensor:
 
 class _FusedEPMoEFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, topk_w, topk_idx, wg, wu, wd, sg: SymmGroup, e_start, cap):
+    def forward(ctx, x, topk_w, topk_idx, wg, wu, wd, sg: SymmGroup, e_start, cap, holders=(None, None, None)):
         C = extension()
+        ctx.holders = holders
         n, rank = sg.size, sg.rank
         T, H = x.shape
         E_loc, I, _ = wg.shape
@@ -89,7 +90,8 @@ class _FusedEPMoEFn(torch.autograd.Function):
 
         dyp = torch.empty((cap, H), dtype=dout.dtype, device=dout.device)
         C.ep_gather_rows(ds.ptrs, T, index.src_of, index.meta, dyp)
-        dwd = OF.grouped_linear_wgrad(dyp, act, index, H, I) if ctx.needs_input_grad[5] else None
+        hg, hu, hd = ctx.holders
+        dwd = OF.grouped_linear_wgrad(dyp, act, index, H, I, hd) if ctx.needs_input_grad[5] else None
         dact = OF.grouped_linear_dgrad(dyp, wd, index)
         del dyp
         dh = torch.empty_like(h)
@@ -98,8 +100,8 @@ class _FusedEPMoEFn(torch.autograd.Function):
         C.swiglu_rowscale_bwd(dact, h[:, :I], h[:, I:], index.src_of, index.k_of, w_all, index.meta, dh[:, :I],
                               dh[:, I:], dwt.local)
         del dact
-        dwg = OF.grouped_linear_wgrad(dh[:, :I], xp, index, I, H) if ctx.needs_input_grad[3] else None
-        dwu = OF.grouped_linear_wgrad(dh[:, I:], xp, index, I, H) if ctx.needs_input_grad[4] else None
+        dwg = OF.grouped_linear_wgrad(dh[:, :I], xp, index, I, H, hg) if ctx.needs_input_grad[3] else None
+        dwu = OF.grouped_linear_wgrad(dh[:, I:], xp, index, I, H, hu) if ctx.needs_input_grad[4] else None
         dxp = sg.named("ep_out", (cap, H), dout.dtype)
         if I % 64 == 0:
             OF.grouped_linear_dgrad_pair(dh, wg, wu, index, out=dxp.local)
@@ -112,7 +114,7 @@ class _FusedEPMoEFn(torch.autograd.Function):
         C.ep_combine(dxp.ptrs, rows, topk_idx, E_loc, dx)
         dtopk = torch.empty((T, K), dtype=torch.float32, device=dout.device)
         C.ep_pull_dweights(dwt.ptrs, topk_idx, rank, E_loc, dtopk)
-        return dx, dtopk, None, dwg, dwu, dwd, None, None, None
+        return dx, dtopk, None, dwg, dwu, dwd, None, None, None, None
 
 
 def fused_ep_moe(block, x, w, idx):
@@ -124,4 +126,5 @@ def fused_ep_moe(block, x, w, idx):
     T = x.shape[0]
     cap = OF.moe_capacity_rows(T * pmap.expert_parallelism, block.num_experts_per_tok, block.num_experts_per_rank,
                                pmap.expert_parallelism, block.capacity_factor)
-    return _FusedEPMoEFn.apply(x.contiguous(), w.float(), idx, wg, wu, wd, sg, block.expert_start_idx, cap)
+    return _FusedEPMoEFn.apply(x.contiguous(), w.float(), idx, wg, wu, wd, sg, block.expert_start_idx, cap,
+                               (OF._holder(wg), OF._holder(wu), OF._holder(wd)))
