@@ -107,12 +107,12 @@ class ParallelAttention(nn.Module):
         clip = getattr(self.config, "clip_qkv", None)
         if clip is not None:
             q, k, v = q.clamp(-clip, clip), k.clamp(-clip, clip), v.clamp(-clip, clip)
+        cos, sin = position_embeddings
+        q = OF.rope(q, cos, sin, heads=self.num_attention_heads_per_rank)   # on the projection output, not a view
+        k = OF.rope(k, cos, sin, heads=self.num_key_value_heads_per_rank)
         q = q.view(B, S, self.num_attention_heads_per_rank, self.head_dim)
         k = k.view(B, S, self.num_key_value_heads_per_rank, self.head_dim)
         v = v.view(B, S, self.num_key_value_heads_per_rank, self.head_dim)
-        cos, sin = position_embeddings
-        q = OF.rope(q, cos, sin)
-        k = OF.rope(k, cos, sin)
         o = OF.attention(q, k, v, scale=self.scaling, causal=True)
         o = self._proj(o.reshape(B, S, self.num_attention_heads_per_rank * self.head_dim), self.o_proj)
         if tp > 1:

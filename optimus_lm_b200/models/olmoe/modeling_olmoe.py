@@ -66,12 +66,12 @@ class OlmoeParallelAttention(nn.Module):
         if self.config.clip_qkv is not None:
             c = self.config.clip_qkv
             q, k, v = q.clamp(-c, c), k.clamp(-c, c), v.clamp(-c, c)
+        cos, sin = position_embeddings
+        q = OF.rope(q, cos, sin, heads=self.num_attention_heads)     # on the projection output, not on a view
+        k = OF.rope(k, cos, sin, heads=self.num_key_value_heads)
         q = q.view(B, S, self.num_attention_heads, self.head_dim)
         k = k.view(B, S, self.num_key_value_heads, self.head_dim)
         v = v.view(B, S, self.num_key_value_heads, self.head_dim)
-        cos, sin = position_embeddings
-        q = OF.rope(q, cos, sin)
-        k = OF.rope(k, cos, sin)
         o = OF.attention(q, k, v, causal=True)
         return OF.linear(o.reshape(B, S, self.num_attention_heads * self.head_dim), self.o_proj.weight)
 

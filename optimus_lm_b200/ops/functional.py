@@ -270,32 +270,42 @@ def swiglu(g, u):
 
 # ------------------------------------------------------------------------------------ RoPE
 class _RopeFn(torch.autograd.Function):
-    """In-place rotary embedding on ``x[..., rot_offset:rot_offset+rot_dim]`` of a
-    ``[B, S, heads, head_dim]`` tensor."""
+    """In-place rotary embedding on ``x[..., rot_offset:rot_offset+rot_dim]`` of a ``[B, S, heads, head_dim]``
+    tensor, or of a ``[B, S, heads * head_dim]`` tensor when ``heads`` is given.  The second form lets a module
+    rotate the projection output itself rather than a view of it: an in-place autograd function on a view makes
+    autograd insert a CopySlices node (one more pass over the tensor in the backward)."""
 
     @staticmethod
-    def forward(ctx, x, cos_tab, sin_tab, rot_offset, rot_dim, interleaved):
-        B, S, Hn, D = x.shape
-        assert x.stride(-1) == 1 and x.stride(2) % 8 == 0 and x.stride(1) % 8 == 0 and rot_offset % 8 == 0
-        assert B == 1 or x.stride(0) == S * x.stride(1)
-        view = x[..., rot_offset:]
-        extension().rope_inplace(view, x.stride(1), B * S, Hn, x.stride(2), rot_dim, S, cos_tab, sin_tab,
+    def forward(ctx, x, cos_tab, sin_tab, rot_offset, rot_dim, interleaved, heads):
+        x4 = x if heads is None else x.view(x.shape[0], x.shape[1], heads, x.shape[2] // heads)
+        B, S, Hn, D = x4.shape
+        assert x4.stride(-1) == 1 and x4.stride(2) % 8 == 0 and x4.stride(1) % 8 == 0 and rot_offset % 8 == 0
+        assert B == 1 or x4.stride(0) == S * x4.stride(1)
+        view = x4[..., rot_offset:]
+        extension().rope_inplace(view, x4.stride(1), B * S, Hn, x4.stride(2), rot_dim, S, cos_tab, sin_tab,
                                  interleaved, False)
         ctx.mark_dirty(x)
         ctx.save_for_backward(cos_tab, sin_tab)
-        ctx.args = (rot_offset, rot_dim, interleaved)
+        ctx.args = (rot_offset, rot_dim, interleaved, heads)
         return x
 
     @staticmethod
     def backward(ctx, dy):
         cos_tab, sin_tab = ctx.saved_tensors
-        rot_offset, rot_dim, interleaved = ctx.args
-        dx = dy.contiguous().clone() if not dy.is_contiguous() else dy.clone()
-        B, S, Hn, D = dx.shape
-        view = dx[..., rot_offset:]
-        extension().rope_inplace(view, dx.stride(1), B * S, Hn, dx.stride(2), rot_dim, S, cos_tab, sin_tab,
+        rot_offset, rot_dim, interleaved, heads = ctx.args
+        # The incoming gradient is rotated in place when it is a whole contiguous tensor of its own (the usual
+        # case: it was just produced by the attention backward and has no other reader); otherwise on a copy.
+        own = _ROPE_BWD_INPLACE and dy.is_contiguous() and (dy._base is None or dy._base.numel() == dy.numel())
+        dx = dy if own else dy.contiguous().clone()
+        d4 = dx if heads is None else dx.view(dx.shape[0], dx.shape[1], heads, dx.shape[2] // heads)
+        B, S, Hn, D = d4.shape
+        view = d4[..., rot_offset:]
+        extension().rope_inplace(view, d4.stride(1), B * S, Hn, d4.stride(2), rot_dim, S, cos_tab, sin_tab,
                                  interleaved, True)
-        return dx, None, None, None, None, None
+        return dx, None, None, None, None, None, None
+
+
+_ROPE_BWD_INPLACE = True
 
 
 def rope_reference(x, cos_tab, sin_tab, rot_offset=0, rot_dim=None, interleaved=False):
@@ -313,12 +323,16 @@ def rope_reference(x, cos_tab, sin_tab, rot_offset=0, rot_dim=None, interleaved=
     return torch.cat([x[..., :rot_offset], out, x[..., rot_offset + rot_dim:]], dim=-1)
 
 
-def rope(x, cos_tab, sin_tab, rot_offset=0, rot_dim=None, interleaved=False):
-    """Rotary embedding on a ``[B, S, heads, head_dim]`` tensor (may modify ``x`` in place on
-    the kernel path; use the return value)."""
-    rot_dim = rot_dim or (x.shape[-1] - rot_offset)
+def rope(x, cos_tab, sin_tab, rot_offset=0, rot_dim=None, interleaved=False, heads=None):
+    """Rotary embedding on a ``[B, S, heads, head_dim]`` tensor, or on ``[B, S, heads * head_dim]`` with ``heads``
+    given (returned in the same shape).  May modify ``x`` in place on the kernel path; use the return value."""
+    if heads is not None and not (_kernel_ok(x) and cos_tab.is_cuda and x.is_contiguous()):
+        B, S, HD = x.shape
+        return rope(x.view(B, S, heads, HD // heads), cos_tab, sin_tab, rot_offset, rot_dim, interleaved).reshape(B, S, HD)
+    head_dim = x.shape[-1] if heads is None else x.shape[-1] // heads
+    rot_dim = rot_dim or (head_dim - rot_offset)
     if _kernel_ok(x) and rot_dim % 16 == 0 and cos_tab.is_cuda:
-        return _RopeFn.apply(x, cos_tab.contiguous(), sin_tab.contiguous(), rot_offset, rot_dim, interleaved)
+        return _RopeFn.apply(x, cos_tab.contiguous(), sin_tab.contiguous(), rot_offset, rot_dim, interleaved, heads)
     return rope_reference(x, cos_tab, sin_tab, rot_offset, rot_dim, interleaved)
 
 
