@@ -1,0 +1,87 @@
+"""DeepSeek-V3, Llama and OLMo on CPU/gloo (fp32): sharded layouts must reproduce the serial loss curve.
+
+DeepSeek-V3: expert parallel (routed experts sharded, dense MLP sharded over the EP group) and pipeline parallel
+with the merged-expert layout; Llama: tensor parallel (vocabulary-parallel embedding / head, column- and
+row-parallel projections); OLMo: pipeline x tensor parallel."""
+import pytest
+import torch
+
+DSV3 = "deepseek-ai/DeepSeek-V3--L3-DL1-N16-K2-MI64-A4-SE1-H128-I256"
+LLAMA = "meta-llama/Llama-3.2-1B--L2-H256-I512"
+OLMO = "allenai/OLMo-1B-hf--L4-H128-I256"
+OVR = {"vocab_size": 512, "max_position_embeddings": 64}
+STEPS, MBS, SEQ = 5, 2, 64
+
+
+def _tokens(n_seq):
+    g = torch.Generator().manual_seed(0)
+    return torch.randint(0, 512, (STEPS, n_seq, SEQ), generator=g)
+
+
+def _engine(model, **kw):
+    from optimus_lm_b200.engine import EngineArgs, TrainEngine
+    ovr = dict(OVR)
+    ovr.update(kw.pop("config_overrides", {}))
+    args = EngineArgs(model_choice=model, dtype="fp32", context_size=SEQ, lr=1e-3, warmup_steps=0,
+                      config_overrides=ovr, use_fused_ep_alltoall=False, **kw)
+    return TrainEngine(args, device=torch.device("cpu"))
+
+
+def _serial(model, n_seq, **kw):
+    torch.manual_seed(0)
+    e = _engine(model, batch_size=n_seq, optimizer="unsharded", **kw)
+    data = _tokens(n_seq)
+    return [e.train_step(data[s]).loss.item() for s in range(STEPS)]
+
+
+def _ep_worker(rank, world, model, ref):
+    import torch.distributed as dist
+    e = _engine(model, batch_size=MBS, optimizer="pgshard", expert_parallelism=world)
+    data = _tokens(MBS * world)
+    for s in range(STEPS):
+        loss = e.train_step(data[s, rank * MBS:(rank + 1) * MBS]).loss.detach().clone()
+        dist.all_reduce(loss)
+        assert abs(loss.item() / world - ref[s]) < 3e-3, (s, loss.item() / world, ref[s])
+
+
+def test_dsv3_ep2_matches_serial():
+    from dist_utils import run_distributed
+    ref = _serial(DSV3, 2 * MBS)
+    run_distributed(_ep_worker, 2, DSV3, ref)
+
+
+def _pp_worker(rank, world, model, ref, extra):
+    e = _engine(model, batch_size=2 * MBS, micro_batch_size=MBS, optimizer="shard", pipeline_parallelism=extra.get("pp", world),
+                tensor_parallelism=extra.get("tp", 1), pp_scheme="1f1b")
+    data = _tokens(2 * MBS)
+    for s in range(STEPS):
+        out = e.train_step(data[s])
+        if e.pmap.is_last_stage_rank:
+            assert abs(out.loss.item() - ref[s]) < 3e-3, (s, out.loss.item(), ref[s])
+
+
+def test_dsv3_pp3_matches_serial():
+    # three stages: the dense layer, and one MoE layer each
+    from dist_utils import run_distributed
+    ref = _serial(DSV3, 2 * MBS)
+    run_distributed(_pp_worker, 3, DSV3, ref, {})
+
+
+def _tp_worker(rank, world, model, ref):
+    e = _engine(model, batch_size=2 * MBS, optimizer="shard", tensor_parallelism=world)
+    data = _tokens(2 * MBS)
+    for s in range(STEPS):
+        out = e.train_step(data[s])
+        assert abs(out.loss.item() - ref[s]) < 3e-3, (s, out.loss.item(), ref[s])
+
+
+def test_llama_tp2_matches_serial():
+    from dist_utils import run_distributed
+    ref = _serial(LLAMA, 2 * MBS)
+    run_distributed(_tp_worker, 2, LLAMA, ref)
+
+
+def test_olmo_pp2_tp2_matches_serial():
+    from dist_utils import run_distributed
+    ref = _serial(OLMO, 2 * MBS)
+    run_distributed(_pp_worker, 4, OLMO, ref, {"pp": 2, "tp": 2})
