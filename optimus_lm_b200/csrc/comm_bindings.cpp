@@ -81,6 +81,50 @@ void pull_reduce_rows(const std::vector<int64_t>& peer_partial, int64_t row0, in
         "olb_pull_reduce_rows");
 }
 
+// Dense GEMM C = A B^T-style (same operand conventions as `gemm`) whose A and/or B outer rows live on peer GPUs:
+// the all-gather of a tensor-parallel projection happens inside the GEMM's TMA loads.  `a_local` / `b_local` are
+// this GPU's slices (shape [rows_per_peer, inner]); the peers' slices are given by address.
+void gemm_peer(const at::Tensor& a_local, const std::vector<int64_t>& a_peers, const at::Tensor& b_local,
+               const std::vector<int64_t>& b_peers, at::Tensor& c, int64_t M, int64_t N, int64_t K, bool a_mn_major,
+               bool b_mn_major, int64_t my_peer, bool accumulate, const c10::optional<at::Tensor>& status) {
+  TORCH_CHECK(a_local.is_cuda() && a_local.scalar_type() == at::kBFloat16 && b_local.scalar_type() == at::kBFloat16,
+              "bf16 CUDA operands expected");
+  TORCH_CHECK(a_local.dim() == 2 && b_local.dim() == 2 && a_local.stride(1) == 1 && b_local.stride(1) == 1);
+  c10::cuda::CUDAGuard guard(a_local.device());
+  auto ap = cptrs(a_peers);
+  auto bp = cptrs(b_peers);
+  olb_gemm_desc d{};
+  d.A = a_local.data_ptr();
+  d.B = b_local.data_ptr();
+  d.C = c.data_ptr();
+  d.lda = a_local.stride(0);
+  d.ldb = b_local.stride(0);
+  d.ldc = c.stride(-2);
+  d.a_rows = a_local.size(0);
+  d.b_rows = b_local.size(0);
+  d.M = static_cast<int>(M);
+  d.N = static_cast<int>(N);
+  d.K = static_cast<int>(K);
+  d.a_mn_major = a_mn_major;
+  d.b_mn_major = b_mn_major;
+  d.mode = OLB_GEMM_DENSE;
+  d.num_experts = 1;
+  d.accumulate = accumulate;
+  d.out_fp32 = c.scalar_type() == at::kFloat;
+  d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
+  d.n_peers = static_cast<int>(ap.empty() ? bp.size() : ap.size());
+  d.my_peer = static_cast<int>(my_peer);
+  if (!ap.empty()) {
+    d.A_peers = ap.data();
+    d.a_peer_rows = static_cast<int>(a_local.size(0));
+  }
+  if (!bp.empty()) {
+    d.B_peers = bp.data();
+    d.b_peer_rows = static_cast<int>(b_local.size(0));
+  }
+  check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (peer operands)");
+}
+
 int64_t rs_adamw_blocks(int64_t n) { return olb_rs_adamw_blocks(n); }
 
 void rs_adamw(const std::vector<int64_t>& peer_grad, const std::vector<int64_t>& peer_param, int64_t shard_off,
@@ -117,6 +161,7 @@ void register_comm(pybind11::module& m) {
   m.def("ep_combine", &ep_combine);
   m.def("ep_pull_dweights", &ep_pull_dweights);
   m.def("pull_reduce_rows", &pull_reduce_rows);
+  m.def("gemm_peer", &gemm_peer);
   m.def("rs_adamw_blocks", &rs_adamw_blocks);
   m.def("rs_adamw", &rs_adamw);
 }

@@ -57,7 +57,22 @@ struct GemmParams {
   int accumulate;              // C += A*B instead of C = A*B
   int out_fp32;
   int kb_split;                // > 0: k-blocks from this one on read B from the second tensor map (K-concatenated B)
+  int a_peer_rows;             // > 0: A is row-partitioned over peers, this many outer rows per peer (PeerArg maps)
+  int b_peer_rows;             // > 0: same for B
+  int m_rotate_blocks;         // row-block rotation of the tile order (start on the rows this GPU owns)
   int* status;
+};
+
+// Per-peer tensor maps of an operand whose outer rows live in the memories of up to 8 GPUs (plain TMA loads
+// from peer memory over NVLink, no multicast).
+template <bool PEER>
+struct PeerArg {
+  char unused;
+};
+template <>
+struct PeerArg<true> {
+  CUtensorMap a[8];
+  CUtensorMap b[8];
 };
 
 template <int BLOCK_N>
@@ -100,7 +115,8 @@ __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int num_m_b
   const int first_m = band * BAND;
   const int rows_in_band = min(BAND, num_m_blocks - first_m);
   const int r = t - band * band_tiles;
-  const int m_blk = first_m + r % rows_in_band;
+  int m_blk = first_m + r % rows_in_band;
+  if (p.m_rotate_blocks) m_blk = (m_blk + p.m_rotate_blocks) % num_m_blocks;
   const int n_blk = r / rows_in_band;
   ti.m0 = m_blk * BLOCK_M;
   ti.n0 = n_blk * BLOCK_N;
@@ -110,10 +126,11 @@ __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int num_m_b
   return true;
 }
 
-template <int BLOCK_N>
+template <int BLOCK_N, bool PEER>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 const __grid_constant__ CUtensorMap tma_b2, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tma_b2, const __grid_constant__ PeerArg<PEER> peers,
+                 const GemmParams p) {
   using L = SmemLayout<BLOCK_N>;
   constexpr int STAGES = L::STAGES;
   constexpr uint32_t TMEM_COLS = (2 * BLOCK_N < 32) ? 32 : 2 * BLOCK_N;
@@ -181,16 +198,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           const uint32_t fb = full_bar(stage);
           mbar_expect_tx(fb, L::STAGE_BYTES);
           const int k0 = kb * BLOCK_K;
+          const CUtensorMap* tma_a_sel = &tma_a;
+          int a_row = p.a_mn_major ? k0 : ti.m0;  // outer-row coordinate of A's 2D view
+          if constexpr (PEER) {
+            if (p.a_peer_rows > 0) {  // the outer rows of A are spread over the peers' memories
+              tma_a_sel = &peers.a[a_row / p.a_peer_rows];
+              a_row = a_row % p.a_peer_rows;
+            }
+          }
           if (!p.a_mn_major) {
-            tma_load_2d(sa, &tma_a, fb, k0, ti.m0);
+            tma_load_2d(sa, tma_a_sel, fb, k0, a_row);
           } else {
 #pragma unroll
-            for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d(sa + j * MN_BOX_BYTES, &tma_a, fb, ti.m0 + j * 64, k0);
+            for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d(sa + j * MN_BOX_BYTES, tma_a_sel, fb, ti.m0 + j * 64, a_row);
           }
           // K-concatenated B: the second half of the K range comes from a second tensor of the same layout
           const bool second = p.kb_split > 0 && kb >= p.kb_split;
           const CUtensorMap* tmb = second ? &tma_b2 : &tma_b;
-          const int kB = second ? k0 - p.kb_split * BLOCK_K : k0;
+          int kB = second ? k0 - p.kb_split * BLOCK_K : k0;
+          if constexpr (PEER) {
+            if (p.b_peer_rows > 0 && p.b_mn_major) {  // B's K rows are spread over the peers' memories
+              tmb = &peers.b[kB / p.b_peer_rows];
+              kB = kB % p.b_peer_rows;
+            }
+          }
           if (!p.b_mn_major) {
             tma_load_2d(sb, tmb, fb, kB, ti.expert * p.b_expert_rows + ti.n0);
           } else {
@@ -412,13 +443,13 @@ int make_tmap_4d_bf16(CUtensorMap* map, const void* base, const uint64_t dims[4]
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-template <int BLOCK_N>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p, int num_sms,
-                  cudaStream_t stream) {
+template <int BLOCK_N, bool PEER>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const PeerArg<PEER>& peers,
+                  const GemmParams& p, int num_sms, cudaStream_t stream) {
   using L = SmemLayout<BLOCK_N>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BLOCK_N, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return -3;
     configured = true;
   }
@@ -427,7 +458,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
   tiles = nm * nn * (p.mode == OLB_GEMM_RAGGED_K ? p.num_experts : 1);
   int grid = static_cast<int>(tiles < num_sms ? tiles : num_sms);
   if (grid <= 0) return 0;
-  gemm_bf16_kernel<BLOCK_N><<<grid, NUM_THREADS, L::TOTAL, stream>>>(ta, tb, tb2, p);
+  gemm_bf16_kernel<BLOCK_N, PEER><<<grid, NUM_THREADS, L::TOTAL, stream>>>(ta, tb, tb2, peers, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -521,12 +552,53 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   p.accumulate = d->accumulate;
   p.out_fp32 = d->out_fp32;
   p.kb_split = kb_split;
+  p.a_peer_rows = 0;
+  p.b_peer_rows = 0;
+  p.m_rotate_blocks = 0;
   p.status = d->status;
   const int sms = d->max_ctas > 0 && d->max_ctas < num_sms ? d->max_ctas : num_sms;
+  if (d->n_peers > 0) {
+    // Operand rows spread over peer GPUs (tensor-parallel all-gather fused into the GEMM's loads).
+    if (d->n_peers > 8 || d->mode != OLB_GEMM_DENSE || kb_split) return -14;
+    PeerArg<true> peers;
+    if (d->A_peers != nullptr) {
+      if (d->a_peer_rows <= 0 || d->a_peer_rows % (d->a_mn_major ? BLOCK_K : BLOCK_M)) return -14;
+      for (int r = 0; r < d->n_peers; ++r) {
+        if (reinterpret_cast<uintptr_t>(d->A_peers[r]) & 15) return -14;
+        rc = !d->a_mn_major ? make_tmap_2d_bf16(&peers.a[r], d->A_peers[r], d->K, d->a_peer_rows, d->lda * 2, BLOCK_K, BLOCK_M)
+                            : make_tmap_2d_bf16(&peers.a[r], d->A_peers[r], d->M, d->a_peer_rows, d->lda * 2, 64, BLOCK_K);
+        if (rc) return rc;
+      }
+      for (int r = d->n_peers; r < 8; ++r) peers.a[r] = peers.a[0];
+      p.a_peer_rows = d->a_peer_rows;
+      if (!d->a_mn_major) p.m_rotate_blocks = (d->my_peer * d->a_peer_rows) / BLOCK_M;
+    } else {
+      for (int r = 0; r < 8; ++r) peers.a[r] = ta;
+    }
+    if (d->B_peers != nullptr) {
+      if (!d->b_mn_major || d->b_peer_rows <= 0 || d->b_peer_rows % BLOCK_K) return -14;
+      for (int r = 0; r < d->n_peers; ++r) {
+        if (reinterpret_cast<uintptr_t>(d->B_peers[r]) & 15) return -14;
+        rc = make_tmap_2d_bf16(&peers.b[r], d->B_peers[r], d->N, d->b_peer_rows, d->ldb * 2, 64, BLOCK_K);
+        if (rc) return rc;
+      }
+      for (int r = d->n_peers; r < 8; ++r) peers.b[r] = peers.b[0];
+      p.b_peer_rows = d->b_peer_rows;
+    } else {
+      for (int r = 0; r < 8; ++r) peers.b[r] = tb;
+    }
+    switch (block_n) {
+      case 256: return launch<256, true>(ta, tb, tb2, peers, p, sms, stream);
+      case 128: return launch<128, true>(ta, tb, tb2, peers, p, sms, stream);
+      case 64: return launch<64, true>(ta, tb, tb2, peers, p, sms, stream);
+      default: return -12;
+    }
+  }
+  PeerArg<false> nopeers{};
   switch (block_n) {
-    case 256: return launch<256>(ta, tb, tb2, p, sms, stream);
-    case 128: return launch<128>(ta, tb, tb2, p, sms, stream);
-    case 64: return launch<64>(ta, tb, tb2, p, sms, stream);
+    case 256: return launch<256, false>(ta, tb, tb2, nopeers, p, sms, stream);
+    case 128: return launch<128, false>(ta, tb, tb2, nopeers, p, sms, stream);
+    case 64: return launch<64, false>(ta, tb, tb2, nopeers, p, sms, stream);
     default: return -12;
   }
 }

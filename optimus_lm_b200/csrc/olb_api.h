@@ -32,6 +32,14 @@ typedef struct {
   int* status;               // device status word (may be NULL)
   const void* B2;            // optional second B of the same layout: K range [k_split, K) is read from it
   int k_split;               // multiple of 64; 0 = single B
+  // Operands whose outer rows are spread over peer GPUs (dense mode): n_peers > 0 enables it.  A_peers[r] /
+  // B_peers[r] point at peer r's slice (mapped in this process), a_peer_rows / b_peer_rows outer rows each;
+  // A/B themselves must still be valid pointers (this GPU's slice).  B must be MN-major when partitioned.
+  int n_peers, my_peer;
+  const void* const* A_peers;
+  int a_peer_rows;
+  const void* const* B_peers;
+  int b_peer_rows;
 } olb_gemm_desc;
 
 int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream);

@@ -78,7 +78,7 @@ class DeepseekV3ParallelMLP(nn.Module):
         if sharded:
             x = x.reshape(-1, shape[-1])
             from ...parallel import tp_fused
-            if tp_fused.usable(x, p.ep_group):
+            if tp_fused.usable(x, p.ep_group, (self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight)):
                 y = tp_fused.ag_swiglu_mlp_rs(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight,
                                               p.ep_ind, p.expert_parallelism, p.ep_group)
                 return y.reshape(shape)

@@ -142,6 +142,42 @@ def w_fused_optimizer_vs_nccl(rank, world):
         assert abs(na - nb) < 5e-2 * abs(na) + 1e-3, (losses)
 
 
+def w_tp_fused_mlp_vs_nccl(rank, world):
+    """All-gather -> GEMM and GEMM -> reduce-scatter over peer memory against the NCCL collectives + local GEMMs."""
+    import torch.distributed as dist
+    from optimus_lm_b200.models.common.comms_ptfunctions import (forward_allgather_backward_reducescatter,
+                                                                forward_reducescatter_backward_allgather)
+    from optimus_lm_b200.ops import functional as OF
+    from optimus_lm_b200.parallel import tp_fused
+    T_loc, H, I = 256, 512, 384
+    grp = dist.group.WORLD
+    gen = torch.Generator(device="cuda").manual_seed(7)          # same weights' seed on every rank, sliced per rank
+    wg_full = (torch.randn(world * I, H, device="cuda", generator=gen) * 0.05).to(torch.bfloat16)
+    wu_full = (torch.randn(world * I, H, device="cuda", generator=gen) * 0.05).to(torch.bfloat16)
+    wd_full = (torch.randn(H, world * I, device="cuda", generator=gen) * 0.05).to(torch.bfloat16)
+    gen = torch.Generator(device="cuda").manual_seed(100 + rank)
+    x0 = torch.randn(T_loc, H, device="cuda", generator=gen).to(torch.bfloat16)
+    go = torch.randn(T_loc, H, device="cuda", generator=gen).to(torch.bfloat16)
+    res = {}
+    for fused in (False, True):
+        wg = wg_full[rank * I:(rank + 1) * I].clone().requires_grad_()
+        wu = wu_full[rank * I:(rank + 1) * I].clone().requires_grad_()
+        wd = wd_full[:, rank * I:(rank + 1) * I].contiguous().clone().requires_grad_()
+        x = x0.clone().requires_grad_()
+        if fused:
+            assert tp_fused.usable(x, grp, (wg, wu, wd))
+            y = tp_fused.ag_swiglu_mlp_rs(x, wg, wu, wd, rank, world, grp)
+        else:
+            xa = forward_allgather_backward_reducescatter.apply(x, rank, world, grp, False)
+            h = OF.swiglu(OF.linear(xa, wg), OF.linear(xa, wu))
+            y = forward_reducescatter_backward_allgather.apply(OF.linear(h, wd), rank, world, grp, False, False)
+        y.backward(go)
+        res[fused] = [t.detach().clone() for t in (y, x.grad, wg.grad, wu.grad, wd.grad)]
+    for name, a, b in zip(("y", "dx", "dwg", "dwu", "dwd"), res[False], res[True]):
+        assert _rel(b, a) < 2e-2, (name, _rel(b, a))
+    assert OF.check_status("cuda") == 0
+
+
 # ----------------------------------------------------------------------------- tests
 def test_symm_barrier_and_pull_reduce():
     _run("w_symm_barrier_and_pull", 2)
@@ -153,3 +189,7 @@ def test_fused_ep_moe_matches_allgather_transport():
 
 def test_fused_engine_matches_nccl_engine():
     _run("w_fused_optimizer_vs_nccl", 2)
+
+
+def test_tp_fused_mlp_matches_nccl_path():
+    _run("w_tp_fused_mlp_vs_nccl", 2)
