@@ -91,29 +91,40 @@ class _FusedEPMoEFn(torch.autograd.Function):
         dyp = torch.empty((cap, H), dtype=dout.dtype, device=dout.device)
         C.ep_gather_rows(ds.ptrs, T, index.src_of, index.meta, dyp)
         hg, hu, hd = ctx.holders
-        dwd = OF.grouped_linear_wgrad(dyp, act, index, H, I, hd) if ctx.needs_input_grad[5] else None
+        # Critical path first: the input-gradient chain up to the rows the other ranks will pull ...
         dact = OF.grouped_linear_dgrad(dyp, wd, index)
-        del dyp
         dh = torch.empty_like(h)
         dwt = sg.named("ep_dw", (n * T, K), torch.float32)
         dwt.local.zero_()
         C.swiglu_rowscale_bwd(dact, h[:, :I], h[:, I:], index.src_of, index.k_of, w_all, index.meta, dh[:, :I],
                               dh[:, I:], dwt.local)
         del dact
-        dwg = OF.grouped_linear_wgrad(dh[:, :I], xp, index, I, H, hg) if ctx.needs_input_grad[3] else None
-        dwu = OF.grouped_linear_wgrad(dh[:, I:], xp, index, I, H, hu) if ctx.needs_input_grad[4] else None
         dxp = sg.named("ep_out", (cap, H), dout.dtype)
         if I % 64 == 0:
             OF.grouped_linear_dgrad_pair(dh, wg, wu, index, out=dxp.local)
         else:
             OF.grouped_linear_dgrad(dh[:, :I], wg, index, out=dxp.local)
             OF.grouped_linear_dgrad(dh[:, I:], wu, index, out=dxp.local, accumulate=True)
-        sg.barrier(3)
-
         dx = torch.empty((T, H), dtype=dout.dtype, device=dout.device)
-        C.ep_combine(dxp.ptrs, rows, topk_idx, E_loc, dx)
         dtopk = torch.empty((T, K), dtype=torch.float32, device=dout.device)
-        C.ep_pull_dweights(dwt.ptrs, topk_idx, rank, E_loc, dtopk)
+        # ... then the combine all-to-all (NVLink-bound pulls) runs on a side stream underneath the three
+        # weight-gradient GEMMs, which nothing downstream waits for.
+        main = torch.cuda.current_stream()
+        side = sg.side_stream()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(ready)
+            sg.barrier(3)
+            C.ep_combine(dxp.ptrs, rows, topk_idx, E_loc, dx)
+            C.ep_pull_dweights(dwt.ptrs, topk_idx, rank, E_loc, dtopk)
+            done = torch.cuda.Event()
+            done.record(side)
+        dwd = OF.grouped_linear_wgrad(dyp, act, index, H, I, hd) if ctx.needs_input_grad[5] else None
+        del dyp
+        dwg = OF.grouped_linear_wgrad(dh[:, :I], xp, index, I, H, hg) if ctx.needs_input_grad[3] else None
+        dwu = OF.grouped_linear_wgrad(dh[:, I:], xp, index, I, H, hu) if ctx.needs_input_grad[4] else None
+        main.wait_event(done)
         return dx, dtopk, None, dwg, dwu, dwd, None, None, None, None
 
 

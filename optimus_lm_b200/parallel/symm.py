@@ -124,6 +124,13 @@ class SymmGroup:
         return st
 
     # ------------------------------------------------------------------ synchronisation
+    def side_stream(self) -> "torch.cuda.Stream":
+        """A second stream of this group for peer-memory kernels that run underneath compute of the main stream."""
+        s = getattr(self, "_side_stream", None)
+        if s is None:
+            s = self._side_stream = torch.cuda.Stream(device=self.device)
+        return s
+
     def barrier(self, channel: int = 0):
         """All ranks' preceding work on the current stream is complete and visible to peers when
         the kernels enqueued after this call start."""
