@@ -28,7 +28,6 @@ namespace olb {
 int attn_tmap(CUtensorMap* map, const void* ptr, int Dh, int H, int S, int B, long long bs, long long ss, long long hs,
               int box_rows);
 
-constexpr int BW_THREADS = 320;  // TMA warp, MMA warp, 8 recompute warps
 constexpr int BW_R = 128;  // resident rows per CTA
 constexpr int BW_T = 64;   // streamed rows per step
 
@@ -36,6 +35,11 @@ template <int D1, int D2, bool KV_MODE>
 struct BwdCfg {
   static constexpr int NB = (KV_MODE && D1 > 128) ? 1 : 2;  // score / dS buffers
   static constexpr int TS = (D1 > 128) ? 2 : 3;               // stages of the streamed-tile ring
+  // Recompute warps: NG warps share each group of 32 rows (TMEM lanes) and split the 64 columns of a tile.  The
+  // per-tile chain (wait, TMEM read, exp, shared-memory write, signal) is latency-bound, so more warps with less
+  // work each hide it better: four per lane group where the epilogue's 32-column pieces allow it.
+  static constexpr int NG = (D1 == 128 && D2 == 128) ? 4 : 2;
+  static constexpr int THREADS = 64 + 128 * NG;                // TMA warp, MMA warp, 4 * NG recompute warps
   static constexpr int R1_BYTES = BW_R * D1 * 2, R2_BYTES = BW_R * D2 * 2;
   static constexpr int T1_BYTES = BW_T * D1 * 2, T2_BYTES = BW_T * D2 * 2;
   static constexpr int DS_BYTES = BW_R * BW_T * 2;
@@ -67,7 +71,7 @@ enum { BB_R = 0, BB_T_FULL0 = 1, BB_T_EMPTY0 = 4, BB_XY_FULL0 = 7, BB_XY_EMPTY0 
        BB_ACC = 15, BB_COUNT = 16 };
 
 template <int D1, int D2, bool KV_MODE>
-__global__ void __launch_bounds__(BW_THREADS, 1)
+__global__ void __launch_bounds__((BwdCfg<D1, D2, KV_MODE>::THREADS), 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant__ CUtensorMap tm_r2,
                 const __grid_constant__ CUtensorMap tm_t1, const __grid_constant__ CUtensorMap tm_t2,
                 const AttnBwdParams p) {
@@ -101,8 +105,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(BB_XY_FULL0 + s), 1);
-      mbar_init(bar(BB_XY_EMPTY0 + s), 8);
-      mbar_init(bar(BB_DS_FULL0 + s), 8);
+      mbar_init(bar(BB_XY_EMPTY0 + s), 4 * L::NG);
+      mbar_init(bar(BB_DS_FULL0 + s), 4 * L::NG);
       mbar_init(bar(BB_DS_EMPTY0 + s), 1);
     }
     mbar_init(bar(BB_ACC), 1);
@@ -204,12 +208,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
     }
   } else {
     // ---------------------------------------------------------------- softmax recompute, dS, epilogue
-    // Warps w and w+4 share the 32 rows (TMEM lanes) of lane group w % 4 and split the 64 columns of every tile.
-    // (Giving the two groups alternate tiles instead was measured slower: 1.67 ms against 1.36 ms for the
+    // Warps w, w+4, ... share the 32 rows (TMEM lanes) of lane group w % 4 and split the 64 columns of every tile.
+    // (Giving the groups alternate tiles instead was measured slower: 1.67 ms against 1.36 ms for the
     // B4 S4096 H16 D128 backward.)
-    constexpr bool TILE_SPLIT = false;
+    constexpr int NG = L::NG;
+    constexpr int CPT = BW_T / NG;   // columns per thread: 32 or 16
     const int lg = warp & 3;
     const int grp = (warp - 2) >> 2;
+    const int c0 = grp * CPT;        // first column of this thread
     const int row = lg * 32 + lane;  // resident row == TMEM lane
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(lg * 32) << 16);
     bool ok = true;
@@ -219,7 +225,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
       my_lse2 = p.lse2[o];
       my_delta = p.delta[o];
     }
-    for (int it = TILE_SPLIT ? grp : 0; it < n_iter && ok; it += TILE_SPLIT ? 2 : 1) {
+    for (int it = 0; it < n_iter && ok; ++it) {
       const int s = it % NB;
       const int tr = t_row0(it);
       if (!mbar_wait(bar(BB_XY_FULL0 + s), (it / NB) & 1u, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) { ok = false; break; }
@@ -233,58 +239,60 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
       const float* lse_col = nullptr;
       const float* dl_col = nullptr;
       if (KV_MODE) {
-        const long long o = (static_cast<long long>(b) * p.Hq + t_head(it)) * p.S + tr;
+        const long long o = (static_cast<long long>(b) * p.Hq + t_head(it)) * p.S + tr + c0;
         lse_col = p.lse2 + o;
         dl_col = p.delta + o;
       }
-#pragma unroll 1
-      for (int c = TILE_SPLIT ? 0 : grp; c < (TILE_SPLIT ? 2 : grp + 1); ++c) {
-        uint32_t x[32], y[32];
-        tmem_ld_32x32b_x32(lane_addr + L::TM_X + s * BW_T + c * 32, x);
-        tmem_ld_32x32b_x32(lane_addr + L::TM_Y + s * BW_T + c * 32, y);
-        tmem_ld_wait();
-        uint32_t pp[16], ds[16];
+      uint32_t x[CPT], y[CPT];
+      if constexpr (CPT == 32) {
+        tmem_ld_32x32b_x32(lane_addr + L::TM_X + s * BW_T + c0, x);
+        tmem_ld_32x32b_x32(lane_addr + L::TM_Y + s * BW_T + c0, y);
+      } else {
+        tmem_ld_32x32b_x16(lane_addr + L::TM_X + s * BW_T + c0, x);
+        tmem_ld_32x32b_x16(lane_addr + L::TM_Y + s * BW_T + c0, y);
+      }
+      tmem_ld_wait();
+      uint32_t pp[CPT / 2], ds[CPT / 2];
 #pragma unroll
-        for (int i8 = 0; i8 < 4; ++i8) {
-          float l2[8], dl[8];
-          if (KV_MODE) {
-            // all threads read the same 8 query statistics: two broadcast 16-byte loads each
-            const float4 a0 = __ldg(reinterpret_cast<const float4*>(lse_col + c * 32 + i8 * 8));
-            const float4 a1 = __ldg(reinterpret_cast<const float4*>(lse_col + c * 32 + i8 * 8 + 4));
-            const float4 b0 = __ldg(reinterpret_cast<const float4*>(dl_col + c * 32 + i8 * 8));
-            const float4 b1 = __ldg(reinterpret_cast<const float4*>(dl_col + c * 32 + i8 * 8 + 4));
-            l2[0] = a0.x; l2[1] = a0.y; l2[2] = a0.z; l2[3] = a0.w; l2[4] = a1.x; l2[5] = a1.y; l2[6] = a1.z; l2[7] = a1.w;
-            dl[0] = b0.x; dl[1] = b0.y; dl[2] = b0.z; dl[3] = b0.w; dl[4] = b1.x; dl[5] = b1.y; dl[6] = b1.z; dl[7] = b1.w;
-          }
-          float pv[8], dv[8];
+      for (int i8 = 0; i8 < CPT / 8; ++i8) {
+        float l2[8], dl[8];
+        if (KV_MODE) {
+          // all threads read the same 8 query statistics: two broadcast 16-byte loads each
+          const float4 a0 = __ldg(reinterpret_cast<const float4*>(lse_col + i8 * 8));
+          const float4 a1 = __ldg(reinterpret_cast<const float4*>(lse_col + i8 * 8 + 4));
+          const float4 b0 = __ldg(reinterpret_cast<const float4*>(dl_col + i8 * 8));
+          const float4 b1 = __ldg(reinterpret_cast<const float4*>(dl_col + i8 * 8 + 4));
+          l2[0] = a0.x; l2[1] = a0.y; l2[2] = a0.z; l2[3] = a0.w; l2[4] = a1.x; l2[5] = a1.y; l2[6] = a1.z; l2[7] = a1.w;
+          dl[0] = b0.x; dl[1] = b0.y; dl[2] = b0.z; dl[3] = b0.w; dl[4] = b1.x; dl[5] = b1.y; dl[6] = b1.z; dl[7] = b1.w;
+        }
+        float pv[8], dv[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int col = c * 32 + i8 * 8 + e;
-            const int kv = KV_MODE ? r0 + row : tr + col;
-            const int qi = KV_MODE ? tr + col : r0 + row;
-            const bool valid = !diag || kv <= qi;
-            const float pr = valid ? ex2_approx(__uint_as_float(x[i8 * 8 + e]) * p.scale_log2 - (KV_MODE ? l2[e] : my_lse2)) : 0.f;
-            pv[e] = pr;
-            dv[e] = pr * (__uint_as_float(y[i8 * 8 + e]) - (KV_MODE ? dl[e] : my_delta));
-          }
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            pp[i8 * 4 + e] = pack_bf16(pv[2 * e], pv[2 * e + 1]);
-            ds[i8 * 4 + e] = pack_bf16(dv[2 * e], dv[2 * e + 1]);
-          }
+        for (int e = 0; e < 8; ++e) {
+          const int col = c0 + i8 * 8 + e;
+          const int kv = KV_MODE ? r0 + row : tr + col;
+          const int qi = KV_MODE ? tr + col : r0 + row;
+          const bool valid = !diag || kv <= qi;
+          const float pr = valid ? ex2_approx(__uint_as_float(x[i8 * 8 + e]) * p.scale_log2 - (KV_MODE ? l2[e] : my_lse2)) : 0.f;
+          pv[e] = pr;
+          dv[e] = pr * (__uint_as_float(y[i8 * 8 + e]) - (KV_MODE ? dl[e] : my_delta));
         }
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int chunk = c * 4 + q;  // 16-byte chunk of the 128-byte row
-          const uint32_t off = row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + L::OFF_DS + s * L::DS_BYTES + off),
-                       "r"(ds[4 * q]), "r"(ds[4 * q + 1]), "r"(ds[4 * q + 2]), "r"(ds[4 * q + 3])
+        for (int e = 0; e < 4; ++e) {
+          pp[i8 * 4 + e] = pack_bf16(pv[2 * e], pv[2 * e + 1]);
+          ds[i8 * 4 + e] = pack_bf16(dv[2 * e], dv[2 * e + 1]);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < CPT / 8; ++q) {
+        const int chunk = grp * (CPT / 8) + q;  // 16-byte chunk of the 128-byte row
+        const uint32_t off = row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + L::OFF_DS + s * L::DS_BYTES + off),
+                     "r"(ds[4 * q]), "r"(ds[4 * q + 1]), "r"(ds[4 * q + 2]), "r"(ds[4 * q + 3])
+                     : "memory");
+        if (KV_MODE)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + L::OFF_P + s * L::DS_BYTES + off),
+                       "r"(pp[4 * q]), "r"(pp[4 * q + 1]), "r"(pp[4 * q + 2]), "r"(pp[4 * q + 3])
                        : "memory");
-          if (KV_MODE)
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + L::OFF_P + s * L::DS_BYTES + off),
-                         "r"(pp[4 * q]), "r"(pp[4 * q + 1]), "r"(pp[4 * q + 2]), "r"(pp[4 * q + 3])
-                         : "memory");
-        }
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -296,9 +304,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
     }
     if (ok && n_iter > 0 && mbar_wait(bar(BB_ACC), 0, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) {
       tc_fence_after();
-      // each warp of a pair stores half of the columns
+      // the warps sharing a lane group store equal pieces of the columns
       auto store_rows = [&](uint32_t tm_col, int width, __nv_bfloat16* out, long long bs, long long ss, long long hs, float mul) {
-        const int half = width / 2;
+        const int half = width / NG;
         const int c = grp;
         __nv_bfloat16* orow = out + static_cast<long long>(b) * bs + static_cast<long long>(r0 + row) * ss +
                               static_cast<long long>(head_r) * hs + c * half;
@@ -406,12 +414,12 @@ static int launch_bwd(const olb_attn_bwd_desc* d, cudaStream_t stream) {
   p.o1_bs = d->dv_bs; p.o1_ss = d->dv_ss; p.o1_hs = d->dv_hs;
   p.out2 = static_cast<__nv_bfloat16*>(d->dk);
   p.o2_bs = d->dk_bs; p.o2_ss = d->dk_ss; p.o2_hs = d->dk_hs;
-  attn_bwd_kernel<D, DV, true><<<dim3(d->S / BW_R, d->Hkv, d->B), BW_THREADS, LK::TOTAL, stream>>>(k128, v128, q64, do64, p);
+  attn_bwd_kernel<D, DV, true><<<dim3(d->S / BW_R, d->Hkv, d->B), LK::THREADS, LK::TOTAL, stream>>>(k128, v128, q64, do64, p);
   // dQ
   p.out1 = nullptr;
   p.out2 = static_cast<__nv_bfloat16*>(d->dq);
   p.o2_bs = d->dq_bs; p.o2_ss = d->dq_ss; p.o2_hs = d->dq_hs;
-  attn_bwd_kernel<D, DV, false><<<dim3(d->S / BW_R, d->Hq, d->B), BW_THREADS, LQ::TOTAL, stream>>>(q128, do128, k64, v64, p);
+  attn_bwd_kernel<D, DV, false><<<dim3(d->S / BW_R, d->Hq, d->B), LQ::THREADS, LQ::TOTAL, stream>>>(q128, do128, k64, v64, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

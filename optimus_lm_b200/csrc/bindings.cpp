@@ -28,7 +28,8 @@ T* opt_ptr(const c10::optional<at::Tensor>& t) {
 void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, int64_t M, int64_t N, int64_t K, bool a_mn_major,
           bool b_mn_major, bool accumulate, int64_t mode, const c10::optional<at::Tensor>& meta, int64_t num_experts,
           int64_t b_expert_rows, int64_t c_expert_stride, const c10::optional<at::Tensor>& status, int64_t block_n,
-          int64_t max_ctas, const c10::optional<at::Tensor>& b2, int64_t k_split) {
+          int64_t max_ctas, const c10::optional<at::Tensor>& b2, int64_t k_split,
+          const c10::optional<at::Tensor>& blk_range) {
   CHECK_CUDA_BF16(a);
   CHECK_CUDA_BF16(b);
   TORCH_CHECK(c.is_cuda() && (c.scalar_type() == at::kBFloat16 || c.scalar_type() == at::kFloat), "c must be bf16/fp32");
@@ -65,6 +66,7 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, int64_t M, in
     d.B2 = b2->data_ptr();
     d.k_split = static_cast<int>(k_split);
   }
+  d.blk_range = opt_ptr<const int>(blk_range);
   check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16");
 }
 

@@ -34,11 +34,12 @@ void symm_barrier(const std::vector<int64_t>& pads, int64_t my_rank, int64_t cha
 }
 
 void ep_gather_rows(const std::vector<int64_t>& peer_x, int64_t T, const at::Tensor& src_of, const at::Tensor& meta,
-                    at::Tensor& out) {
+                    at::Tensor& out, const c10::optional<at::Tensor>& blk_range) {
   c10::cuda::CUDAGuard guard(out.device());
   auto p = cptrs(peer_x);
   check(olb_ep_gather_rows(p.data(), static_cast<int>(p.size()), static_cast<int>(T), src_of.data_ptr<int>(),
-                           meta.data_ptr<int>(), out.data_ptr(), static_cast<int>(out.size(0)),
+                           meta.data_ptr<int>(), blk_range.has_value() ? blk_range->data_ptr<int>() : nullptr,
+                           out.data_ptr(), static_cast<int>(out.size(0)),
                            static_cast<int>(out.size(1)), cur_stream()),
         "olb_ep_gather_rows");
 }

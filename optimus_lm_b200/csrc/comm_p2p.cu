@@ -61,22 +61,42 @@ __global__ void symm_barrier_kernel(PeerPtrsMut pads, int my_rank, int n, int ch
   }
 }
 
-// out[row,:] = peer_x[g / T][(g % T), :] with g = src_of[row]; padding rows -> 0.  One warp per row.
+// out[row,:] = peer_x[g / T][(g % T), :] with g = src_of[row]; padding rows -> 0.  One warp per row; a lane keeps up
+// to eight 16-byte loads in flight, so that few resident warps saturate NVLink and the kernel can run underneath a
+// GEMM (the grid is capped well below the SMs' thread capacity).  `blk_range` (optional, device) restricts the rows to
+// the 128-row blocks [blk_range[0], blk_range[1]).
 __global__ void __launch_bounds__(256)
 ep_gather_rows_kernel(PeerPtrs peer_x, int T, const int* __restrict__ src_of, const int* __restrict__ meta,
-                      __nv_bfloat16* __restrict__ out, int cap, int cols) {
+                      const int* __restrict__ blk_range, __nv_bfloat16* __restrict__ out, int cap, int cols) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nrows = min(meta[0] * 128, cap);
-  for (int row = blockIdx.x * 8 + warp; row < nrows; row += gridDim.x * 8) {
+  int row_begin = 0, row_end = min(meta[0] * 128, cap);
+  if (blk_range) {
+    row_begin = blk_range[0] * 128;
+    row_end = min(row_end, blk_range[1] * 128);
+  }
+  const int vec = cols / 8;  // 16-byte vectors per row
+  for (int row = row_begin + blockIdx.x * 8 + warp; row < row_end; row += gridDim.x * 8) {
     const int g = src_of[row];
     uint4* dst = reinterpret_cast<uint4*>(out + static_cast<long long>(row) * cols);
     if (g >= 0) {
       const int r = g / T, t = g - r * T;
       const uint4* s = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(peer_x.p[r]) +
                                                       static_cast<long long>(t) * cols);
-      for (int c = lane; c < cols / 8; c += 32) dst[c] = s[c];
+      for (int c0 = 0; c0 < vec; c0 += 256) {
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = c0 + i * 32 + lane;
+          if (c < vec) v[i] = s[c];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = c0 + i * 32 + lane;
+          if (c < vec) dst[c] = v[i];
+        }
+      }
     } else {
-      for (int c = lane; c < cols / 8; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+      for (int c = lane; c < vec; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
     }
   }
 }
@@ -108,16 +128,24 @@ ep_combine_kernel(PeerPtrs peer_y, const int* __restrict__ rows, const int* __re
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int k = 0; k < K; ++k) {
-        const int row = s_row[k];
-        if (row < 0) continue;
-        const uint4 v = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(peer_y.p[s_rank[k]]) +
-                                                        static_cast<long long>(row) * cols + c);
-        float2 a;
-        a = unpack_bf16(v.x); acc[0] += a.x; acc[1] += a.y;
-        a = unpack_bf16(v.y); acc[2] += a.x; acc[3] += a.y;
-        a = unpack_bf16(v.z); acc[4] += a.x; acc[5] += a.y;
-        a = unpack_bf16(v.w); acc[6] += a.x; acc[7] += a.y;
+      for (int k0 = 0; k0 < K; k0 += 8) {  // up to eight peer loads in flight per thread, summed in fixed k order
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int k = k0 + i;
+          v[i] = make_uint4(0, 0, 0, 0);
+          if (k < K && s_row[k] >= 0)
+            v[i] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(peer_y.p[s_rank[k]]) +
+                                                   static_cast<long long>(s_row[k]) * cols + c);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float2 a;
+          a = unpack_bf16(v[i].x); acc[0] += a.x; acc[1] += a.y;
+          a = unpack_bf16(v[i].y); acc[2] += a.x; acc[3] += a.y;
+          a = unpack_bf16(v[i].z); acc[4] += a.x; acc[5] += a.y;
+          a = unpack_bf16(v[i].w); acc[6] += a.x; acc[7] += a.y;
+        }
       }
       uint4 o;
       o.x = pack_bf16(acc[0], acc[1]);
@@ -268,14 +296,14 @@ extern "C" int olb_symm_barrier(void* const* pads, int my_rank, int n, int chann
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-extern "C" int olb_ep_gather_rows(const void* const* peer_x, int n, int T, const int* src_of, const int* meta, void* out,
-                                  int cap, int cols, cudaStream_t stream) {
+extern "C" int olb_ep_gather_rows(const void* const* peer_x, int n, int T, const int* src_of, const int* meta,
+                                  const int* blk_range, void* out, int cap, int cols, cudaStream_t stream) {
   if (n > MAX_PEERS || cols % 8) return -1;
   int grid = (cap + 7) / 8;
-  if (grid > 148 * 8) grid = 148 * 8;
+  if (grid > 148 * 3) grid = 148 * 3;  // leaves room for a GEMM CTA on every SM
   if (grid <= 0) return 0;
-  ep_gather_rows_kernel<<<grid, 256, 0, stream>>>(to_peers(peer_x, n), T, src_of, meta, static_cast<__nv_bfloat16*>(out),
-                                                  cap, cols);
+  ep_gather_rows_kernel<<<grid, 256, 0, stream>>>(to_peers(peer_x, n), T, src_of, meta, blk_range,
+                                                  static_cast<__nv_bfloat16*>(out), cap, cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -293,7 +321,8 @@ extern "C" int olb_ep_combine(const void* const* peer_y, int n, const int* rows,
                               int E_loc, void* out, int cols, cudaStream_t stream) {
   if (n > MAX_PEERS || cols % 8 || K > 32) return -1;
   if (T <= 0) return 0;
-  const int grid = T < 148 * 16 ? T : 148 * 16;
+  // at most three 256-thread blocks per SM: leaves room for a GEMM CTA running on the main stream meanwhile
+  const int grid = T < 148 * 3 ? T : 148 * 3;
   ep_combine_kernel<<<grid, 256, 0, stream>>>(to_peers(peer_y, n), rows, idx, T, K, E_loc,
                                               static_cast<__nv_bfloat16*>(out), cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;

@@ -60,6 +60,7 @@ struct GemmParams {
   int a_peer_rows;             // > 0: A is row-partitioned over peers, this many outer rows per peer (PeerArg maps)
   int b_peer_rows;             // > 0: same for B
   int m_rotate_blocks;         // row-block rotation of the tile order (start on the rows this GPU owns)
+  const int* blk_range;        // ragged-M only, optional (device): restrict to row blocks [blk_range[0], blk_range[1])
   int* status;
 };
 
@@ -92,7 +93,7 @@ struct TileInfo {
 
 // Map a linear tile id to its coordinates.  Returns false when `t` is past the last tile.
 template <int BLOCK_N>
-__device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int num_m_blocks, TileInfo& ti) {
+__device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int num_m_blocks, int blk0, TileInfo& ti) {
   const int num_n_blocks = (p.N + BLOCK_N - 1) / BLOCK_N;
   if (p.mode == OLB_GEMM_RAGGED_K) {
     const int per_expert = num_m_blocks * num_n_blocks;
@@ -118,6 +119,7 @@ __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int num_m_b
   int m_blk = first_m + r % rows_in_band;
   if (p.m_rotate_blocks) m_blk = (m_blk + p.m_rotate_blocks) % num_m_blocks;
   const int n_blk = r / rows_in_band;
+  m_blk += blk0;  // first row block of the requested range
   ti.m0 = m_blk * BLOCK_M;
   ti.n0 = n_blk * BLOCK_N;
   ti.kb_begin = 0;
@@ -173,9 +175,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  int num_m_blocks;
+  int num_m_blocks, blk0 = 0;
   if (p.mode == OLB_GEMM_RAGGED_M) {
     num_m_blocks = min(p.meta[0], (p.M + BLOCK_M - 1) / BLOCK_M);
+    if (p.blk_range) {
+      blk0 = p.blk_range[0];
+      num_m_blocks = max(0, min(num_m_blocks, p.blk_range[1]) - blk0);
+    }
   } else {
     num_m_blocks = (p.M + BLOCK_M - 1) / BLOCK_M;
   }
@@ -187,7 +193,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       TileInfo ti;
-      for (int t = blockIdx.x; ok && get_tile<BLOCK_N>(p, t, num_m_blocks, ti); t += gridDim.x) {
+      for (int t = blockIdx.x; ok && get_tile<BLOCK_N>(p, t, num_m_blocks, blk0, ti); t += gridDim.x) {
         for (int kb = ti.kb_begin; kb < ti.kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) {
             ok = false;
@@ -257,7 +263,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t acc_phase = 0;
       bool ok = true;
       TileInfo ti;
-      for (int t = blockIdx.x; ok && get_tile<BLOCK_N>(p, t, num_m_blocks, ti); t += gridDim.x) {
+      for (int t = blockIdx.x; ok && get_tile<BLOCK_N>(p, t, num_m_blocks, blk0, ti); t += gridDim.x) {
         if (ti.kb_end <= ti.kb_begin) continue;  // empty expert: the epilogue writes zeros
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, p.status, ST_TIMEOUT_ACC_EMPTY, abort_flag)) break;
         tc_fence_after();
@@ -298,7 +304,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     int acc = 0;
     uint32_t acc_phase = 0;
     TileInfo ti;
-    for (int t = blockIdx.x; get_tile<BLOCK_N>(p, t, num_m_blocks, ti); t += gridDim.x) {
+    for (int t = blockIdx.x; get_tile<BLOCK_N>(p, t, num_m_blocks, blk0, ti); t += gridDim.x) {
       const int row = ti.m0 + lane_group * 32 + lane;
       const bool row_ok = row < p.M;
       const bool has_k = ti.kb_end > ti.kb_begin;
@@ -555,6 +561,7 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   p.a_peer_rows = 0;
   p.b_peer_rows = 0;
   p.m_rotate_blocks = 0;
+  p.blk_range = d->mode == OLB_GEMM_RAGGED_M ? d->blk_range : nullptr;
   p.status = d->status;
   const int sms = d->max_ctas > 0 && d->max_ctas < num_sms ? d->max_ctas : num_sms;
   if (d->n_peers > 0) {

@@ -40,6 +40,7 @@ typedef struct {
   int a_peer_rows;
   const void* const* B_peers;
   int b_peer_rows;
+  const int* blk_range;      // RAGGED_M, optional (device memory): only row blocks [blk_range[0], blk_range[1])
 } olb_gemm_desc;
 
 int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream);
@@ -167,8 +168,8 @@ int olb_adamw_step(const void* grad, int grad_fp32, float* master, float* m, flo
 int olb_symm_barrier(void* const* pads, int my_rank, int n, int channel, unsigned epoch, int* status,
                      cudaStream_t stream);
 // out[row,:] = peer_x[g / T][g % T, :], g = src_of[row] (global token id), rows < meta[0]*128; padding -> 0.
-int olb_ep_gather_rows(const void* const* peer_x, int n, int T, const int* src_of, const int* meta, void* out, int cap,
-                       int cols, cudaStream_t stream);
+int olb_ep_gather_rows(const void* const* peer_x, int n, int T, const int* src_of, const int* meta,
+                       const int* blk_range, void* out, int cap, int cols, cudaStream_t stream);
 // rows[t,k] = peer_row_of[d][(my_rank*T+t)*K+k], d = idx[t,k] / E_loc  (row of each of my pairs on its owner).
 int olb_ep_resolve_rows(const void* const* peer_row_of, int n, const int* idx, int my_rank, int T, int K, int E_loc,
                         int* rows, cudaStream_t stream);

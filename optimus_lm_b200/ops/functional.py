@@ -54,16 +54,17 @@ def _kernel_ok(*ts) -> bool:
 def gemm(a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, *, a_mn_major=False, b_mn_major=False,
          out: Optional[torch.Tensor] = None, accumulate=False, mode=GEMM_DENSE, meta=None, num_experts=1,
          b_expert_rows=0, c_expert_stride=0, out_dtype=torch.bfloat16, block_n=0, max_ctas=0,
-         b2: Optional[torch.Tensor] = None, k_split=0) -> torch.Tensor:
+         b2: Optional[torch.Tensor] = None, k_split=0, blk_range: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Raw tcgen05 GEMM on 2D bf16 views (unit inner stride). See csrc/olb_api.h.  With ``b2`` (same
     layout as ``b``) the K range ``[k_split, K)`` is read from ``b2``: one launch for
-    ``a[:, :k_split] @ b + a[:, k_split:] @ b2``."""
+    ``a[:, :k_split] @ b + a[:, k_split:] @ b2``.  ``blk_range`` (ragged-M, two int32 on the device) restricts the
+    launch to the 128-row blocks ``[blk_range[0], blk_range[1])``."""
     if out is None:
         assert not accumulate
         shape = (num_experts, M, N) if mode == GEMM_RAGGED_K else (M, N)
         out = torch.empty(shape, dtype=out_dtype, device=a.device)
     extension().gemm(a, b, out, M, N, K, a_mn_major, b_mn_major, accumulate, mode, meta, num_experts,
-                     b_expert_rows, c_expert_stride, status_word(a.device), block_n, max_ctas, b2, k_split)
+                     b_expert_rows, c_expert_stride, status_word(a.device), block_n, max_ctas, b2, k_split, blk_range)
     return out
 
 
@@ -541,6 +542,9 @@ def moe_capacity_rows(T: int, K: int, E_loc: int, ep: int = 1, capacity_factor: 
     return ((rows + 127) // 128) * 128
 
 
+_PART_CUTS = {}
+
+
 class MoEIndex:
     """Device-resident permutation of routed (token, k) pairs into expert-grouped rows."""
 
@@ -561,18 +565,31 @@ class MoEIndex:
         C.moe_build_index(topk_idx.contiguous(), e_start, E_loc, cap, ws, self.row_of, self.src_of, self.k_of,
                           self.meta, self.offsets, self.counts, status_word(dev))
 
+    def part_ranges(self, parts: int) -> torch.Tensor:
+        """``[parts, 2]`` int32 (device): first and one-past-last 128-row block of each group of consecutive local
+        experts.  Lets a consumer start on the first experts' rows while the rest is still in flight."""
+        parts = max(1, min(parts, self.E_loc))
+        key = (self.E_loc, parts, self.offsets.device)
+        cuts = _PART_CUTS.get(key)
+        if cuts is None:  # built once: a host-to-device copy here would stall the launch queue every layer
+            cuts = _PART_CUTS[key] = torch.tensor([(p * self.E_loc) // parts for p in range(parts + 1)],
+                                                  device=self.offsets.device)
+        b = torch.div(self.offsets[cuts], 128, rounding_mode="floor").to(torch.int32)
+        return torch.stack([b[:-1], b[1:]], dim=1).contiguous()
 
-def grouped_linear_fwd(xp, w, index: MoEIndex, out=None):
+
+def grouped_linear_fwd(xp, w, index: MoEIndex, out=None, blk_range=None):
     """``y[rows of e] = xp[rows of e] @ w[e].T`` for merged weights ``w [E, N, K]``."""
     E, N, K = w.shape
-    return gemm(xp, w.view(E * N, K), index.cap, N, K, mode=GEMM_RAGGED_M, meta=index.meta, b_expert_rows=N, out=out)
+    return gemm(xp, w.view(E * N, K), index.cap, N, K, mode=GEMM_RAGGED_M, meta=index.meta, b_expert_rows=N, out=out,
+                blk_range=blk_range)
 
 
-def grouped_linear_dgrad(dy, w, index: MoEIndex, out=None, accumulate=False):
+def grouped_linear_dgrad(dy, w, index: MoEIndex, out=None, accumulate=False, blk_range=None):
     """``dx[rows of e] (+)= dy[rows of e] @ w[e]``."""
     E, N, K = w.shape
     return gemm(dy, w.view(E * N, K), index.cap, K, N, b_mn_major=True, mode=GEMM_RAGGED_M, meta=index.meta,
-                b_expert_rows=N, out=out, accumulate=accumulate)
+                b_expert_rows=N, out=out, accumulate=accumulate, blk_range=blk_range)
 
 
 def grouped_linear_dgrad_pair(dh, w1, w2, index: MoEIndex, out=None):

@@ -20,6 +20,8 @@ reuse; all waits are bounded.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -32,6 +34,34 @@ def _all_gather_rows(t: torch.Tensor, n: int, group) -> torch.Tensor:
     out = torch.empty((n * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
     dist.all_gather_into_tensor(out, t.contiguous(), group=group)
     return out
+
+
+def _parts(E_loc: int) -> int:
+    """Groups of local experts the dispatch is pipelined over (OLB_EP_PARTS, default 4, 1 = no pipelining)."""
+    return max(1, min(int(os.environ.get("OLB_EP_PARTS", "4")), E_loc))
+
+
+def _pipelined_gather(sg: SymmGroup, peer_ptrs, T, index, out, parts: int):
+    """Pull the routed rows of ``out`` from their owners in ``parts`` groups of experts on the side stream.
+    Returns ``(ranges, events)``: the consumer waits for ``events[p]`` on its own stream before touching the row
+    blocks ``ranges[p]``, so the first experts' GEMMs run while the later experts' rows still cross NVLink."""
+    C = extension()
+    if parts <= 1:
+        C.ep_gather_rows(peer_ptrs, T, index.src_of, index.meta, out, None)
+        return None, None
+    ranges = index.part_ranges(parts)
+    main, side = torch.cuda.current_stream(), sg.side_stream()
+    start = torch.cuda.Event()
+    start.record(main)
+    events = []
+    with torch.cuda.stream(side):
+        side.wait_event(start)
+        for p in range(parts):
+            C.ep_gather_rows(peer_ptrs, T, index.src_of, index.meta, out, ranges[p])
+            ev = torch.cuda.Event()
+            ev.record(side)
+            events.append(ev)
+    return ranges, events
 
 
 class _FusedEPMoEFn(torch.autograd.Function):
@@ -54,10 +84,16 @@ class _FusedEPMoEFn(torch.autograd.Function):
 
         index = OF.MoEIndex(idx_all, e_start, E_loc, cap)
         xp = torch.empty((cap, H), dtype=x.dtype, device=x.device)
-        C.ep_gather_rows(xs.ptrs, T, index.src_of, index.meta, xp)
         h = torch.empty((cap, 2 * I), dtype=x.dtype, device=x.device)
-        OF.grouped_linear_fwd(xp, wg, index, out=h[:, :I])
-        OF.grouped_linear_fwd(xp, wu, index, out=h[:, I:])
+        ranges, events = _pipelined_gather(sg, xs.ptrs, T, index, xp, _parts(E_loc))
+        main = torch.cuda.current_stream()
+        for p in range(len(events) if events else 1):
+            r = None
+            if events:
+                main.wait_event(events[p])
+                r = ranges[p]
+            OF.grouped_linear_fwd(xp, wg, index, out=h[:, :I], blk_range=r)
+            OF.grouped_linear_fwd(xp, wu, index, out=h[:, I:], blk_range=r)
         act = torch.empty((cap, I), dtype=x.dtype, device=x.device)
         C.swiglu_rowscale_fwd(h[:, :I], h[:, I:], index.src_of, index.k_of, w_all, index.meta, act)
         ys = sg.named("ep_out", (cap, H), x.dtype)
@@ -89,10 +125,17 @@ class _FusedEPMoEFn(torch.autograd.Function):
         sg.barrier(2)
 
         dyp = torch.empty((cap, H), dtype=dout.dtype, device=dout.device)
-        C.ep_gather_rows(ds.ptrs, T, index.src_of, index.meta, dyp)
+        dact = torch.empty((cap, I), dtype=dout.dtype, device=dout.device)
         hg, hu, hd = ctx.holders
         # Critical path first: the input-gradient chain up to the rows the other ranks will pull ...
-        dact = OF.grouped_linear_dgrad(dyp, wd, index)
+        ranges, events = _pipelined_gather(sg, ds.ptrs, T, index, dyp, _parts(E_loc))
+        main = torch.cuda.current_stream()
+        for p in range(len(events) if events else 1):
+            r = None
+            if events:
+                main.wait_event(events[p])
+                r = ranges[p]
+            OF.grouped_linear_dgrad(dyp, wd, index, out=dact, blk_range=r)
         dh = torch.empty_like(h)
         dwt = sg.named("ep_dw", (n * T, K), torch.float32)
         dwt.local.zero_()
