@@ -367,3 +367,19 @@ def test_adamw_and_sumsq():
     assert abs(s.item() - (g.float() * 0.5).pow(2).sum().item()) / s.item() < 1e-5
     s2 = OF.sum_of_squares(g, 0.5)
     assert torch.equal(s, s2)
+
+
+def test_kernels_package_entry_points():
+    """The reference-named GEMM wrappers: NN, NT, TN, accumulate."""
+    import optimus_lm_b200.kernels as K
+    a, b_nk, b_kn = bf(256, 192, seed=1), bf(320, 192, seed=2), bf(192, 320, seed=3)
+    assert rel_err(K.gemm(a, b_kn), a.float() @ b_kn.float()) < 1e-2
+    assert rel_err(K.gemm_trans(a, b_nk), a.float() @ b_nk.float().t()) < 1e-2
+    assert rel_err(K.linear_forward(a, b_nk), a.float() @ b_nk.float().t()) < 1e-2
+    dy = bf(256, 320, seed=4)
+    dx = K.linear_backward_input(dy, b_nk)
+    assert rel_err(dx, dy.float() @ b_nk.float()) < 1e-2
+    base = dx.clone()
+    K.linear_backward_input_add(dy, b_nk, dx)
+    assert rel_err(dx, 2 * base.float()) < 1e-2
+    assert rel_err(K.linear_backward_weight(dy, a), dy.float().t() @ a.float()) < 1e-2
