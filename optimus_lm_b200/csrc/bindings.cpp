@@ -70,6 +70,29 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, int64_t M, in
   check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16");
 }
 
+void embedding_fwd(const at::Tensor& ids, const at::Tensor& w, at::Tensor& out, int64_t v_start) {
+  CHECK_CUDA_BF16(w);
+  TORCH_CHECK(ids.scalar_type() == at::kLong && ids.is_contiguous() && w.is_contiguous() && out.is_contiguous());
+  c10::cuda::CUDAGuard guard(w.device());
+  check(olb_embedding_fwd(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), w.data_ptr(), out.data_ptr(),
+                          static_cast<int>(ids.numel()), static_cast<int>(w.size(1)), static_cast<int>(v_start),
+                          static_cast<int>(w.size(0)), cur_stream()),
+        "olb_embedding_fwd");
+}
+
+void embedding_bwd(const at::Tensor& sorted_ids, const at::Tensor& perm, const at::Tensor& dy, at::Tensor& dw,
+                   int64_t v_start, int64_t padding_idx, bool accumulate) {
+  CHECK_CUDA_BF16(dy);
+  TORCH_CHECK(sorted_ids.scalar_type() == at::kLong && perm.scalar_type() == at::kLong && dy.is_contiguous() &&
+              dw.is_contiguous() && dw.scalar_type() == at::kBFloat16);
+  c10::cuda::CUDAGuard guard(dy.device());
+  check(olb_embedding_bwd(reinterpret_cast<const long long*>(sorted_ids.data_ptr<int64_t>()),
+                          reinterpret_cast<const long long*>(perm.data_ptr<int64_t>()), dy.data_ptr(), dw.data_ptr(),
+                          static_cast<int>(sorted_ids.numel()), static_cast<int>(dw.size(1)), static_cast<int>(v_start),
+                          static_cast<int>(dw.size(0)), padding_idx, accumulate, cur_stream()),
+        "olb_embedding_bwd");
+}
+
 void rmsnorm_fwd(const at::Tensor& x, const c10::optional<at::Tensor>& w, at::Tensor& y, at::Tensor& rstd, double eps) {
   CHECK_CUDA_BF16(x);
   c10::cuda::CUDAGuard guard(x.device());
@@ -350,6 +373,8 @@ void register_comm(pybind11::module& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd", &embedding_bwd);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("rmsnorm_bwd_blocks", &rmsnorm_bwd_blocks);

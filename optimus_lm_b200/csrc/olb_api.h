@@ -220,6 +220,15 @@ typedef struct {
 } olb_attn_bwd_desc;
 int olb_attn_bwd(const olb_attn_bwd_desc* d, cudaStream_t stream);
 
+// ---------------------------------------------------------------- embedding (embedding.cu)
+// out[t,:] = W[ids[t] - v_start,:] for ids inside [v_start, v_start + rows), else 0.  bf16, cols % 8 == 0.
+int olb_embedding_fwd(const long long* ids, const void* w, void* out, int tokens, int cols, int v_start, int rows,
+                      cudaStream_t stream);
+// dW[v,:] (+)= sum of dy[perm[j],:] over the run of sorted_ids equal to v (ids sorted stably, perm = source token).
+// Rows of dW that no token hits are left untouched.  padding_idx (or -1): that id gets no gradient.
+int olb_embedding_bwd(const long long* sorted_ids, const long long* perm, const void* dy, void* dw, int tokens, int cols,
+                      int v_start, int rows, long long padding_idx, int accumulate, cudaStream_t stream);
+
 // ---------------------------------------------------------------- timing (event_profiler.cu)
 // Writes %globaltimer (ns) of the moment the kernel runs on `stream` into slot[0].
 int olb_stamp_globaltimer(unsigned long long* slot, cudaStream_t stream);

@@ -190,7 +190,7 @@ class ParallelDenseModel(nn.Module):
         self.rotary_emb = RotaryEmbedding(config)
 
     def forward(self, input_ids, vp_ind=0):
-        hidden_states = self.embed_tokens(input_ids) if vp_ind == 0 else input_ids
+        hidden_states = OF.embed(self.embed_tokens, input_ids) if vp_ind == 0 else input_ids
         pos = self.rotary_emb.table(hidden_states.size(1), hidden_states.device)
         LV = self.num_hidden_layers_per_vpp_rank
         for i in range(vp_ind * LV, (vp_ind + 1) * LV):

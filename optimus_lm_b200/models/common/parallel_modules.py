@@ -25,12 +25,11 @@ class ParallelEmbedding(nn.Module):
             self.local_padding_idx = padding_idx - self.start_embedding_id
 
     def forward(self, input):
+        from ...ops import functional as OF
         if self.tensor_parallelism == 1:
-            return nn.functional.embedding(input, self.weight, self.local_padding_idx)
-        outside = (input < self.start_embedding_id) | (input >= self.end_embedding_id)
-        local = (input - self.start_embedding_id).masked_fill(outside, 0)
-        out = nn.functional.embedding(local, self.weight, self.local_padding_idx)
-        out = out.masked_fill(outside.unsqueeze(-1), 0)
+            return OF.embedding(input, self.weight, self.local_padding_idx)
+        # rows of other ranks' vocabulary ranges come back as zeros; the all-reduce assembles the lookup
+        out = OF.embedding(input, self.weight, self.local_padding_idx, v_start=self.start_embedding_id, masked=True)
         return forward_allreduce_backward_identity.apply(out, self.group)
 
     @torch.no_grad()

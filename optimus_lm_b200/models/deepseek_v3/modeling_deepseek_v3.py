@@ -413,7 +413,7 @@ class DeepseekV3ParallelModel(nn.Module):
         self.ckpt_norm = bool(lvl & 4)
 
     def forward(self, input_ids):
-        hidden_states = self.embed_tokens(input_ids)
+        hidden_states = OF.embed(self.embed_tokens, input_ids)
         pos = self.rotary_emb.table(hidden_states.size(1), hidden_states.device)
         for layer in self.layers:
             hidden_states = layer(hidden_states, pos)

@@ -172,7 +172,7 @@ class OlmoeParallelModel(nn.Module):
     def forward(self, inputs, vp_ind=None):
         first_chunk = vp_ind is None or vp_ind == 0
         last_chunk = vp_ind is None or vp_ind == self.VPP - 1
-        hidden_states = self.embed_tokens(inputs) if first_chunk else inputs
+        hidden_states = OF.embed(self.embed_tokens, inputs) if first_chunk else inputs
         S = hidden_states.size(1)
         position_embeddings = self.rotary_emb.table(S, hidden_states.device)
 

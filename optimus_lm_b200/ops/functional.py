@@ -162,6 +162,62 @@ def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return F.linear(x, w)
 
 
+# ------------------------------------------------------------------------------------ embedding
+class _EmbeddingFn(torch.autograd.Function):
+    """Row lookup with an optional vocabulary range (rows outside ``[v_start, v_start + rows)`` give zeros) and a
+    deterministic backward that accumulates straight into the weight's gradient buffer when it has one."""
+
+    @staticmethod
+    def forward(ctx, ids, w, v_start, padding_idx, holder):
+        C = extension()
+        flat = ids.reshape(-1).contiguous()
+        out = torch.empty((flat.numel(), w.shape[1]), dtype=w.dtype, device=w.device)
+        C.embedding_fwd(flat, w, out, v_start)
+        ctx.save_for_backward(flat)
+        ctx.misc = (v_start, -1 if padding_idx is None else int(padding_idx) + v_start, holder, tuple(w.shape))
+        return out.view(*ids.shape, w.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        (flat,) = ctx.saved_tensors
+        v_start, pad, holder, wshape = ctx.misc
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        sorted_ids, perm = torch.sort(flat, stable=True)
+        C = extension()
+        if holder is not None:
+            if not holder.ready:
+                holder.buf.zero_()
+                holder.ready = True
+            C.embedding_bwd(sorted_ids, perm, dy2, holder.buf, v_start, pad, True)
+            return None, None, None, None, None
+        dw = torch.zeros(wshape, dtype=dy.dtype, device=dy.device)
+        C.embedding_bwd(sorted_ids, perm, dy2, dw, v_start, pad, False)
+        return None, dw, None, None, None
+
+
+def embedding(ids: torch.Tensor, weight: torch.Tensor, padding_idx=None, v_start: int = 0, masked: bool = False) -> torch.Tensor:
+    """``weight[ids - v_start]`` (zeros for ids outside this rank's vocabulary range; ``padding_idx`` is local to the
+    weight and receives no gradient; ``masked`` says that ids beyond the weight's rows may occur).  Reference: ``F.embedding`` / ``ParallelEmbedding``
+    (optimus/models/common/parallel_modules.py:32-45)."""
+    if _kernel_ok(weight) and ids.is_cuda and ids.dtype == torch.long and weight.is_contiguous() \
+            and weight.shape[1] % 8 == 0:
+        return _EmbeddingFn.apply(ids, weight, v_start, padding_idx, _holder(weight))
+    if v_start == 0 and not masked:
+        return F.embedding(ids, weight, padding_idx)
+    local = ids - v_start
+    outside = (local < 0) | (local >= weight.shape[0])
+    out = F.embedding(local.masked_fill(outside, 0), weight, padding_idx)
+    return out.masked_fill(outside.unsqueeze(-1), 0.0)
+
+
+def embed(module, ids):
+    """Call an embedding module: ``nn.Embedding`` goes through ``embedding`` (kernel path on bf16 CUDA), anything
+    else (``ParallelEmbedding``, ``nn.Identity`` on non-first pipeline stages) is called as is."""
+    if isinstance(module, torch.nn.Embedding):
+        return embedding(ids, module.weight, module.padding_idx)
+    return module(ids)
+
+
 # ------------------------------------------------------------------------------------ norms
 def rms_norm_reference(x, weight, eps):
     """Reference RMSNorm (optimus/models/olmoe/modeling_olmoe.py:93-104)."""

@@ -383,3 +383,35 @@ def test_kernels_package_entry_points():
     K.linear_backward_input_add(dy, b_nk, dx)
     assert rel_err(dx, 2 * base.float()) < 1e-2
     assert rel_err(K.linear_backward_weight(dy, a), dy.float().t() @ a.float()) < 1e-2
+
+
+@pytest.mark.parametrize("v_start,rows", [(0, 1000), (300, 400)])
+def test_embedding_fwd_bwd(v_start, rows):
+    V, H, T = 1000, 256, 3000
+    g = torch.Generator(device="cuda").manual_seed(0)
+    ids = torch.randint(0, V, (3, T // 3), device="cuda", generator=g)
+    ids[0, :50] = 7 + v_start          # a long run of one id
+    w = bf(rows, H, seed=1).requires_grad_()
+    pad = 5
+    y = OF.embedding(ids, w, padding_idx=pad, v_start=v_start)
+    local = ids - v_start
+    inside = (local >= 0) & (local < rows)
+    ref = torch.where(inside[..., None], w.detach().float()[local.clamp(0, rows - 1)], torch.zeros(1, device="cuda"))
+    assert torch.equal(y.float(), ref)
+    dy = bf(3, T // 3, H, seed=2)
+    y.backward(dy)
+    want = torch.zeros(rows, H, device="cuda")
+    sel = inside & (local != pad)
+    want.index_add_(0, local[sel], dy.float()[sel])
+    assert rel_err(w.grad, want) < 1e-2
+    assert w.grad[pad].abs().max().item() == 0
+    # deterministic, and accumulation into an existing gradient buffer
+    g1 = w.grad.clone()
+    w.grad = None
+    OF.embedding(ids, w, padding_idx=pad, v_start=v_start).backward(dy)
+    assert torch.equal(w.grad, g1)
+    h = OF.DirectGrad(torch.zeros_like(w))
+    w._olb_direct = h
+    for _ in range(2):
+        OF.embedding(ids, w, padding_idx=pad, v_start=v_start).backward(dy)
+    assert rel_err(h.buf, 2 * want) < 1e-2
