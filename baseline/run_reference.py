@@ -36,7 +36,7 @@ def _unavailable(why):
 
 def run_reference(opts):
     if not os.path.isdir(os.path.join(REF, "optimus")):
-        _unavailable("baseline/_ref is missing (offline install of /root/reference was not done on this machine)")
+        _unavailable("baseline/_ref is missing (the offline install of the reference was not done on this machine)")
         return
     try:
         _run(opts)

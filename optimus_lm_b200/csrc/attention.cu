@@ -49,7 +49,7 @@ struct AttnFwdSmem {
   static constexpr int OFF_PAIR = OFF_V + VS * V_BYTES;  // row statistics exchanged between warp pairs
   static constexpr int OFF_BAR = OFF_PAIR + 2 * 2 * ATT_BQ * 4;
   static constexpr int TOTAL = OFF_BAR + 256;  // no alignment slack: the kernel checks that the window is 1024-aligned
-  static_assert(TOTAL <= 232448, "shared memory budget");
+  static_assert(TOTAL <= 232448, "shared memory size");
 };
 
 struct AttnFwdParams {
@@ -72,7 +72,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   using L = AttnFwdSmem<D, DV, BKV>;
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t TM_S0 = 0, TM_S1 = BKV, TM_O = 2 * BKV;  // column offsets
-  static_assert(2 * BKV + DV <= 512, "TMEM budget");
+  static_assert(2 * BKV + DV <= 512, "TMEM columns");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);

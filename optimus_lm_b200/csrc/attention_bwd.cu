@@ -53,8 +53,8 @@ struct BwdCfg {
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
   static constexpr uint32_t TM_X = 0, TM_Y = BW_T * NB, TM_ACC1 = 2 * BW_T * NB;
   static constexpr uint32_t TM_ACC2 = KV_MODE ? TM_ACC1 + 128 : TM_ACC1;
-  static_assert(TM_ACC2 + D1 <= 512 && D2 <= 128, "TMEM budget");
-  static_assert(TOTAL <= 232448, "shared memory budget");
+  static_assert(TM_ACC2 + D1 <= 512 && D2 <= 128, "TMEM columns");
+  static_assert(TOTAL <= 232448, "shared memory size");
 };
 
 struct AttnBwdParams {

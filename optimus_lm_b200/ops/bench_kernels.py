@@ -111,6 +111,32 @@ def profile_case(name: str, launches: int = 4):
         o = OA.flash_attention(q, k, v)
         do = torch.randn_like(o)
         fn = lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True)
+    elif name == "ep":
+        # The expert-parallel MoE function with a process group of ONE rank: the peer-memory kernels (row pulls,
+        # combine, device barrier) run with this GPU as their only "peer", so that a single-process profiler can
+        # look at them.  NVLink does not appear in such a capture; the multi-GPU timings are taken with CUDA events.
+        import os
+        import torch.distributed as dist
+        from ..parallel.ep_alltoall import _FusedEPMoEFn
+        from ..parallel.symm import SymmGroup
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29577")
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+        sg = SymmGroup.get(dist.group.WORLD)
+        T, E, K, H, I = 16384, 64, 8, 2048, 1024
+        x = torch.randn(T, H, device="cuda").to(torch.bfloat16).requires_grad_()
+        idx = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(T)]).to(torch.int32)
+        tw = torch.rand(T, K, device="cuda")
+        wg = (torch.randn(E, I, H, device="cuda") * 0.02).to(torch.bfloat16).requires_grad_()
+        wu = (torch.randn(E, I, H, device="cuda") * 0.02).to(torch.bfloat16).requires_grad_()
+        wd = (torch.randn(E, H, I, device="cuda") * 0.02).to(torch.bfloat16).requires_grad_()
+        cap = OF.moe_capacity_rows(T, K, E)
+        go = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+
+        def fn():
+            y = _FusedEPMoEFn.apply(x, tw, idx, wg, wu, wd, sg, 0, cap)
+            y.backward(go)
     elif name == "rmsnorm-bwd":
         x = torch.randn(16384, 2048, device="cuda").to(torch.bfloat16).requires_grad_()
         w = torch.ones(2048, device="cuda", dtype=torch.bfloat16, requires_grad=True)
