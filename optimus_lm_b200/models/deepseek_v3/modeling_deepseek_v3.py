@@ -333,8 +333,7 @@ class DeepseekV3ParallelAttention(nn.Module):
         H, dn, dr, dv = self.num_heads, self.qk_nope_head_dim, self.qk_rope_head_dim, self.v_head_dim
         cos, sin = position_embeddings
         q = OF.linear(self.q_a_layernorm(OF.linear(hidden_states, self.q_a_proj.weight)), self.q_b_proj.weight)
-        q = q.view(B, S, H, dn + dr)
-        q = OF.rope(q, cos, sin, rot_offset=dn, rot_dim=dr, interleaved=True)
+        q = OF.rope(q, cos, sin, rot_offset=dn, rot_dim=dr, interleaved=True, heads=H).view(B, S, H, dn + dr)
 
         ckv = OF.linear(hidden_states, self.kv_a_proj_with_mqa.weight)
         k_lat, k_rot = ckv[..., :self.kv_lora_rank], ckv[..., self.kv_lora_rank:]

@@ -130,11 +130,14 @@ class _LinearFn(torch.autograd.Function):
         x2 = _as_2d(x)
         M, K = x2.shape
         N = w.shape[0]
-        y = gemm(x2, w, M, N, K)
+        # the result is allocated in its final shape: a view made inside the function could not be modified in
+        # place by a later op (the in-place RoPE kernel works on projection outputs)
+        y = torch.empty((*x.shape[:-1], N), dtype=x.dtype, device=x.device)
+        gemm(x2, w, M, N, K, out=y.view(M, N))
         ctx.save_for_backward(x2, w)
         ctx.x_shape = x.shape
         ctx.holder = holder
-        return y.view(*x.shape[:-1], N)
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -171,11 +174,11 @@ class _EmbeddingFn(torch.autograd.Function):
     def forward(ctx, ids, w, v_start, padding_idx, holder):
         C = extension()
         flat = ids.reshape(-1).contiguous()
-        out = torch.empty((flat.numel(), w.shape[1]), dtype=w.dtype, device=w.device)
-        C.embedding_fwd(flat, w, out, v_start)
+        out = torch.empty((*ids.shape, w.shape[1]), dtype=w.dtype, device=w.device)
+        C.embedding_fwd(flat, w, out.view(flat.numel(), w.shape[1]), v_start)
         ctx.save_for_backward(flat)
         ctx.misc = (v_start, -1 if padding_idx is None else int(padding_idx) + v_start, holder, tuple(w.shape))
-        return out.view(*ids.shape, w.shape[1])
+        return out
 
     @staticmethod
     def backward(ctx, dy):

@@ -55,3 +55,34 @@ def test_loss_decreases_on_a_repeated_batch():
     losses = [float(eng.train_step(ids).loss) for _ in range(8)]
     assert losses[-1] < losses[0] - 0.5, losses
     assert eng.check_device_status() == 0
+
+
+FAMILIES = [
+    ("allenai/OLMo-1B-hf--L2", dict(optimizer="shard")),
+    ("meta-llama/Llama-3.2-1B--L2", dict(optimizer="shard")),
+    ("deepseek-ai/DeepSeek-V3--L3-DL1-N16-K4-MI512-A16-SE1-H1024-I2048",
+     dict(optimizer="pgshard", use_fast_moe=True, use_merged_mlp_in_fast_moe=True)),
+]
+
+
+@pytest.mark.parametrize("model,kw", FAMILIES, ids=["olmo", "llama", "deepseek_v3"])
+def test_other_families_train_on_the_kernel_path(model, kw, monkeypatch):
+    """OLMo, Llama and DeepSeek-V3 (no QK-norm between projection and RoPE, MLA's partial interleaved RoPE) step
+    through the kernels, and their first loss equals the plain PyTorch path's on the same weights and batch."""
+    def first_losses(n):
+        torch.manual_seed(0)
+        eng = TrainEngine(EngineArgs(model_choice=model, dtype="bf16", batch_size=2, context_size=512, warmup_steps=0,
+                                     lr=1e-3, seed=0, **kw))
+        g = torch.Generator().manual_seed(5)
+        ids = torch.randint(0, 32000, (2, 512), generator=g)
+        out = [float(eng.train_step(ids).loss) for _ in range(n)]
+        assert eng.check_device_status() == 0
+        del eng
+        torch.cuda.empty_cache()
+        return out
+
+    ker = first_losses(4)
+    monkeypatch.setenv("OLB_DISABLE_KERNELS", "1")
+    ref = first_losses(1)
+    assert abs(ker[0] - ref[0]) < 3e-2, (ker, ref)
+    assert ker[-1] < ker[0] - 0.3, ker

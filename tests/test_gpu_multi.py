@@ -178,6 +178,36 @@ def w_tp_fused_mlp_vs_nccl(rank, world):
     assert OF.check_status("cuda") == 0
 
 
+LAYOUTS = {
+    "olmo_dp2_shard": ("allenai/OLMo-1B-hf--L2", dict(optimizer="shard", batch_size=4)),
+    "olmoe_pp2_1f1b": ("allenai/OLMoE-1B-7B-0924--L4-SH0.5-SI0.5",
+                       dict(optimizer="pgshard", pipeline_parallelism=2, pp_scheme="1f1b", batch_size=4,
+                            micro_batch_size=2, use_fast_moe=True, use_merged_mlp_in_fast_moe=True)),
+    "deepseek_v3_ep2": ("deepseek-ai/DeepSeek-V3--L3-DL1-N16-K4-MI512-A16-SE1-H1024-I2048",
+                        dict(optimizer="pgshard", expert_parallelism=2, batch_size=2, use_fast_moe=True,
+                             use_merged_mlp_in_fast_moe=True)),
+    "llama_tp2": ("meta-llama/Llama-3.2-1B--L2", dict(optimizer="shard", tensor_parallelism=2, batch_size=2)),
+}
+
+
+def w_family_layout(rank, world, name):
+    """A few optimizer steps of a model family in a two-GPU layout on the kernel path: the loss of a repeated
+    batch falls and no kernel reports an error."""
+    from optimus_lm_b200.engine import EngineArgs, TrainEngine
+    model, kw = LAYOUTS[name]
+    eng = TrainEngine(EngineArgs(model_choice=model, dtype="bf16", context_size=512, warmup_steps=0, lr=1e-3, seed=0, **kw))
+    g = torch.Generator().manual_seed(11 + 7 * eng.pmap.dp_ind)   # one batch per data-parallel replica
+    ids = torch.randint(0, 32000, (kw["batch_size"], 512), generator=g)
+    losses = []
+    for _ in range(5):
+        o = eng.train_step(ids.cuda())
+        if o.loss is not None:
+            losses.append(float(o.loss))
+    assert eng.check_device_status() == 0
+    if losses:       # ranks that are not on the last pipeline stage see no loss
+        assert all(l == l for l in losses) and losses[-1] < losses[0] - 0.3, losses
+
+
 # ----------------------------------------------------------------------------- tests
 def test_symm_barrier_and_pull_reduce():
     _run("w_symm_barrier_and_pull", 2)
@@ -193,3 +223,8 @@ def test_fused_engine_matches_nccl_engine():
 
 def test_tp_fused_mlp_matches_nccl_path():
     _run("w_tp_fused_mlp_vs_nccl", 2)
+
+
+@pytest.mark.parametrize("name", list(LAYOUTS))
+def test_model_families_in_two_gpu_layouts(name):
+    _run("w_family_layout", 2, name)
