@@ -82,48 +82,49 @@ void pull_reduce_rows(const std::vector<int64_t>& peer_partial, int64_t row0, in
         "olb_pull_reduce_rows");
 }
 
-// Dense GEMM C = A B^T-style (same operand conventions as `gemm`) whose A and/or B outer rows live on peer GPUs:
-// the all-gather of a tensor-parallel projection happens inside the GEMM's TMA loads.  `a_local` / `b_local` are
-// this GPU's slices (shape [rows_per_peer, inner]); the peers' slices are given by address.
-void gemm_peer(const at::Tensor& a_local, const std::vector<int64_t>& a_peers, const at::Tensor& b_local,
-               const std::vector<int64_t>& b_peers, at::Tensor& c, int64_t M, int64_t N, int64_t K, bool a_mn_major,
-               bool b_mn_major, int64_t my_peer, bool accumulate, const c10::optional<at::Tensor>& status) {
-  TORCH_CHECK(a_local.is_cuda() && a_local.scalar_type() == at::kBFloat16 && b_local.scalar_type() == at::kBFloat16,
+// All-gather -> GEMM in one kernel: C[M, N] = A B^T (or A B with `b_mn_major`), where A's rows are spread over the
+// GPUs of a group.  `a_gathered` [n * rows, K] is this GPU's gathered copy with its own block of rows filled in;
+// `a_peers[r]` is the address of peer r's slice [rows, K].  Extra warps of the GEMM copy the other slices into
+// `a_gathered` over NVLink while the tiles of the local rows run (csrc/gemm_tcgen05.cu: PeerArg<true>); when the
+// call returns to the stream, `a_gathered` is complete and later GEMMs read it locally.
+void gemm_peer(at::Tensor& a_gathered, const std::vector<int64_t>& a_peers, const at::Tensor& b, at::Tensor& c,
+               int64_t M, int64_t N, int64_t K, bool b_mn_major, int64_t my_peer, at::Tensor& flags,
+               const c10::optional<at::Tensor>& status) {
+  TORCH_CHECK(a_gathered.is_cuda() && a_gathered.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16,
               "bf16 CUDA operands expected");
-  TORCH_CHECK(a_local.dim() == 2 && b_local.dim() == 2 && a_local.stride(1) == 1 && b_local.stride(1) == 1);
-  c10::cuda::CUDAGuard guard(a_local.device());
+  TORCH_CHECK(a_gathered.dim() == 2 && b.dim() == 2 && a_gathered.stride(1) == 1 && b.stride(1) == 1);
+  const int64_t n = static_cast<int64_t>(a_peers.size());
+  TORCH_CHECK(n >= 1 && n <= 8 && M % n == 0 && a_gathered.size(0) >= M, "bad peer layout");
+  TORCH_CHECK(flags.scalar_type() == at::kInt && flags.is_contiguous() && flags.numel() >= (M + 127) / 128,
+              "flags: one int per 128-row block");
+  c10::cuda::CUDAGuard guard(a_gathered.device());
+  flags.zero_();
   auto ap = cptrs(a_peers);
-  auto bp = cptrs(b_peers);
   olb_gemm_desc d{};
-  d.A = a_local.data_ptr();
-  d.B = b_local.data_ptr();
+  d.A = a_gathered.data_ptr();
+  d.B = b.data_ptr();
   d.C = c.data_ptr();
-  d.lda = a_local.stride(0);
-  d.ldb = b_local.stride(0);
+  d.lda = a_gathered.stride(0);
+  d.ldb = b.stride(0);
   d.ldc = c.stride(-2);
-  d.a_rows = a_local.size(0);
-  d.b_rows = b_local.size(0);
+  d.a_rows = a_gathered.size(0);
+  d.b_rows = b.size(0);
   d.M = static_cast<int>(M);
   d.N = static_cast<int>(N);
   d.K = static_cast<int>(K);
-  d.a_mn_major = a_mn_major;
+  d.a_mn_major = false;
   d.b_mn_major = b_mn_major;
   d.mode = OLB_GEMM_DENSE;
   d.num_experts = 1;
-  d.accumulate = accumulate;
+  d.accumulate = false;
   d.out_fp32 = c.scalar_type() == at::kFloat;
   d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
-  d.n_peers = static_cast<int>(ap.empty() ? bp.size() : ap.size());
+  d.n_peers = static_cast<int>(n);
   d.my_peer = static_cast<int>(my_peer);
-  if (!ap.empty()) {
-    d.A_peers = ap.data();
-    d.a_peer_rows = static_cast<int>(a_local.size(0));
-  }
-  if (!bp.empty()) {
-    d.B_peers = bp.data();
-    d.b_peer_rows = static_cast<int>(b_local.size(0));
-  }
-  check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (peer operands)");
+  d.A_peers = ap.data();
+  d.a_peer_rows = static_cast<int>(M / n);
+  d.stage_flags = flags.data_ptr<int>();
+  check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (all-gather variant)");
 }
 
 int64_t rs_adamw_blocks(int64_t n) { return olb_rs_adamw_blocks(n); }

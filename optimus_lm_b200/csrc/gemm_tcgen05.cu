@@ -10,6 +10,8 @@
 //                two TMEM accumulators and commits to mbarriers
 //   * warps 2-5: epilogue - tcgen05.ld the accumulator (each warp owns 32 TMEM lanes),
 //                convert and store / accumulate into C while the next tile's main loop runs
+//   * warps 6-7: only in the all-gather variant (PeerArg<true>): copy the other GPUs' rows of A into the local
+//                gathered copy over NVLink while the tiles of the local rows are computed
 // Each operand may be K-major (rows of K contiguous) or MN-major (rows of M/N contiguous),
 // which gives NT / NN / TN / TT products without a transpose pass:
 //   forward   Y  = X  W^T    A K-major,  B K-major
@@ -57,24 +59,30 @@ struct GemmParams {
   int accumulate;              // C += A*B instead of C = A*B
   int out_fp32;
   int kb_split;                // > 0: k-blocks from this one on read B from the second tensor map (K-concatenated B)
-  int a_peer_rows;             // > 0: A is row-partitioned over peers, this many outer rows per peer (PeerArg maps)
-  int b_peer_rows;             // > 0: same for B
   int m_rotate_blocks;         // row-block rotation of the tile order (start on the rows this GPU owns)
   const int* blk_range;        // ragged-M only, optional (device): restrict to row blocks [blk_range[0], blk_range[1])
   int* status;
 };
 
-// Per-peer tensor maps of an operand whose outer rows live in the memories of up to 8 GPUs (plain TMA loads
-// from peer memory over NVLink, no multicast).
+// All-gather fused into the GEMM: the outer rows of A live in the memories of up to 8 GPUs.  Two extra warps per
+// CTA ("stagers") copy the other GPUs' rows into this GPU's gathered copy of A with plain loads over NVLink and
+// count the rows that have landed per 128-row block; the TMA producer waits (bounded) for a block's count before it
+// loads tiles of that block from the local copy.  A remote row crosses NVLink once, however many column tiles read it.
 template <bool PEER>
 struct PeerArg {
   char unused;
 };
 template <>
 struct PeerArg<true> {
-  CUtensorMap a[8];
-  CUtensorMap b[8];
+  const void* src[8];  // peer r's slice [rows, K], row stride ld
+  void* dst;           // this GPU's gathered copy [n * rows, K] (what tma_a covers), row stride ld
+  int* flags;          // rows landed per 128-row block of dst; zero at launch
+  long long ld;        // elements between rows
+  int rows;            // rows per peer, a multiple of BLOCK_M
+  int row_vecs;        // 16-byte vectors per row (K / 8)
+  int n, me;
 };
+constexpr int NUM_THREADS_STAGED = NUM_THREADS + 64;
 
 template <int BLOCK_N>
 struct SmemLayout {
@@ -129,7 +137,7 @@ __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int num_m_b
 }
 
 template <int BLOCK_N, bool PEER>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(PEER ? NUM_THREADS_STAGED : NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_b2, const __grid_constant__ PeerArg<PEER> peers,
                  const GemmParams p) {
@@ -194,6 +202,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       bool ok = true;
       TileInfo ti;
       for (int t = blockIdx.x; ok && get_tile<BLOCK_N>(p, t, num_m_blocks, blk0, ti); t += gridDim.x) {
+        if constexpr (PEER) {
+          // rows of another GPU: wait until the stagers have brought the whole row block into the local copy
+          if (ti.m0 / peers.rows != peers.me) {
+            const int* flag = peers.flags + ti.m0 / BLOCK_M;
+            const int need = min(BLOCK_M, p.M - ti.m0);
+            unsigned long long t0 = 0;
+            for (uint32_t it = 0; ld_acquire_gpu_s32(flag) < need; ++it) {
+              if ((it & 15u) == 15u) {
+                const unsigned long long now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                if (*abort_flag || now - t0 > WAIT_LIMIT_NS) {
+                  *abort_flag = 1;
+                  if (p.status) atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
+                  ok = false;
+                  break;
+                }
+              }
+            }
+            if (!ok) break;
+            fence_proxy_async_all();  // the rows were written by ordinary stores; the loads below are TMA
+          }
+        }
         for (int kb = ti.kb_begin; kb < ti.kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) {
             ok = false;
@@ -204,30 +234,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           const uint32_t fb = full_bar(stage);
           mbar_expect_tx(fb, L::STAGE_BYTES);
           const int k0 = kb * BLOCK_K;
-          const CUtensorMap* tma_a_sel = &tma_a;
-          int a_row = p.a_mn_major ? k0 : ti.m0;  // outer-row coordinate of A's 2D view
-          if constexpr (PEER) {
-            if (p.a_peer_rows > 0) {  // the outer rows of A are spread over the peers' memories
-              tma_a_sel = &peers.a[a_row / p.a_peer_rows];
-              a_row = a_row % p.a_peer_rows;
-            }
-          }
           if (!p.a_mn_major) {
-            tma_load_2d(sa, tma_a_sel, fb, k0, a_row);
+            tma_load_2d(sa, &tma_a, fb, k0, ti.m0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d(sa + j * MN_BOX_BYTES, tma_a_sel, fb, ti.m0 + j * 64, a_row);
+            for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d(sa + j * MN_BOX_BYTES, &tma_a, fb, ti.m0 + j * 64, k0);
           }
           // K-concatenated B: the second half of the K range comes from a second tensor of the same layout
           const bool second = p.kb_split > 0 && kb >= p.kb_split;
           const CUtensorMap* tmb = second ? &tma_b2 : &tma_b;
-          int kB = second ? k0 - p.kb_split * BLOCK_K : k0;
-          if constexpr (PEER) {
-            if (p.b_peer_rows > 0 && p.b_mn_major) {  // B's K rows are spread over the peers' memories
-              tmb = &peers.b[kB / p.b_peer_rows];
-              kB = kB % p.b_peer_rows;
-            }
-          }
+          const int kB = second ? k0 - p.kb_split * BLOCK_K : k0;
           if (!p.b_mn_major) {
             tma_load_2d(sb, tmb, fb, kB, ti.expert * p.b_expert_rows + ti.n0);
           } else {
@@ -298,7 +314,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, +32) belong to this warp
     int acc = 0;
@@ -386,6 +402,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
   }
 
+  if constexpr (PEER) {
+    if (warp >= 6) {
+      // ---------------------------------------------------------- stagers (warps 6..7): the all-gather
+      // Remote rows in the order the tiles need them: the peer after this one first.  Every CTA's stagers take rows
+      // of the same block at the same time, so blocks complete one after the other.  Nothing here waits.
+      const long long total = static_cast<long long>(peers.n - 1) * peers.rows;
+      for (long long u = blockIdx.x * 2 + (warp - 6); u < total; u += static_cast<long long>(gridDim.x) * 2) {
+        const int j = static_cast<int>(u / peers.rows);
+        const int r = static_cast<int>(u - static_cast<long long>(j) * peers.rows);
+        const int peer = (peers.me + 1 + j) % peers.n;
+        const long long drow = static_cast<long long>(peer) * peers.rows + r;
+        const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.src[peer]) + r * peers.ld * 2);
+        uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.dst) + drow * peers.ld * 2);
+        for (int c0 = 0; c0 < peers.row_vecs; c0 += 256) {
+          uint4 v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int c = c0 + i * 32 + lane;
+            if (c < peers.row_vecs) v[i] = s[c];
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int c = c0 + i * 32 + lane;
+            if (c < peers.row_vecs) d[c] = v[i];
+          }
+        }
+        fence_proxy_async_all();
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(peers.flags + drow / BLOCK_M, 1);
+      }
+    }
+  }
+
   tc_fence_before();
   __syncthreads();
   if (warp == 2) {
@@ -464,7 +514,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
   tiles = nm * nn * (p.mode == OLB_GEMM_RAGGED_K ? p.num_experts : 1);
   int grid = static_cast<int>(tiles < num_sms ? tiles : num_sms);
   if (grid <= 0) return 0;
-  gemm_bf16_kernel<BLOCK_N, PEER><<<grid, NUM_THREADS, L::TOTAL, stream>>>(ta, tb, tb2, peers, p);
+  gemm_bf16_kernel<BLOCK_N, PEER><<<grid, PEER ? NUM_THREADS_STAGED : NUM_THREADS, L::TOTAL, stream>>>(ta, tb, tb2, peers, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -558,42 +608,29 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   p.accumulate = d->accumulate;
   p.out_fp32 = d->out_fp32;
   p.kb_split = kb_split;
-  p.a_peer_rows = 0;
-  p.b_peer_rows = 0;
   p.m_rotate_blocks = 0;
   p.blk_range = d->mode == OLB_GEMM_RAGGED_M ? d->blk_range : nullptr;
   p.status = d->status;
   const int sms = d->max_ctas > 0 && d->max_ctas < num_sms ? d->max_ctas : num_sms;
   if (d->n_peers > 0) {
-    // Operand rows spread over peer GPUs (tensor-parallel all-gather fused into the GEMM's loads).
-    if (d->n_peers > 8 || d->mode != OLB_GEMM_DENSE || kb_split) return -14;
+    // All-gather of A's rows fused into the GEMM (see PeerArg<true>).
+    if (d->n_peers > 8 || d->mode != OLB_GEMM_DENSE || d->a_mn_major || d->A_peers == nullptr || d->stage_flags == nullptr ||
+        d->a_peer_rows <= 0 || d->a_peer_rows % BLOCK_M || d->my_peer < 0 || d->my_peer >= d->n_peers ||
+        d->M != d->n_peers * d->a_peer_rows || d->a_rows < d->M || d->K % 8)
+      return -14;
     PeerArg<true> peers;
-    if (d->A_peers != nullptr) {
-      if (d->a_peer_rows <= 0 || d->a_peer_rows % (d->a_mn_major ? BLOCK_K : BLOCK_M)) return -14;
-      for (int r = 0; r < d->n_peers; ++r) {
-        if (reinterpret_cast<uintptr_t>(d->A_peers[r]) & 15) return -14;
-        rc = !d->a_mn_major ? make_tmap_2d_bf16(&peers.a[r], d->A_peers[r], d->K, d->a_peer_rows, d->lda * 2, BLOCK_K, BLOCK_M)
-                            : make_tmap_2d_bf16(&peers.a[r], d->A_peers[r], d->M, d->a_peer_rows, d->lda * 2, 64, BLOCK_K);
-        if (rc) return rc;
-      }
-      for (int r = d->n_peers; r < 8; ++r) peers.a[r] = peers.a[0];
-      p.a_peer_rows = d->a_peer_rows;
-      if (!d->a_mn_major) p.m_rotate_blocks = (d->my_peer * d->a_peer_rows) / BLOCK_M;
-    } else {
-      for (int r = 0; r < 8; ++r) peers.a[r] = ta;
+    for (int r = 0; r < 8; ++r) {
+      peers.src[r] = d->A_peers[r < d->n_peers ? r : 0];
+      if (reinterpret_cast<uintptr_t>(peers.src[r]) & 15) return -14;
     }
-    if (d->B_peers != nullptr) {
-      if (!d->b_mn_major || d->b_peer_rows <= 0 || d->b_peer_rows % BLOCK_K) return -14;
-      for (int r = 0; r < d->n_peers; ++r) {
-        if (reinterpret_cast<uintptr_t>(d->B_peers[r]) & 15) return -14;
-        rc = make_tmap_2d_bf16(&peers.b[r], d->B_peers[r], d->N, d->b_peer_rows, d->ldb * 2, 64, BLOCK_K);
-        if (rc) return rc;
-      }
-      for (int r = d->n_peers; r < 8; ++r) peers.b[r] = peers.b[0];
-      p.b_peer_rows = d->b_peer_rows;
-    } else {
-      for (int r = 0; r < 8; ++r) peers.b[r] = tb;
-    }
+    peers.dst = const_cast<void*>(d->A);
+    peers.flags = d->stage_flags;
+    peers.ld = d->lda;
+    peers.rows = d->a_peer_rows;
+    peers.row_vecs = d->K / 8;
+    peers.n = d->n_peers;
+    peers.me = d->my_peer;
+    p.m_rotate_blocks = (d->my_peer * d->a_peer_rows) / BLOCK_M;
     switch (block_n) {
       case 256: return launch<256, true>(ta, tb, tb2, peers, p, sms, stream);
       case 128: return launch<128, true>(ta, tb, tb2, peers, p, sms, stream);

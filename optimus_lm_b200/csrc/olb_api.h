@@ -32,14 +32,16 @@ typedef struct {
   int* status;               // device status word (may be NULL)
   const void* B2;            // optional second B of the same layout: K range [k_split, K) is read from it
   int k_split;               // multiple of 64; 0 = single B
-  // Operands whose outer rows are spread over peer GPUs (dense mode): n_peers > 0 enables it.  A_peers[r] /
-  // B_peers[r] point at peer r's slice (mapped in this process), a_peer_rows / b_peer_rows outer rows each;
-  // A/B themselves must still be valid pointers (this GPU's slice).  B must be MN-major when partitioned.
+  // All-gather fused into the GEMM (dense mode, A K-major): n_peers > 0 enables it.  A is this GPU's gathered copy
+  // [n_peers * a_peer_rows, K]; its own a_peer_rows rows (block my_peer) are already there.  A_peers[r] points at
+  // peer r's slice [a_peer_rows, K] (mapped in this process, row stride lda).  Two extra warps of every CTA copy the
+  // other peers' rows into A over NVLink and count them per 128-row block in stage_flags (zero at launch, one int
+  // per block); the TMA producer waits for a block's count before it loads tiles of it, and the tile order starts
+  // on the rows this GPU owns.  Each remote row crosses NVLink once.
   int n_peers, my_peer;
   const void* const* A_peers;
   int a_peer_rows;
-  const void* const* B_peers;
-  int b_peer_rows;
+  int* stage_flags;
   const int* blk_range;      // RAGGED_M, optional (device memory): only row blocks [blk_range[0], blk_range[1])
 } olb_gemm_desc;
 

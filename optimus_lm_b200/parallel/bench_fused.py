@@ -2,7 +2,7 @@
 fraction of each path's roofline.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29555 \
-        -m optimus_lm_b200.parallel.bench_fused [ep|adamw|tp|all]
+        -m optimus_lm_b200.parallel.bench_fused [ep,adamw,tp|all]
 
 Every number is a CUDA-event time on the launching stream after warm-up, median of the iterations, maximum over
 ranks.  The roofline of a path is the slower of (its FLOPs / the GEMM peak) and (the bytes that cross NVLink into
@@ -195,14 +195,16 @@ def bench_tp():
 
 
 def main():
-    what = sys.argv[1] if len(sys.argv) > 1 else "all"
+    what = (sys.argv[1] if len(sys.argv) > 1 else "all").split(",")
+    if "all" in what:
+        what = ["ep", "adamw", "tp"]
     from ..dutils import setup_distributed
     setup_distributed("nccl", timeout_s=600)
-    if what in ("ep", "all"):
+    if "ep" in what:
         bench_ep()
-    if what in ("adamw", "all"):
+    if "adamw" in what:
         bench_adamw()
-    if what in ("tp", "all"):
+    if "tp" in what:
         bench_tp()
     dist.barrier()
     torch.cuda.synchronize()

@@ -6,15 +6,16 @@ sequence-parallel TP block.  The reference runs all-gather -> three GEMMs -> red
 collectives and library GEMMs (optimus/models/deepseek_v3/modeling_deepseek_v3.py:90-118 with
 comms_ptfunctions.py:118-156).  Here:
 
-* **all-gather -> GEMM**: every rank publishes its ``x`` rows in a symmetric buffer; the gate / up GEMMs read the
-  row blocks of ``A`` straight from the owners' memories with TMA loads over NVLink (per-peer tensor maps inside
-  the tcgen05 GEMM kernel, row-block order rotated so that a rank starts on its own rows).  No gathered copy of
-  the activations exists in the forward; the backward re-publishes the saved local ``x`` for the weight gradients.
+* **all-gather -> GEMM**: every rank publishes its ``x`` rows in a symmetric buffer.  The gate GEMM is launched on
+  a gathered copy ``[T, H]`` that holds only the local rows; two extra warps of each of its CTAs copy the other
+  ranks' rows in over NVLink (plain peer loads, each row crosses once) and count them per 128-row block, and the
+  TMA producer waits for a block's count before loading its tiles.  The tile order starts on the local rows, so the
+  copy runs underneath the math.  The up GEMM and the backward's weight gradients read the gathered copy locally.
 * **GEMM -> reduce-scatter**: the down projection writes this rank's partial ``[T, H]`` into a symmetric buffer;
   after a device-side barrier each rank pulls and sums (fp32) only its own rows from all peers.
 
-The backward mirrors it (all-gather of ``dout`` inside the dgrad / wgrad GEMMs - the K rows of ``dout^T`` and of
-``x`` are read from the peers - and a pull-reduce of ``dx``).  All waits are bounded device barriers.
+The backward mirrors it (all-gather of ``dout`` inside the first dgrad GEMM, a pull-reduce of ``dx``).  All waits
+are bounded: device barriers, and the producer's wait for a staged row block.
 """
 from __future__ import annotations
 
@@ -48,6 +49,13 @@ def usable(x, group, weights=()) -> bool:
     return _PEER_OK[key]
 
 
+def _flags(sg: SymmGroup, T: int) -> torch.Tensor:
+    f = getattr(sg, "_tp_flags", None)
+    if f is None or f.numel() < T // 128:
+        f = sg._tp_flags = torch.zeros(max(T // 128, 1), dtype=torch.int32, device=sg.device)
+    return f
+
+
 class _AGSwiGLURSFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, wg, wu, wd, rank, n, sg: SymmGroup, holders):
@@ -58,11 +66,13 @@ class _AGSwiGLURSFn(torch.autograd.Function):
         st = OF.status_word(x.device)
         xs = sg.named("tp_x", (T_loc, H), x.dtype)
         xs.local.copy_(x)
+        xg = torch.empty((T, H), dtype=x.dtype, device=x.device)       # gathered x, kept for the weight gradients
+        xg[rank * T_loc:(rank + 1) * T_loc].copy_(x)
         sg.barrier(_CH_X)
         gu = torch.empty((T, 2 * I), dtype=x.dtype, device=x.device)
-        # all-gather -> GEMM: A row blocks come from the peers' copies of x
-        C.gemm_peer(xs.local, xs.ptrs, wg, [], gu[:, :I], T, I, H, False, False, rank, False, st)
-        C.gemm_peer(xs.local, xs.ptrs, wu, [], gu[:, I:], T, I, H, False, False, rank, False, st)
+        # all-gather -> GEMM: the gate projection brings the peers' rows into xg while it computes
+        C.gemm_peer(xg, xs.ptrs, wg, gu[:, :I], T, I, H, False, rank, _flags(sg, T), st)
+        OF.gemm(xg, wu, T, I, H, out=gu[:, I:])
         act = torch.empty((T, I), dtype=x.dtype, device=x.device)
         C.swiglu_fwd(gu[:, :I], gu[:, I:], act)
         ys = sg.named("tp_y", (T, H), x.dtype)
@@ -71,51 +81,46 @@ class _AGSwiGLURSFn(torch.autograd.Function):
         # GEMM -> reduce-scatter: sum my rows of every rank's partial
         out = torch.empty((T_loc, H), dtype=x.dtype, device=x.device)
         C.pull_reduce_rows(ys.ptrs, rank * T_loc, H, out)
-        ctx.save_for_backward(x, gu, act, wg, wu, wd)
-        ctx.misc = (rank, n, sg, holders)
+        ctx.save_for_backward(xg, gu, act, wg, wu, wd)
+        ctx.misc = (rank, n, sg, holders, T_loc)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         C = extension()
-        x, gu, act, wg, wu, wd = ctx.saved_tensors
-        rank, n, sg, (hg, hu, hd) = ctx.misc
-        T_loc, H = x.shape
+        xg, gu, act, wg, wu, wd = ctx.saved_tensors
+        rank, n, sg, (hg, hu, hd), T_loc = ctx.misc
+        T, H = xg.shape
         I = wg.shape[0]
-        T = n * T_loc
-        st = OF.status_word(x.device)
-        xs = sg.named("tp_x", (T_loc, H), x.dtype)
-        dys = sg.named("tp_dy", (T_loc, H), x.dtype)
-        xs.local.copy_(x)                      # the weight gradients need every rank's x again
+        st = OF.status_word(xg.device)
+        dys = sg.named("tp_dy", (T_loc, H), xg.dtype)
         dys.local.copy_(dout)
+        dyg = torch.empty((T, H), dtype=xg.dtype, device=xg.device)
+        dyg[rank * T_loc:(rank + 1) * T_loc].copy_(dout)
         sg.barrier(_CH_DY)
 
-        def wgrad(holder, a_local, a_ptrs, b_local, b_ptrs, M, N):
-            """dW[M, N] = A^T B over all T rows, A / B given row-major [rows, M] / [rows, N] (MN-major operands)."""
+        def wgrad(holder, a, b, M, N):
+            """dW[M, N] = a^T b over all T rows; a / b row-major [T, M] / [T, N] (MN-major operands)."""
             if holder is not None:
-                C.gemm_peer(a_local, a_ptrs, b_local, b_ptrs, holder.buf, M, N, T, True, True, rank, holder.ready, st)
+                OF.gemm(a, b, M, N, T, a_mn_major=True, b_mn_major=True, out=holder.buf, accumulate=holder.ready)
                 holder.ready = True
                 return None
-            dw = torch.empty((M, N), dtype=x.dtype, device=x.device)
-            C.gemm_peer(a_local, a_ptrs, b_local, b_ptrs, dw, M, N, T, True, True, rank, False, st)
-            return dw
+            return OF.gemm(a, b, M, N, T, a_mn_major=True, b_mn_major=True)
 
-        # d(act) = dout_full @ wd : A rows (dout) from the peers, B = wd read MN-major
-        dact = torch.empty((T, I), dtype=x.dtype, device=x.device)
-        C.gemm_peer(dys.local, dys.ptrs, wd, [], dact, T, I, H, False, True, rank, False, st)
-        # d(wd)[H, I] = dout_full^T @ act : the K rows of A come from the peers
-        dwd = wgrad(hd, dys.local, dys.ptrs, act, [], H, I) if ctx.needs_input_grad[3] else None
+        # d(act) = dout_full @ wd: the all-gather of dout happens inside this GEMM (B = wd read MN-major)
+        dact = torch.empty((T, I), dtype=xg.dtype, device=xg.device)
+        C.gemm_peer(dyg, dys.ptrs, wd, dact, T, I, H, True, rank, _flags(sg, T), st)
+        dwd = wgrad(hd, dyg, act, H, I) if ctx.needs_input_grad[3] else None
         dgu = torch.empty_like(gu)
         C.swiglu_bwd(dact, gu[:, :I], gu[:, I:], dgu[:, :I], dgu[:, I:])
         del dact
-        # d(wg)[I, H] = dg^T @ x_full : the K rows of B come from the peers
-        dwg = wgrad(hg, dgu[:, :I], [], xs.local, xs.ptrs, I, H) if ctx.needs_input_grad[1] else None
-        dwu = wgrad(hu, dgu[:, I:], [], xs.local, xs.ptrs, I, H) if ctx.needs_input_grad[2] else None
+        dwg = wgrad(hg, dgu[:, :I], xg, I, H) if ctx.needs_input_grad[1] else None
+        dwu = wgrad(hu, dgu[:, I:], xg, I, H) if ctx.needs_input_grad[2] else None
         # d(x_full) = dg @ wg + du @ wu in one launch, then reduce-scatter by peer pulls
-        dxs = sg.named("tp_y", (T, H), x.dtype)
+        dxs = sg.named("tp_y", (T, H), xg.dtype)
         OF.gemm(dgu, wg, T, H, 2 * I, b_mn_major=True, out=dxs.local, b2=wu, k_split=I)
         sg.barrier(_CH_DX)
-        dx = torch.empty((T_loc, H), dtype=x.dtype, device=x.device)
+        dx = torch.empty((T_loc, H), dtype=xg.dtype, device=xg.device)
         C.pull_reduce_rows(dxs.ptrs, rank * T_loc, H, dx)
         return dx, dwg, dwu, dwd, None, None, None, None
 

@@ -190,6 +190,29 @@ def test_gemm_k_concatenated_b():
     assert rel_err(y, want) < 1e-2
 
 
+@pytest.mark.parametrize("n,me,rows,N,K,b_mn", [(2, 0, 256, 512, 320, False), (4, 2, 1024, 1024, 2048, False),
+                                                 (8, 7, 512, 384, 1024, True), (1, 0, 256, 128, 128, False)])
+def test_gemm_with_fused_all_gather(n, me, rows, N, K, b_mn):
+    """The all-gather variant of the GEMM with the "peers" standing in this GPU's memory: the stager warps copy the
+    other slices into the gathered operand while the tiles of the local rows run, the producer waits per row block."""
+    from optimus_lm_b200.ops import extension
+    M = n * rows
+    full = bf(M, K, seed=11)
+    slices = [full[r * rows:(r + 1) * rows].clone() for r in range(n)]
+    gathered = torch.full((M, K), float("nan"), dtype=torch.bfloat16, device="cuda")
+    gathered[me * rows:(me + 1) * rows] = slices[me]
+    b = bf(K, N, seed=12) if b_mn else bf(N, K, seed=12)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    flags = torch.empty(M // 128, dtype=torch.int32, device="cuda")
+    extension().gemm_peer(gathered, [t.data_ptr() for t in slices], b, c, M, N, K, b_mn, me, flags,
+                          OF.status_word("cuda"))
+    want = full.float() @ (b.float() if b_mn else b.float().t())
+    assert torch.equal(gathered, full)
+    assert rel_err(c, want) < 1e-2
+    counts = flags.tolist()
+    assert all(v == (0 if i * 128 // rows == me else 128) for i, v in enumerate(counts)), counts
+
+
 @pytest.mark.parametrize("T,E,K,H,I,e_start,E_loc", [(512, 8, 2, 256, 512, 0, 8), (1000, 16, 4, 128, 256, 4, 8),
                                                      (2048, 64, 8, 512, 256, 0, 64)])
 def test_moe_experts_fwd_bwd(T, E, K, H, I, e_start, E_loc):
