@@ -127,6 +127,55 @@ void gemm_peer(at::Tensor& a_gathered, const std::vector<int64_t>& a_peers, cons
   check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (all-gather variant)");
 }
 
+// GEMM -> reduce-scatter transport in one kernel: C[M, N] = A B^T (or A B with `b_mn_major`; `b2` / `k_split` as in
+// `gemm`) is this GPU's partial of a sum over the group; rows [r * M/n, (r+1) * M/n) belong to peer r.  The kernel
+// computes the next peer's rows first and its own last, and extra warps copy every finished row that belongs to
+// another peer into `c_peers[r]` (that peer's receive slot for this GPU, [M/n, N], row stride as `c`) with stores
+// over NVLink while later tiles run.  After a barrier each GPU sums its slots and its own rows of `c` locally.
+void gemm_push(const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& b2, int64_t k_split,
+               at::Tensor& c, const std::vector<int64_t>& c_peers, int64_t M, int64_t N, int64_t K, bool b_mn_major,
+               int64_t my_peer, at::Tensor& flags, const c10::optional<at::Tensor>& status) {
+  TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 &&
+                  c.scalar_type() == at::kBFloat16,
+              "bf16 CUDA operands expected");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && c.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && c.stride(1) == 1);
+  const int64_t n = static_cast<int64_t>(c_peers.size());
+  TORCH_CHECK(n >= 1 && n <= 8 && M % n == 0 && c.size(0) >= M, "bad peer layout");
+  TORCH_CHECK(flags.scalar_type() == at::kInt && flags.is_contiguous() && flags.numel() >= (M + 127) / 128,
+              "flags: one int per 128-row block");
+  c10::cuda::CUDAGuard guard(a.device());
+  flags.zero_();
+  auto cp = mptrs(c_peers);
+  olb_gemm_desc d{};
+  d.A = a.data_ptr();
+  d.B = b.data_ptr();
+  d.C = c.data_ptr();
+  d.lda = a.stride(0);
+  d.ldb = b.stride(0);
+  d.ldc = c.stride(0);
+  d.a_rows = a.size(0);
+  d.b_rows = b.size(0);
+  d.M = static_cast<int>(M);
+  d.N = static_cast<int>(N);
+  d.K = static_cast<int>(K);
+  d.a_mn_major = false;
+  d.b_mn_major = b_mn_major;
+  d.mode = OLB_GEMM_DENSE;
+  d.num_experts = 1;
+  d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
+  if (b2.has_value() && k_split > 0) {
+    TORCH_CHECK(b2->scalar_type() == at::kBFloat16 && b2->stride(0) == b.stride(0) && b2->size(0) == b.size(0));
+    d.B2 = b2->data_ptr();
+    d.k_split = static_cast<int>(k_split);
+  }
+  d.n_peers = static_cast<int>(n);
+  d.my_peer = static_cast<int>(my_peer);
+  d.a_peer_rows = static_cast<int>(M / n);
+  d.C_peers = cp.data();
+  d.stage_flags = flags.data_ptr<int>();
+  check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (reduce-scatter variant)");
+}
+
 int64_t rs_adamw_blocks(int64_t n) { return olb_rs_adamw_blocks(n); }
 
 void rs_adamw(const std::vector<int64_t>& peer_grad, const std::vector<int64_t>& peer_param, int64_t shard_off,
@@ -164,6 +213,7 @@ void register_comm(pybind11::module& m) {
   m.def("ep_pull_dweights", &ep_pull_dweights);
   m.def("pull_reduce_rows", &pull_reduce_rows);
   m.def("gemm_peer", &gemm_peer);
+  m.def("gemm_push", &gemm_push);
   m.def("rs_adamw_blocks", &rs_adamw_blocks);
   m.def("rs_adamw", &rs_adamw);
 }

@@ -79,8 +79,15 @@ struct PeerArg<true> {
   int* flags;          // rows landed per 128-row block of dst; zero at launch
   long long ld;        // elements between rows
   int rows;            // rows per peer, a multiple of BLOCK_M
-  int row_vecs;        // 16-byte vectors per row (K / 8)
+  int row_vecs;        // 16-byte vectors per row (K / 8; N / 8 when pushing)
   int n, me;
+  // Reduce-scatter transport instead (push != 0): `flags` counts the epilogue warps that have stored their part of a
+  // 128-row block of C; the stagers copy finished rows of peer r's block from C to push_dst[r] (its receive slot).
+  int push;
+  int flags_full;      // count at which a row block of C is complete (4 epilogue warps x column tiles)
+  void* push_dst[8];
+  const void* c_base;  // C and its row stride, as the stagers read it
+  long long ldc;
 };
 constexpr int NUM_THREADS_STAGED = NUM_THREADS + 64;
 
@@ -204,7 +211,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       for (int t = blockIdx.x; ok && get_tile<BLOCK_N>(p, t, num_m_blocks, blk0, ti); t += gridDim.x) {
         if constexpr (PEER) {
           // rows of another GPU: wait until the stagers have brought the whole row block into the local copy
-          if (ti.m0 / peers.rows != peers.me) {
+          if (!peers.push && ti.m0 / peers.rows != peers.me) {
             const int* flag = peers.flags + ti.m0 / BLOCK_M;
             const int need = min(BLOCK_M, p.M - ti.m0);
             unsigned long long t0 = 0;
@@ -390,6 +397,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           }
         }
       }
+      if constexpr (PEER) {
+        if (peers.push) {  // this warp's 32 rows of the tile are stored: let the stagers know
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) atomicAdd(peers.flags + ti.m0 / BLOCK_M, 1);
+        }
+      }
       if (has_k) {
         tc_fence_before();
         __syncwarp();
@@ -406,13 +420,54 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     if (warp >= 6) {
       // ---------------------------------------------------------- stagers (warps 6..7): the all-gather
       // Remote rows in the order the tiles need them: the peer after this one first.  Every CTA's stagers take rows
-      // of the same block at the same time, so blocks complete one after the other.  Nothing here waits.
+      // of the same block at the same time, so blocks complete one after the other.  The gather waits for nothing;
+      // the push waits (bounded) for this GPU's own epilogues.
       const long long total = static_cast<long long>(peers.n - 1) * peers.rows;
-      for (long long u = blockIdx.x * 2 + (warp - 6); u < total; u += static_cast<long long>(gridDim.x) * 2) {
+      int ready_blk = -1;
+      bool ok = true;
+      for (long long u = blockIdx.x * 2 + (warp - 6); ok && u < total; u += static_cast<long long>(gridDim.x) * 2) {
         const int j = static_cast<int>(u / peers.rows);
         const int r = static_cast<int>(u - static_cast<long long>(j) * peers.rows);
         const int peer = (peers.me + 1 + j) % peers.n;
         const long long drow = static_cast<long long>(peer) * peers.rows + r;
+        if (peers.push) {
+          // -------- reduce-scatter transport: row `drow` of C goes to its owner once every tile of its block is stored
+          const int blk = static_cast<int>(drow / BLOCK_M);
+          if (blk != ready_blk) {
+            unsigned long long t0 = 0;
+            for (uint32_t it = 0; ld_acquire_gpu_s32(peers.flags + blk) < peers.flags_full; ++it) {
+              if ((it & 15u) == 15u) {
+                const unsigned long long now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                if (*abort_flag || now - t0 > WAIT_LIMIT_NS) {
+                  *abort_flag = 1;
+                  if (p.status) atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
+                  ok = false;
+                  break;
+                }
+              }
+              __nanosleep(200);
+            }
+            if (!ok) break;
+            ready_blk = blk;
+          }
+          const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.c_base) + drow * peers.ldc * 2);
+          uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.push_dst[peer]) + r * peers.ldc * 2);
+          for (int c0 = 0; c0 < peers.row_vecs; c0 += 256) {
+            uint4 v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int c = c0 + i * 32 + lane;
+              if (c < peers.row_vecs) v[i] = __ldcg(s + c);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int c = c0 + i * 32 + lane;
+              if (c < peers.row_vecs) d[c] = v[i];
+            }
+          }
+          continue;
+        }
         const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.src[peer]) + r * peers.ld * 2);
         uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.dst) + drow * peers.ld * 2);
         for (int c0 = 0; c0 < peers.row_vecs; c0 += 256) {
@@ -614,23 +669,39 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   const int sms = d->max_ctas > 0 && d->max_ctas < num_sms ? d->max_ctas : num_sms;
   if (d->n_peers > 0) {
     // All-gather of A's rows fused into the GEMM (see PeerArg<true>).
-    if (d->n_peers > 8 || d->mode != OLB_GEMM_DENSE || d->a_mn_major || d->A_peers == nullptr || d->stage_flags == nullptr ||
-        d->a_peer_rows <= 0 || d->a_peer_rows % BLOCK_M || d->my_peer < 0 || d->my_peer >= d->n_peers ||
-        d->M != d->n_peers * d->a_peer_rows || d->a_rows < d->M || d->K % 8)
+    const bool push = d->C_peers != nullptr;
+    if (d->n_peers > 8 || d->mode != OLB_GEMM_DENSE || d->stage_flags == nullptr || d->a_peer_rows <= 0 ||
+        d->a_peer_rows % BLOCK_M || d->my_peer < 0 || d->my_peer >= d->n_peers || d->M != d->n_peers * d->a_peer_rows)
       return -14;
-    PeerArg<true> peers;
-    for (int r = 0; r < 8; ++r) {
-      peers.src[r] = d->A_peers[r < d->n_peers ? r : 0];
-      if (reinterpret_cast<uintptr_t>(peers.src[r]) & 15) return -14;
-    }
-    peers.dst = const_cast<void*>(d->A);
+    if (push ? (d->A_peers != nullptr || d->out_fp32 || d->accumulate)
+             : (d->A_peers == nullptr || d->a_mn_major || d->a_rows < d->M || d->K % 8))
+      return -14;
+    PeerArg<true> peers{};
     peers.flags = d->stage_flags;
-    peers.ld = d->lda;
     peers.rows = d->a_peer_rows;
-    peers.row_vecs = d->K / 8;
     peers.n = d->n_peers;
     peers.me = d->my_peer;
-    p.m_rotate_blocks = (d->my_peer * d->a_peer_rows) / BLOCK_M;
+    if (push) {
+      for (int r = 0; r < 8; ++r) {
+        peers.push_dst[r] = d->C_peers[r < d->n_peers ? r : 0];
+        if (reinterpret_cast<uintptr_t>(peers.push_dst[r]) & 15) return -14;
+      }
+      peers.push = 1;
+      peers.flags_full = 4 * ((d->N + block_n - 1) / block_n);
+      peers.c_base = d->C;
+      peers.ldc = d->ldc;
+      peers.row_vecs = d->N / 8;
+      p.m_rotate_blocks = (((d->my_peer + 1) % d->n_peers) * d->a_peer_rows) / BLOCK_M;  // own rows last
+    } else {
+      for (int r = 0; r < 8; ++r) {
+        peers.src[r] = d->A_peers[r < d->n_peers ? r : 0];
+        if (reinterpret_cast<uintptr_t>(peers.src[r]) & 15) return -14;
+      }
+      peers.dst = const_cast<void*>(d->A);
+      peers.ld = d->lda;
+      peers.row_vecs = d->K / 8;
+      p.m_rotate_blocks = (d->my_peer * d->a_peer_rows) / BLOCK_M;  // own rows first
+    }
     switch (block_n) {
       case 256: return launch<256, true>(ta, tb, tb2, peers, p, sms, stream);
       case 128: return launch<128, true>(ta, tb, tb2, peers, p, sms, stream);

@@ -42,6 +42,13 @@ typedef struct {
   const void* const* A_peers;
   int a_peer_rows;
   int* stage_flags;
+  // Reduce-scatter's transport fused into the GEMM (dense mode): n_peers > 0 with C_peers set (and A_peers null).
+  // C [n_peers * a_peer_rows, N] is this GPU's partial result; row block r of it belongs to peer r.  The epilogue
+  // counts finished tiles per 128-row block in stage_flags (zero at launch), and the two extra warps copy each
+  // finished row of another peer's block to C_peers[r] (that peer's receive slot for this GPU, [a_peer_rows, N] with
+  // row stride ldc) with stores over NVLink.  The tile order starts on the next peer's rows and ends on this GPU's
+  // own.  The sum over the slots is a local pass after a barrier.
+  void* const* C_peers;
   const int* blk_range;      // RAGGED_M, optional (device memory): only row blocks [blk_range[0], blk_range[1])
 } olb_gemm_desc;
 

@@ -11,11 +11,13 @@ comms_ptfunctions.py:118-156).  Here:
   ranks' rows in over NVLink (plain peer loads, each row crosses once) and count them per 128-row block, and the
   TMA producer waits for a block's count before loading its tiles.  The tile order starts on the local rows, so the
   copy runs underneath the math.  The up GEMM and the backward's weight gradients read the gathered copy locally.
-* **GEMM -> reduce-scatter**: the down projection writes this rank's partial ``[T, H]`` into a symmetric buffer;
-  after a device-side barrier each rank pulls and sums (fp32) only its own rows from all peers.
+* **GEMM -> reduce-scatter**: the down projection computes this rank's partial ``[T, H]`` with the next rank's rows
+  first and its own last; its epilogue counts finished tiles per row block, and the same two extra warps copy each
+  finished row of another rank's block into that rank's receive slot with stores over NVLink while later tiles run.
+  After a device-side barrier each rank sums its slots and its own rows (fp32, fixed rank order) from local memory.
 
-The backward mirrors it (all-gather of ``dout`` inside the first dgrad GEMM, a pull-reduce of ``dx``).  All waits
-are bounded: device barriers, and the producer's wait for a staged row block.
+The backward mirrors it (all-gather of ``dout`` inside the first dgrad GEMM, the same push for ``dx``).  All waits
+are bounded: device barriers, the producer's wait for a staged row block, the stagers' wait for finished tiles.
 """
 from __future__ import annotations
 
@@ -27,7 +29,7 @@ from ..ops import functional as OF
 from ..ops._ext import extension, use_kernels
 from .symm import SymmGroup, peer_access_ok
 
-_CH_X, _CH_Y, _CH_DY, _CH_DX = 8, 9, 10, 11   # barrier channels (the EP kernels use 0-3)
+_CH_X, _CH_Y, _CH_DY = 8, 9, 10   # barrier channels (the EP kernels use 0-3)
 _PEER_OK = {}
 
 
@@ -56,6 +58,24 @@ def _flags(sg: SymmGroup, T: int) -> torch.Tensor:
     return f
 
 
+def _gemm_reduce_scatter(sg: SymmGroup, a, b, T, N, K, rank, n, b_mn_major=False, b2=None, k_split=0):
+    """``reduce_scatter(a @ b^T)`` over the group: returns this rank's ``[T / n, N]`` rows of the sum."""
+    C = extension()
+    T_loc = T // n
+    part = getattr(sg, "_tp_part", None)
+    if part is None or part.shape != (T, N) or part.dtype != a.dtype:
+        part = sg._tp_part = torch.empty((T, N), dtype=a.dtype, device=a.device)
+    recv = sg.named("tp_recv", (n, T_loc, N), a.dtype)       # slot s: rank s's partial of my rows
+    slot_bytes = T_loc * N * a.element_size()
+    C.gemm_push(a, b, b2, k_split, part, [ptr + rank * slot_bytes for ptr in recv.ptrs], T, N, K, b_mn_major, rank,
+                _flags(sg, T), OF.status_word(a.device))
+    sg.barrier(_CH_Y)
+    out = torch.empty((T_loc, N), dtype=a.dtype, device=a.device)
+    mine = part.data_ptr() + rank * slot_bytes
+    C.pull_reduce_rows([mine if s == rank else recv.local.data_ptr() + s * slot_bytes for s in range(n)], 0, N, out)
+    return out
+
+
 class _AGSwiGLURSFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, wg, wu, wd, rank, n, sg: SymmGroup, holders):
@@ -75,12 +95,8 @@ class _AGSwiGLURSFn(torch.autograd.Function):
         OF.gemm(xg, wu, T, I, H, out=gu[:, I:])
         act = torch.empty((T, I), dtype=x.dtype, device=x.device)
         C.swiglu_fwd(gu[:, :I], gu[:, I:], act)
-        ys = sg.named("tp_y", (T, H), x.dtype)
-        OF.gemm(act, wd, T, H, I, out=ys.local)
-        sg.barrier(_CH_Y)
-        # GEMM -> reduce-scatter: sum my rows of every rank's partial
-        out = torch.empty((T_loc, H), dtype=x.dtype, device=x.device)
-        C.pull_reduce_rows(ys.ptrs, rank * T_loc, H, out)
+        # GEMM -> reduce-scatter: finished rows travel to their owners while the down projection is still running
+        out = _gemm_reduce_scatter(sg, act, wd, T, H, I, rank, n)
         ctx.save_for_backward(xg, gu, act, wg, wu, wd)
         ctx.misc = (rank, n, sg, holders, T_loc)
         return out
@@ -116,12 +132,8 @@ class _AGSwiGLURSFn(torch.autograd.Function):
         del dact
         dwg = wgrad(hg, dgu[:, :I], xg, I, H) if ctx.needs_input_grad[1] else None
         dwu = wgrad(hu, dgu[:, I:], xg, I, H) if ctx.needs_input_grad[2] else None
-        # d(x_full) = dg @ wg + du @ wu in one launch, then reduce-scatter by peer pulls
-        dxs = sg.named("tp_y", (T, H), xg.dtype)
-        OF.gemm(dgu, wg, T, H, 2 * I, b_mn_major=True, out=dxs.local, b2=wu, k_split=I)
-        sg.barrier(_CH_DX)
-        dx = torch.empty((T_loc, H), dtype=xg.dtype, device=xg.device)
-        C.pull_reduce_rows(dxs.ptrs, rank * T_loc, H, dx)
+        # d(x_full) = dg @ wg + du @ wu in one launch, reduce-scattered the same way
+        dx = _gemm_reduce_scatter(sg, dgu, wg, T, H, 2 * I, rank, n, b_mn_major=True, b2=wu, k_split=I)
         return dx, dwg, dwu, dwd, None, None, None, None
 
 

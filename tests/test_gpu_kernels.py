@@ -213,6 +213,33 @@ def test_gemm_with_fused_all_gather(n, me, rows, N, K, b_mn):
     assert all(v == (0 if i * 128 // rows == me else 128) for i, v in enumerate(counts)), counts
 
 
+@pytest.mark.parametrize("n,me,rows,N,K,b_mn,split", [(2, 1, 256, 512, 320, False, 0), (4, 0, 1024, 1024, 1024, True, 512),
+                                                       (8, 3, 256, 328, 256, False, 0), (1, 0, 256, 128, 128, False, 0)])
+def test_gemm_with_fused_reduce_scatter_push(n, me, rows, N, K, b_mn, split):
+    """The reduce-scatter variant of the GEMM with the peers' receive slots standing in this GPU's memory: every
+    finished row that belongs to another peer is copied to that peer's slot by the stager warps."""
+    from optimus_lm_b200.ops import extension
+    M = n * rows
+    a = bf(M, K, seed=21)
+    b = bf(K if not split else split, N, seed=22) if b_mn else bf(N, K, seed=22)
+    b2 = bf(split, N, seed=23) if split else None
+    part = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    slots = [torch.full((rows, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(n)]
+    flags = torch.empty(M // 128, dtype=torch.int32, device="cuda")
+    extension().gemm_push(a, b, b2, split, part, [t.data_ptr() for t in slots], M, N, K, b_mn, me, flags,
+                          OF.status_word("cuda"))
+    if split:
+        want = a[:, :split].float() @ b.float() + a[:, split:].float() @ b2[:K - split].float()
+    else:
+        want = a.float() @ (b.float() if b_mn else b.float().t())
+    assert rel_err(part, want) < 1e-2
+    for r in range(n):
+        if r == me:
+            assert torch.isnan(slots[r].float()).all()          # nothing is sent to oneself
+        else:
+            assert torch.equal(slots[r], part[r * rows:(r + 1) * rows]), r
+
+
 @pytest.mark.parametrize("T,E,K,H,I,e_start,E_loc", [(512, 8, 2, 256, 512, 0, 8), (1000, 16, 4, 128, 256, 4, 8),
                                                      (2048, 64, 8, 512, 256, 0, 64)])
 def test_moe_experts_fwd_bwd(T, E, K, H, I, e_start, E_loc):
