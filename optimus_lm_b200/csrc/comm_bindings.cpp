@@ -176,6 +176,55 @@ void gemm_push(const at::Tensor& a, const at::Tensor& b, const c10::optional<at:
   check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (reduce-scatter variant)");
 }
 
+// Grouped expert GEMM (ragged-M: rows grouped by expert, `meta` as in `gemm`) whose finished rows travel to the owners
+// of their tokens inside the kernel: C[u, :] = A[u, :] W[expert(u)]^T, and row u is copied to
+// `c_peers[owner]`'s [tokens, topk, N] buffer at (token, k) = (src_of[u] % tokens, k_of[u]) by extra warps while later
+// tiles run (the expert-parallel combine's all-to-all).  The owner sums its topk slots locally after a barrier.
+void gemm_ep_push(const at::Tensor& a, const at::Tensor& w2d, at::Tensor& c, const std::vector<int64_t>& c_peers,
+                  const at::Tensor& meta, const at::Tensor& src_of, const at::Tensor& k_of, int64_t M, int64_t N, int64_t K,
+                  int64_t b_expert_rows, int64_t num_experts, int64_t tokens, int64_t topk, int64_t my_peer,
+                  at::Tensor& flags, const c10::optional<at::Tensor>& status) {
+  TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && w2d.scalar_type() == at::kBFloat16 &&
+                  c.scalar_type() == at::kBFloat16,
+              "bf16 CUDA operands expected");
+  TORCH_CHECK(a.dim() == 2 && w2d.dim() == 2 && c.dim() == 2 && a.stride(1) == 1 && w2d.stride(1) == 1 && c.stride(1) == 1);
+  TORCH_CHECK(meta.scalar_type() == at::kInt && src_of.scalar_type() == at::kInt && k_of.scalar_type() == at::kInt);
+  TORCH_CHECK(src_of.numel() >= M && k_of.numel() >= M && a.size(0) >= M && c.size(0) >= M);
+  const int64_t n = static_cast<int64_t>(c_peers.size());
+  TORCH_CHECK(n >= 1 && n <= 8, "bad peer count");
+  TORCH_CHECK(flags.scalar_type() == at::kInt && flags.is_contiguous() && flags.numel() >= (M + 127) / 128,
+              "flags: one int per 128-row block");
+  c10::cuda::CUDAGuard guard(a.device());
+  flags.zero_();
+  auto cp = mptrs(c_peers);
+  olb_gemm_desc d{};
+  d.A = a.data_ptr();
+  d.B = w2d.data_ptr();
+  d.C = c.data_ptr();
+  d.lda = a.stride(0);
+  d.ldb = w2d.stride(0);
+  d.ldc = c.stride(0);
+  d.a_rows = a.size(0);
+  d.b_rows = w2d.size(0);
+  d.M = static_cast<int>(M);
+  d.N = static_cast<int>(N);
+  d.K = static_cast<int>(K);
+  d.mode = OLB_GEMM_RAGGED_M;
+  d.meta = meta.data_ptr<int>();
+  d.num_experts = static_cast<int>(num_experts);
+  d.b_expert_rows = static_cast<int>(b_expert_rows);
+  d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
+  d.n_peers = static_cast<int>(n);
+  d.my_peer = static_cast<int>(my_peer);
+  d.C_peers = cp.data();
+  d.stage_flags = flags.data_ptr<int>();
+  d.ep_src_of = src_of.data_ptr<int>();
+  d.ep_k_of = k_of.data_ptr<int>();
+  d.ep_tokens = static_cast<int>(tokens);
+  d.ep_topk = static_cast<int>(topk);
+  check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (expert-parallel combine variant)");
+}
+
 int64_t rs_adamw_blocks(int64_t n) { return olb_rs_adamw_blocks(n); }
 
 void rs_adamw(const std::vector<int64_t>& peer_grad, const std::vector<int64_t>& peer_param, int64_t shard_off,
@@ -214,6 +263,7 @@ void register_comm(pybind11::module& m) {
   m.def("pull_reduce_rows", &pull_reduce_rows);
   m.def("gemm_peer", &gemm_peer);
   m.def("gemm_push", &gemm_push);
+  m.def("gemm_ep_push", &gemm_ep_push);
   m.def("rs_adamw_blocks", &rs_adamw_blocks);
   m.def("rs_adamw", &rs_adamw);
 }

@@ -10,7 +10,7 @@
 //                two TMEM accumulators and commits to mbarriers
 //   * warps 2-5: epilogue - tcgen05.ld the accumulator (each warp owns 32 TMEM lanes),
 //                convert and store / accumulate into C while the next tile's main loop runs
-//   * warps 6-7: only in the all-gather variant (PeerArg<true>): copy the other GPUs' rows of A into the local
+//   * warps 6-9: only in the variants with a fused collective (PeerArg<true>): copy the other GPUs' rows of A into the local
 //                gathered copy over NVLink while the tiles of the local rows are computed
 // Each operand may be K-major (rows of K contiguous) or MN-major (rows of M/N contiguous),
 // which gives NT / NN / TN / TT products without a transpose pass:
@@ -64,7 +64,7 @@ struct GemmParams {
   int* status;
 };
 
-// All-gather fused into the GEMM: the outer rows of A live in the memories of up to 8 GPUs.  Two extra warps per
+// All-gather fused into the GEMM: the outer rows of A live in the memories of up to 8 GPUs.  Four extra warps per
 // CTA ("stagers") copy the other GPUs' rows into this GPU's gathered copy of A with plain loads over NVLink and
 // count the rows that have landed per 128-row block; the TMA producer waits (bounded) for a block's count before it
 // loads tiles of that block from the local copy.  A remote row crosses NVLink once, however many column tiles read it.
@@ -88,8 +88,15 @@ struct PeerArg<true> {
   void* push_dst[8];
   const void* c_base;  // C and its row stride, as the stagers read it
   long long ldc;
+  // Expert-parallel combine transport (push == 2, ragged-M mode): row u of C is the expert output of the routed pair
+  // (token src_of[u] of the group's T-token-per-rank numbering, choice k_of[u]); it goes to the token owner's
+  // receive buffer [T, topk, N] at push_dst[owner] + (t * topk + k) * ld.  Padding rows (src_of < 0) are not sent.
+  const int* src_of;
+  const int* k_of;
+  int T, topk;
 };
-constexpr int NUM_THREADS_STAGED = NUM_THREADS + 64;
+constexpr int STAGER_WARPS = 4;
+constexpr int NUM_THREADS_STAGED = NUM_THREADS + 32 * STAGER_WARPS;
 
 template <int BLOCK_N>
 struct SmemLayout {
@@ -141,6 +148,43 @@ __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int num_m_b
   ti.kb_end = (p.K + BLOCK_K - 1) / BLOCK_K;
   ti.expert = (p.mode == OLB_GEMM_RAGGED_M) ? p.meta[1 + m_blk] : 0;
   return true;
+}
+
+// Bounded wait until `*count >= need` (a counter that warps of this GPU raise).  False, with the status word set,
+// when the limit runs out or another role of the CTA has given up.
+__device__ __forceinline__ bool wait_count(const int* count, int need, int* status, volatile int* abort_flag) {
+  unsigned long long t0 = 0;
+  for (uint32_t it = 0; ld_acquire_gpu_s32(count) < need; ++it) {
+    if ((it & 15u) == 15u) {
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (*abort_flag || now - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, ST_TIMEOUT_PEER);
+        return false;
+      }
+    }
+    __nanosleep(100);
+  }
+  return true;
+}
+
+// One warp copies a row of `vecs` 16-byte vectors, up to eight loads in flight per lane; the loads bypass L1
+// (the row was written by other SMs during this kernel).
+__device__ __forceinline__ void copy_row_ldcg(const uint4* s, uint4* d, int vecs, int lane) {
+  for (int c0 = 0; c0 < vecs; c0 += 256) {
+    uint4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = c0 + i * 32 + lane;
+      if (c < vecs) v[i] = __ldcg(s + c);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = c0 + i * 32 + lane;
+      if (c < vecs) d[c] = v[i];
+    }
+  }
 }
 
 template <int BLOCK_N, bool PEER>
@@ -212,22 +256,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if constexpr (PEER) {
           // rows of another GPU: wait until the stagers have brought the whole row block into the local copy
           if (!peers.push && ti.m0 / peers.rows != peers.me) {
-            const int* flag = peers.flags + ti.m0 / BLOCK_M;
-            const int need = min(BLOCK_M, p.M - ti.m0);
-            unsigned long long t0 = 0;
-            for (uint32_t it = 0; ld_acquire_gpu_s32(flag) < need; ++it) {
-              if ((it & 15u) == 15u) {
-                const unsigned long long now = globaltimer_ns();
-                if (t0 == 0) t0 = now;
-                if (*abort_flag || now - t0 > WAIT_LIMIT_NS) {
-                  *abort_flag = 1;
-                  if (p.status) atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
-                  ok = false;
-                  break;
-                }
-              }
+            if (!wait_count(peers.flags + ti.m0 / BLOCK_M, min(BLOCK_M, p.M - ti.m0), p.status, abort_flag)) {
+              ok = false;
+              break;
             }
-            if (!ok) break;
             fence_proxy_async_all();  // the rows were written by ordinary stores; the loads below are TMA
           }
         }
@@ -418,14 +450,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   if constexpr (PEER) {
     if (warp >= 6) {
-      // ---------------------------------------------------------- stagers (warps 6..7): the all-gather
+      // ---------------------------------------------------------- stagers (warps 6..9): the all-gather
       // Remote rows in the order the tiles need them: the peer after this one first.  Every CTA's stagers take rows
       // of the same block at the same time, so blocks complete one after the other.  The gather waits for nothing;
       // the push waits (bounded) for this GPU's own epilogues.
-      const long long total = static_cast<long long>(peers.n - 1) * peers.rows;
+      const long long total = peers.push == 2 ? min(static_cast<long long>(num_m_blocks) * BLOCK_M, static_cast<long long>(p.M))
+                                              : static_cast<long long>(peers.n - 1) * peers.rows;
       int ready_blk = -1;
       bool ok = true;
-      for (long long u = blockIdx.x * 2 + (warp - 6); ok && u < total; u += static_cast<long long>(gridDim.x) * 2) {
+      for (long long u = blockIdx.x * STAGER_WARPS + (warp - 6); ok && u < total;
+           u += static_cast<long long>(gridDim.x) * STAGER_WARPS) {
+        if (peers.push == 2) {
+          // -------- expert-parallel combine transport: a finished row goes to the owner of its token
+          const int blk = static_cast<int>(u / BLOCK_M);
+          if (blk != ready_blk) {
+            if (!wait_count(peers.flags + blk, peers.flags_full, p.status, abort_flag)) {
+              ok = false;
+              break;
+            }
+            ready_blk = blk;
+          }
+          const int g = peers.src_of[u];
+          if (g < 0) continue;
+          const int owner = g / peers.T;
+          const long long slot = static_cast<long long>(g - owner * peers.T) * peers.topk + peers.k_of[u];
+          const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.c_base) + u * peers.ldc * 2);
+          uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.push_dst[owner]) + slot * peers.ld * 2);
+          copy_row_ldcg(s, d, peers.row_vecs, lane);
+          continue;
+        }
         const int j = static_cast<int>(u / peers.rows);
         const int r = static_cast<int>(u - static_cast<long long>(j) * peers.rows);
         const int peer = (peers.me + 1 + j) % peers.n;
@@ -434,38 +487,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           // -------- reduce-scatter transport: row `drow` of C goes to its owner once every tile of its block is stored
           const int blk = static_cast<int>(drow / BLOCK_M);
           if (blk != ready_blk) {
-            unsigned long long t0 = 0;
-            for (uint32_t it = 0; ld_acquire_gpu_s32(peers.flags + blk) < peers.flags_full; ++it) {
-              if ((it & 15u) == 15u) {
-                const unsigned long long now = globaltimer_ns();
-                if (t0 == 0) t0 = now;
-                if (*abort_flag || now - t0 > WAIT_LIMIT_NS) {
-                  *abort_flag = 1;
-                  if (p.status) atomicCAS(p.status, 0, ST_TIMEOUT_PEER);
-                  ok = false;
-                  break;
-                }
-              }
-              __nanosleep(200);
+            if (!wait_count(peers.flags + blk, peers.flags_full, p.status, abort_flag)) {
+              ok = false;
+              break;
             }
-            if (!ok) break;
             ready_blk = blk;
           }
           const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.c_base) + drow * peers.ldc * 2);
           uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.push_dst[peer]) + r * peers.ldc * 2);
-          for (int c0 = 0; c0 < peers.row_vecs; c0 += 256) {
-            uint4 v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int c = c0 + i * 32 + lane;
-              if (c < peers.row_vecs) v[i] = __ldcg(s + c);
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int c = c0 + i * 32 + lane;
-              if (c < peers.row_vecs) d[c] = v[i];
-            }
-          }
+          copy_row_ldcg(s, d, peers.row_vecs, lane);
           continue;
         }
         const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.src[peer]) + r * peers.ld * 2);
@@ -670,6 +700,36 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   if (d->n_peers > 0) {
     // All-gather of A's rows fused into the GEMM (see PeerArg<true>).
     const bool push = d->C_peers != nullptr;
+    if (d->mode == OLB_GEMM_RAGGED_M) {
+      // Expert-parallel combine transport: finished rows of C go to the owners of their tokens.
+      if (!push || d->n_peers > 8 || d->stage_flags == nullptr || d->ep_src_of == nullptr || d->ep_k_of == nullptr ||
+          d->ep_tokens <= 0 || d->ep_topk <= 0 || d->out_fp32 || d->accumulate || d->blk_range != nullptr || d->N % 8)
+        return -14;
+      PeerArg<true> peers{};
+      for (int r = 0; r < 8; ++r) {
+        peers.push_dst[r] = d->C_peers[r < d->n_peers ? r : 0];
+        if (reinterpret_cast<uintptr_t>(peers.push_dst[r]) & 15) return -14;
+      }
+      peers.flags = d->stage_flags;
+      peers.n = d->n_peers;
+      peers.me = d->my_peer;
+      peers.push = 2;
+      peers.flags_full = 4 * ((d->N + block_n - 1) / block_n);
+      peers.c_base = d->C;
+      peers.ldc = d->ldc;
+      peers.ld = d->N;
+      peers.row_vecs = d->N / 8;
+      peers.src_of = d->ep_src_of;
+      peers.k_of = d->ep_k_of;
+      peers.T = d->ep_tokens;
+      peers.topk = d->ep_topk;
+      switch (block_n) {
+        case 256: return launch<256, true>(ta, tb, tb2, peers, p, sms, stream);
+        case 128: return launch<128, true>(ta, tb, tb2, peers, p, sms, stream);
+        case 64: return launch<64, true>(ta, tb, tb2, peers, p, sms, stream);
+        default: return -12;
+      }
+    }
     if (d->n_peers > 8 || d->mode != OLB_GEMM_DENSE || d->stage_flags == nullptr || d->a_peer_rows <= 0 ||
         d->a_peer_rows % BLOCK_M || d->my_peer < 0 || d->my_peer >= d->n_peers || d->M != d->n_peers * d->a_peer_rows)
       return -14;

@@ -34,7 +34,7 @@ typedef struct {
   int k_split;               // multiple of 64; 0 = single B
   // All-gather fused into the GEMM (dense mode, A K-major): n_peers > 0 enables it.  A is this GPU's gathered copy
   // [n_peers * a_peer_rows, K]; its own a_peer_rows rows (block my_peer) are already there.  A_peers[r] points at
-  // peer r's slice [a_peer_rows, K] (mapped in this process, row stride lda).  Two extra warps of every CTA copy the
+  // peer r's slice [a_peer_rows, K] (mapped in this process, row stride lda).  Extra warps of every CTA copy the
   // other peers' rows into A over NVLink and count them per 128-row block in stage_flags (zero at launch, one int
   // per block); the TMA producer waits for a block's count before it loads tiles of it, and the tile order starts
   // on the rows this GPU owns.  Each remote row crosses NVLink once.
@@ -44,11 +44,18 @@ typedef struct {
   int* stage_flags;
   // Reduce-scatter's transport fused into the GEMM (dense mode): n_peers > 0 with C_peers set (and A_peers null).
   // C [n_peers * a_peer_rows, N] is this GPU's partial result; row block r of it belongs to peer r.  The epilogue
-  // counts finished tiles per 128-row block in stage_flags (zero at launch), and the two extra warps copy each
+  // counts finished tiles per 128-row block in stage_flags (zero at launch), and the extra warps copy each
   // finished row of another peer's block to C_peers[r] (that peer's receive slot for this GPU, [a_peer_rows, N] with
   // row stride ldc) with stores over NVLink.  The tile order starts on the next peer's rows and ends on this GPU's
   // own.  The sum over the slots is a local pass after a barrier.
   void* const* C_peers;
+  // Expert-parallel combine transport (RAGGED_M mode with n_peers > 0 and C_peers set): row u of C is the expert
+  // output of the routed pair (token ep_src_of[u] in the group-wide numbering with ep_tokens tokens per rank, choice
+  // ep_k_of[u]); once every tile of its 128-row block is stored (stage_flags, zero at launch) the extra warps copy
+  // it to C_peers[owner] + ((token % ep_tokens) * ep_topk + k) * N: the owner's receive buffer [ep_tokens, ep_topk, N].
+  const int* ep_src_of;
+  const int* ep_k_of;
+  int ep_tokens, ep_topk;
   const int* blk_range;      // RAGGED_M, optional (device memory): only row blocks [blk_range[0], blk_range[1])
 } olb_gemm_desc;
 

@@ -63,6 +63,8 @@ class EngineArgs:
     opt_use_chunked_allreduce: bool = False
     use_fused_optimizer: bool = True
     use_direct_grads: bool = True         # weight-gradient GEMMs store into the flat gradient buffer themselves
+    use_early_updates: bool = False       # AdamW of a finished layer runs under the backward of the layers before it
+                                          # (measured neutral on a power-capped B200: 205.1 vs 205.0 ms/step)
     use_activation_checkpointing: bool = False
     activation_checkpointing_level: int = 0
     use_fast_moe: bool = True
@@ -203,6 +205,7 @@ class TrainEngine:
         self.trainer = self._build_trainer()
         self.step_id = 0
         self._staging = None
+        self._setup_early_updates()
 
     # ------------------------------------------------------------------ construction
     def _build_optimizer(self):
@@ -233,6 +236,29 @@ class TrainEngine:
                 and hasattr(opt, "enable_direct_grads"):
             opt.enable_direct_grads()
         return opt
+
+    def _setup_early_updates(self):
+        """Hook every decoder layer's input: when its gradient arrives, the layer's backward is complete and the
+        optimizer may update that layer's parameters on a side stream (``optimizers.enable_early_updates``)."""
+        a, opt = self.args, self.optimizer
+        self._early = False
+        layers = getattr(getattr(self.model, "model", None), "layers", None)
+        if not (a.use_early_updates and os.environ.get("OLB_EARLY_UPDATES", "1") != "0" and self.device.type == "cuda" and self.trainer is None and layers is not None
+                and hasattr(opt, "enable_early_updates") and not a.skip_backward_pass):
+            return
+        if opt.enable_early_updates([list(layer.parameters()) for layer in layers]) == 0:
+            return
+        self._early = True
+
+        def pre_hook(idx):
+            def hook(module, inputs):
+                h = inputs[0] if inputs else None
+                if opt._early_armed and torch.is_tensor(h) and h.requires_grad and torch.is_grad_enabled():
+                    h.register_hook(lambda g, i=idx: opt.early_update_layer(i))
+            return hook
+
+        for i, layer in enumerate(layers):
+            layer.register_forward_pre_hook(pre_hook(i))
 
     def _build_trainer(self):
         a, p = self.args, self.pmap
@@ -270,6 +296,8 @@ class TrainEngine:
 
     def train_step(self, input_ids: torch.Tensor) -> StepOutput:
         ids = self.stage_inputs(input_ids)
+        if self._early:
+            self.optimizer.arm_early_updates((self.step_id + 1) % self.args.opt_grad_acc_steps == 0)
         loss = self.forward_backward(ids)
         grad_norm = None
         did = False

@@ -262,6 +262,111 @@ class _FlatAdamWEngine(Optimizer):
         for fam in self.families:
             fam.flat_grad.zero_()
 
+    # ------------------------------------------------------------------ updates underneath the backward
+    def enable_early_updates(self, layers) -> int:
+        """Let the AdamW update of a decoder layer run on a side stream as soon as that layer's backward has
+        finished, underneath the backward of the layers before it (the update is bound by HBM bandwidth, the
+        backward by the tensor cores).  ``layers``: one list of parameters per decoder layer.  Only parameters of
+        families that need no gradient reduction (one shard) take part, and only while gradient clipping is
+        inactive - with delayed clipping the reference does not clip during the first ``warmup_steps`` optimizer
+        steps (optimus/optimizers.py:394-412), so the norm is a by-product there and the update needs no global
+        quantity.  Everything else is updated in ``step`` as before.  Returns the number of layers enabled."""
+        self._early_layers = []
+        if self.device.type != "cuda" or self.skip_optimizer_step or type(self)._norm_sq_local is not _FlatAdamWEngine._norm_sq_local:
+            return 0
+        for params in layers:
+            ids = {id(p) for p in params}
+            ranges = []
+            for fam in self.families:
+                if (_group_ok(fam.spec.group) and fam.spec.num_shards > 1) or len(fam.slices) != 1 or fam.master is None:
+                    continue
+                idx = [i for i, p in enumerate(fam.spec.params) if id(p) in ids]
+                if not idx:
+                    continue
+                if idx != list(range(idx[0], idx[-1] + 1)):
+                    ranges = None  # the layer's parameters are not one run of the flat buffer
+                    break
+                lo = fam.param_start_inds[idx[0]]
+                hi = fam.param_start_inds[idx[-1]] + fam.param_sizes[idx[-1]]
+                if lo % 8 or (hi - lo) % 8:
+                    ranges = None
+                    break
+                holders = [h for h in (getattr(fam.spec.params[i], "_olb_direct", None) for i in idx) if h is not None]
+                ranges.append((fam, lo, hi, holders))
+            self._early_layers.append(ranges or [])
+        self._early_stream = torch.cuda.Stream(device=self.device)
+        self._early_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._early_done = {}      # id(family) -> [(lo, hi), ...] updated during this step's backward
+        self._early_armed = False
+        return sum(1 for r in self._early_layers if r)
+
+    def arm_early_updates(self, armed: bool):
+        """Called before a forward pass: ``armed`` when its backward is the last one before ``step``."""
+        if getattr(self, "_early_layers", None):
+            self._early_armed = bool(armed) and not self._clipping_active()
+
+    @torch.no_grad()
+    def early_update_layer(self, layer_idx: int):
+        """Backward hook: the gradients of layer ``layer_idx`` are final; update its parameters on the side stream."""
+        if not getattr(self, "_early_armed", False):
+            return
+        ranges = self._early_layers[layer_idx]
+        if not ranges:
+            return
+        beta1, beta2 = self.defaults["betas"]
+        eps, wd = self.defaults["eps"], self.defaults["weight_decay"]
+        lr = self.param_groups[0]["lr"]
+        for fam, lo, hi, holders in ranges:
+            for h in holders:
+                if not h.ready:            # received no gradient in this step
+                    h.buf.zero_()
+                    h.ready = True
+        main = torch.cuda.current_stream(self.device)
+        ev = torch.cuda.Event()
+        ev.record(main)
+        with torch.cuda.stream(self._early_stream):
+            self._early_stream.wait_event(ev)
+            for fam, lo, hi, _ in ranges:
+                if any(lo < b and a < hi for a, b in self._early_done.get(id(fam), ())):
+                    continue               # already updated (a hook that fired twice)
+                scale = 1.0 / fam.spec.grad_divisor
+                OF.sum_of_squares(fam.flat_grad[lo:hi], scale, out=self._early_sq, accumulate=True)
+                OF.adamw_step(fam.flat_grad[lo:hi], fam.master[lo:hi], fam.exp_avg[lo:hi], fam.exp_avg_sq[lo:hi],
+                              fam.flat_param[lo:hi], lr, beta1, beta2, eps, wd, self.step_id + 1, grad_scale=scale,
+                              clip_coef=None, skip_weight_update=self.skip_optimizer_step_weight_update)
+                self._early_done.setdefault(id(fam), []).append((lo, hi))
+
+    def _pending_ranges(self, fam: _Family, sl: _Slice):
+        """The parts ``(lo, hi)`` of this rank's part of slice ``sl`` (offsets inside the part) that ``step`` still has
+        to update: everything, minus what the backward hooks have updated already."""
+        done = sorted(getattr(self, "_early_done", {}).get(id(fam), ()))
+        if not done:
+            return [(0, sl.part)]
+        out, cur = [], 0
+        for lo, hi in done:
+            if lo > cur:
+                out.append((cur, lo))
+            cur = max(cur, hi)
+        if cur < sl.part:
+            out.append((cur, sl.part))
+        return out
+
+    def _join_early_updates(self):
+        """Before ``step`` touches anything: the side stream's updates are ordered before the current stream.
+        Returns the sum of squares of the gradients they covered (None when there were none)."""
+        if not getattr(self, "_early_done", None):
+            return None
+        ev = torch.cuda.Event()
+        ev.record(self._early_stream)
+        torch.cuda.current_stream(self.device).wait_event(ev)
+        return self._early_sq
+
+    def _finish_early_updates(self):
+        if getattr(self, "_early_done", None):
+            self._early_done = {}
+            self._early_sq.zero_()
+        self._early_armed = False
+
     def _clipping_active(self) -> bool:
         return self.opt_disable_delayed_grad_clipping or self.step_id >= self.warmup_steps
 
@@ -273,7 +378,9 @@ class _FlatAdamWEngine(Optimizer):
         for fam in self.families:
             scale = 1.0 / fam.spec.grad_divisor
             for sl in fam.slices:
-                OF.sum_of_squares(fam.grad_part(sl), scale, out=acc, accumulate=True)
+                g = fam.grad_part(sl)
+                for lo, hi in self._pending_ranges(fam, sl):
+                    OF.sum_of_squares(g[lo:hi], scale, out=acc, accumulate=True)
         return acc
 
     def _reduce_family(self, fam: _Family):
@@ -342,11 +449,16 @@ class _FlatAdamWEngine(Optimizer):
 
         if fused is not None:
             grad_norm = fused.step(self)
+            self._finish_early_updates()
             self.step_id += 1
             return grad_norm
 
         with record_pcl_function("4opt-step_grad-clip"):
-            grad_norm = self._global_norm(self._norm_sq_local()).reshape(())
+            early_sq = self._join_early_updates()
+            norm_sq = self._norm_sq_local()
+            if early_sq is not None:
+                norm_sq = norm_sq + early_sq
+            grad_norm = self._global_norm(norm_sq).reshape(())
             clip_coef = None
             if self._clipping_active():
                 clip_coef = torch.clamp(self.max_grad_norm / (grad_norm + 1e-6), max=1.0).reshape(1).float()
@@ -358,11 +470,14 @@ class _FlatAdamWEngine(Optimizer):
                 lr = self.param_groups[0]["lr"]
                 for fam in self.families:
                     for sl in fam.slices:
-                        s0, s1 = sl.state_start, sl.state_start + sl.part
-                        OF.adamw_step(fam.grad_part(sl), fam.master[s0:s1], fam.exp_avg[s0:s1], fam.exp_avg_sq[s0:s1],
-                                      fam.param_part(sl), lr, beta1, beta2, eps, wd, self.step_id + 1,
-                                      grad_scale=1.0 / fam.spec.grad_divisor, clip_coef=clip_coef,
-                                      skip_weight_update=self.skip_optimizer_step_weight_update)
+                        g, pp = fam.grad_part(sl), fam.param_part(sl)
+                        for lo, hi in self._pending_ranges(fam, sl):
+                            s0, s1 = sl.state_start + lo, sl.state_start + hi
+                            OF.adamw_step(g[lo:hi], fam.master[s0:s1], fam.exp_avg[s0:s1], fam.exp_avg_sq[s0:s1],
+                                          pp[lo:hi], lr, beta1, beta2, eps, wd, self.step_id + 1,
+                                          grad_scale=1.0 / fam.spec.grad_divisor, clip_coef=clip_coef,
+                                          skip_weight_update=self.skip_optimizer_step_weight_update)
+        self._finish_early_updates()
         with record_pcl_function("3dp-comms-2param_gather-block"):
             for fam in self.families:
                 self._gather_family(fam)

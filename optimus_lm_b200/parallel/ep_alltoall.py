@@ -11,8 +11,11 @@ rows themselves never go through a collective:
   over NVLink, straight into the grouped-GEMM operand (dispatch all-to-all + permutation, one
   kernel, no staging copy of all tokens);
 * experts   - grouped tcgen05 GEMMs with the routing weight folded into the activation;
-* combine   - each rank's combine kernel pulls the K expert outputs of each of its tokens from the
-  owners' output buffers and reduces them in fp32 (combine all-to-all + weighted sum, one kernel).
+* combine   - forward: the down projection's GEMM kernel sends every finished output row to the owner of
+  its token with stores over NVLink from extra warps of each CTA, while its later tiles are still running
+  (combine all-to-all inside the grouped GEMM); after a barrier the owner sums the K slots of each token from
+  local memory in fp32.  Backward: each rank's combine kernel pulls the K input-gradient rows of each of its
+  tokens from the owners' buffers on a side stream underneath the weight-gradient GEMMs.
 
 The backward pass is the mirror image (gather of output gradients, combine of input gradients,
 pull of the routing-weight gradients).  Two device-side barriers per direction order the buffer
@@ -39,6 +42,29 @@ def _all_gather_rows(t: torch.Tensor, n: int, group) -> torch.Tensor:
 def _parts(E_loc: int) -> int:
     """Groups of local experts the dispatch is pipelined over (OLB_EP_PARTS, default 4, 1 = no pipelining)."""
     return max(1, min(int(os.environ.get("OLB_EP_PARTS", "4")), E_loc))
+
+
+def _push_combine(n: int) -> bool:
+    """Forward combine as stores from the down projection's kernel instead of pulls after it.  ``OLB_EP_PUSH`` = 1 / 0
+    forces it on / off; by default it is used from 4 ranks on: with 2 ranks half of a token's rows are local and the
+    pull (205.4 ms/step) beats the push and its extra pass through the receive buffer (208.8 ms/step)."""
+    v = os.environ.get("OLB_EP_PUSH", "auto")
+    return n >= 4 if v == "auto" else v != "0"
+
+
+def _scratch(sg: SymmGroup, name: str, shape, dtype) -> torch.Tensor:
+    t = getattr(sg, name, None)
+    if t is None or tuple(t.shape) != tuple(shape) or t.dtype != dtype:
+        t = torch.empty(shape, dtype=dtype, device=sg.device)
+        setattr(sg, name, t)
+    return t
+
+
+def _slot_ids(sg: SymmGroup, T: int, K: int) -> torch.Tensor:
+    t = getattr(sg, "_ep_slot_ids", None)
+    if t is None or tuple(t.shape) != (T, K):
+        t = sg._ep_slot_ids = torch.arange(T * K, dtype=torch.int32, device=sg.device).view(T, K)
+    return t
 
 
 def _pipelined_gather(sg: SymmGroup, peer_ptrs, T, index, out, parts: int):
@@ -96,16 +122,28 @@ class _FusedEPMoEFn(torch.autograd.Function):
             OF.grouped_linear_fwd(xp, wu, index, out=h[:, I:], blk_range=r)
         act = torch.empty((cap, I), dtype=x.dtype, device=x.device)
         C.swiglu_rowscale_fwd(h[:, :I], h[:, I:], index.src_of, index.k_of, w_all, index.meta, act)
-        ys = sg.named("ep_out", (cap, H), x.dtype)
-        OF.grouped_linear_fwd(act, wd, index, out=ys.local)
         rt = sg.named("ep_rowof", (n * T, K), torch.int32)
         rt.local.copy_(index.row_of)
-        sg.barrier(1)
-
         rows = torch.empty((T, K), dtype=torch.int32, device=x.device)
-        C.ep_resolve_rows(rt.ptrs, topk_idx, rank, E_loc, rows)
         out = torch.empty((T, H), dtype=x.dtype, device=x.device)
-        C.ep_combine(ys.ptrs, rows, topk_idx, E_loc, out)
+        if _push_combine(n):
+            # combine all-to-all inside the down projection: its extra warps send every finished row to the owner of
+            # its token (slot [token, k] of the owner's receive buffer) while later tiles run
+            ys = _scratch(sg, "_ep_ys", (cap, H), x.dtype)
+            recv = sg.named("ep_recv", (T, K, H), x.dtype)
+            C.gemm_ep_push(act, wd.view(E_loc * H, I), ys, recv.ptrs, index.meta, index.src_of, index.k_of, cap, H, I, H,
+                           E_loc, T, K, rank, _scratch(sg, "_ep_flags", (cap // 128 + 1,), torch.int32),
+                           OF.status_word(x.device))
+            sg.barrier(1)
+            C.ep_resolve_rows(rt.ptrs, topk_idx, rank, E_loc, rows)
+            slots = torch.where(rows >= 0, _slot_ids(sg, T, K), -1)      # pairs dropped at the owner stay out of the sum
+            C.ep_combine([recv.local.data_ptr()] * n, slots, topk_idx, E_loc, out)
+        else:
+            ys = sg.named("ep_out", (cap, H), x.dtype)
+            OF.grouped_linear_fwd(act, wd, index, out=ys.local)
+            sg.barrier(1)
+            C.ep_resolve_rows(rt.ptrs, topk_idx, rank, E_loc, rows)
+            C.ep_combine(ys.ptrs, rows, topk_idx, E_loc, out)
 
         ctx.save_for_backward(xp, h, act, w_all, wg, wu, wd, rows, topk_idx)
         ctx.index, ctx.sg = index, sg

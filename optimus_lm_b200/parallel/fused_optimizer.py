@@ -87,6 +87,9 @@ class FusedShardedStep:
         step_no = opt.step_id + 1
         clipping = opt._clipping_active()
         total_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        early_sq = opt._join_early_updates()      # layers of unreduced families already updated under the backward
+        if early_sq is not None:
+            total_sq.add_(early_sq)
 
         for sg in {id(g): g for g in self.groups.values()}.values():
             sg.barrier(8)  # every rank's gradients are complete
@@ -106,13 +109,15 @@ class FusedShardedStep:
                         if clip_coef is None:
                             total_sq.add_(partial.sum())
                     else:
-                        if clip_coef is None:
-                            OF.sum_of_squares(fam.grad_part(sl), scale, out=total_sq, accumulate=True)
-                        if mode == 1:
-                            OF.adamw_step(fam.grad_part(sl), fam.master[s0:s1], fam.exp_avg[s0:s1],
-                                          fam.exp_avg_sq[s0:s1], fam.param_part(sl), lr, beta1, beta2, eps, wd, step_no,
-                                          grad_scale=scale, clip_coef=clip_coef,
-                                          skip_weight_update=opt.skip_optimizer_step_weight_update)
+                        g, pp = fam.grad_part(sl), fam.param_part(sl)
+                        for lo, hi in opt._pending_ranges(fam, sl):
+                            if clip_coef is None:
+                                OF.sum_of_squares(g[lo:hi], scale, out=total_sq, accumulate=True)
+                            if mode == 1:
+                                OF.adamw_step(g[lo:hi], fam.master[s0 + lo:s0 + hi], fam.exp_avg[s0 + lo:s0 + hi],
+                                              fam.exp_avg_sq[s0 + lo:s0 + hi], pp[lo:hi], lr, beta1, beta2, eps, wd,
+                                              step_no, grad_scale=scale, clip_coef=clip_coef,
+                                              skip_weight_update=opt.skip_optimizer_step_weight_update)
 
         if clipping:
             run(0, None)

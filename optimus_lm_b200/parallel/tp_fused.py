@@ -7,12 +7,12 @@ collectives and library GEMMs (optimus/models/deepseek_v3/modeling_deepseek_v3.p
 comms_ptfunctions.py:118-156).  Here:
 
 * **all-gather -> GEMM**: every rank publishes its ``x`` rows in a symmetric buffer.  The gate GEMM is launched on
-  a gathered copy ``[T, H]`` that holds only the local rows; two extra warps of each of its CTAs copy the other
+  a gathered copy ``[T, H]`` that holds only the local rows; extra warps of each of its CTAs copy the other
   ranks' rows in over NVLink (plain peer loads, each row crosses once) and count them per 128-row block, and the
   TMA producer waits for a block's count before loading its tiles.  The tile order starts on the local rows, so the
   copy runs underneath the math.  The up GEMM and the backward's weight gradients read the gathered copy locally.
 * **GEMM -> reduce-scatter**: the down projection computes this rank's partial ``[T, H]`` with the next rank's rows
-  first and its own last; its epilogue counts finished tiles per row block, and the same two extra warps copy each
+  first and its own last; its epilogue counts finished tiles per row block, and the same extra warps copy each
   finished row of another rank's block into that rank's receive slot with stores over NVLink while later tiles run.
   After a device-side barrier each rank sums its slots and its own rows (fp32, fixed rank order) from local memory.
 

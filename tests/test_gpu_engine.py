@@ -86,3 +86,27 @@ def test_other_families_train_on_the_kernel_path(model, kw, monkeypatch):
     ref = first_losses(1)
     assert abs(ker[0] - ref[0]) < 3e-2, (ker, ref)
     assert ker[-1] < ker[0] - 0.3, ker
+
+
+def test_updates_under_the_backward_match_the_plain_step():
+    """AdamW of a finished layer on a side stream during the backward (clipping inactive) against the same updates
+    all done in ``step``: same parameters bit for bit, same gradient norm up to summation order."""
+    def run(early):
+        torch.manual_seed(0)
+        eng = TrainEngine(EngineArgs(model_choice=MODEL, dtype="bf16", batch_size=2, context_size=256, optimizer="pgshard",
+                                     warmup_steps=100, lr=1e-3, use_fast_moe=True, use_merged_mlp_in_fast_moe=True,
+                                     use_early_updates=early, config_overrides={"output_router_logits": True}))
+        assert eng._early == early
+        g = torch.Generator().manual_seed(1)
+        out = []
+        for _ in range(4):
+            o = eng.train_step(torch.randint(0, 50280, (2, 256), generator=g))
+            out.append((float(o.loss), float(o.grad_norm)))
+        assert eng.check_device_status() == 0
+        return out, torch.cat([f.flat_param.float().cpu() for f in eng.optimizer.families])
+
+    a, pa = run(True)
+    b, pb = run(False)
+    assert torch.equal(pa, pb)
+    for (la, na), (lb, nb) in zip(a, b):
+        assert la == lb and abs(na - nb) <= 1e-4 * abs(nb), (a, b)

@@ -240,6 +240,38 @@ def test_gemm_with_fused_reduce_scatter_push(n, me, rows, N, K, b_mn, split):
             assert torch.equal(slots[r], part[r * rows:(r + 1) * rows]), r
 
 
+@pytest.mark.parametrize("n,T,E_loc,K,H,I", [(2, 256, 4, 2, 256, 128), (4, 512, 8, 4, 512, 256), (1, 384, 8, 8, 320, 64)])
+def test_grouped_gemm_with_fused_combine_push(n, T, E_loc, K, H, I):
+    """The expert-parallel combine variant of the grouped GEMM with the token owners' receive buffers standing in
+    this GPU's memory: every routed row of the output lands in slot [token, k] of its owner's buffer."""
+    from optimus_lm_b200.ops import extension
+    E = n * E_loc                                            # this "rank" owns experts [E_loc, 2 * E_loc) when n > 1
+    e_start = E_loc if n > 1 else 0
+    g = torch.Generator(device="cuda").manual_seed(3)
+    idx_all = torch.stack([torch.randperm(E, device="cuda", generator=g)[:K] for _ in range(n * T)]).to(torch.int32)
+    cap = OF.moe_capacity_rows(n * T, K, E_loc)
+    ix = OF.MoEIndex(idx_all, e_start, E_loc, cap)
+    act = bf(cap, I, seed=31)
+    wd = bf(E_loc, H, I, seed=32, scale=0.1)
+    ys = torch.empty(cap, H, dtype=torch.bfloat16, device="cuda")
+    recv = [torch.full((T, K, H), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(n)]
+    flags = torch.empty(cap // 128 + 1, dtype=torch.int32, device="cuda")
+    extension().gemm_ep_push(act, wd.view(E_loc * H, I), ys, [t.data_ptr() for t in recv], ix.meta, ix.src_of, ix.k_of,
+                             cap, H, I, H, E_loc, T, K, 0, flags, OF.status_word("cuda"))
+    want = OF.grouped_linear_fwd(act, wd, ix)
+    used = int(ix.meta[0].item()) * 128
+    src = ix.src_of[:used].long()
+    rows = torch.nonzero(src >= 0).flatten()
+    assert rows.numel() == int(((idx_all >= e_start) & (idx_all < e_start + E_loc)).sum().item())
+    assert torch.equal(ys[rows], want[rows])
+    owner, tok, k = src[rows] // T, src[rows] % T, ix.k_of[:used].long()[rows]
+    got = torch.stack(recv)[owner, tok, k]
+    assert torch.equal(got, ys[rows])
+    written = torch.zeros(n, T, K, dtype=torch.bool, device="cuda")
+    written[owner, tok, k] = True
+    assert torch.isnan(torch.stack(recv).float()).all(dim=-1).eq(~written).all()   # nothing else was touched
+
+
 @pytest.mark.parametrize("T,E,K,H,I,e_start,E_loc", [(512, 8, 2, 256, 512, 0, 8), (1000, 16, 4, 128, 256, 4, 8),
                                                      (2048, 64, 8, 512, 256, 0, 64)])
 def test_moe_experts_fwd_bwd(T, E, K, H, I, e_start, E_loc):
