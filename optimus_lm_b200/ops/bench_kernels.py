@@ -87,6 +87,7 @@ def bench_attention():
 def profile_case(name: str, launches: int = 4):
     """A few launches of ONE kernel on operands larger than L2 and well under a GB each: the case to
     put under a hardware profiler (``profile-gemm``, ``profile-grouped``, ``profile-attention``,
+    ``profile-attention-bwd``, ``profile-ep``, ``profile-gemm-allgather``, ``profile-gemm-push``, ``profile-rs-adamw``,
     ``profile-rmsnorm-bwd``)."""
     torch.manual_seed(0)
     if name == "gemm":
@@ -137,6 +138,48 @@ def profile_case(name: str, launches: int = 4):
         def fn():
             y = _FusedEPMoEFn.apply(x, tw, idx, wg, wu, wd, sg, 0, cap)
             y.backward(go)
+    elif name in ("gemm-allgather", "gemm-push"):
+        # The GEMM variants with a collective inside, with the four "peers" standing in this GPU's memory: the stager
+        # warps, the per-row-block counters and the waits run exactly as between GPUs, only NVLink is missing.
+        from ._ext import extension
+        n, rows, N, K, me = 4, 2048, 8192, 4096, 1
+        M = n * rows
+        b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        flags = torch.empty(M // 128, dtype=torch.int32, device="cuda")
+        st = OF.status_word("cuda")
+        if name == "gemm-allgather":
+            slices = [torch.randn(rows, K, device="cuda").to(torch.bfloat16) for _ in range(n)]
+            gathered = torch.empty(M, K, device="cuda", dtype=torch.bfloat16)
+            gathered[me * rows:(me + 1) * rows] = slices[me]
+            ptrs = [t.data_ptr() for t in slices]
+            fn = lambda: extension().gemm_peer(gathered, ptrs, b, c, M, N, K, False, me, flags, st)
+        else:
+            a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+            slots = [torch.empty(rows, N, device="cuda", dtype=torch.bfloat16) for _ in range(n)]
+            ptrs = [t.data_ptr() for t in slots]
+            fn = lambda: extension().gemm_push(a, b, None, 0, c, ptrs, M, N, K, False, me, flags, st)
+    elif name == "rs-adamw":
+        # Reduce-scatter + AdamW + all-gather kernel with a process group of one rank (its only "peer" is itself).
+        import os
+        import torch.distributed as dist
+        from ._ext import extension
+        from ..parallel.symm import SymmGroup
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29578")
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+        sg = SymmGroup.get(dist.group.WORLD)
+        C = extension()
+        nel = 128 * 1024 * 1024
+        grad, param = sg.empty((nel,), torch.bfloat16), sg.empty((nel,), torch.bfloat16)
+        grad.local.normal_(0.0, 1e-3)
+        param.local.normal_(0.0, 0.02)
+        master = param.local.float()
+        m, v = torch.zeros_like(master), torch.zeros_like(master)
+        partial = torch.empty(C.rs_adamw_blocks(nel), dtype=torch.float32, device="cuda")
+        fn = lambda: C.rs_adamw(grad.ptrs, param.ptrs, 0, master, m, v, 4e-4, 0.9, 0.95, 1e-8, 0.1, 1, 1.0, None,
+                                partial, 1, False)
     elif name == "rmsnorm-bwd":
         x = torch.randn(16384, 2048, device="cuda").to(torch.bfloat16).requires_grad_()
         w = torch.ones(2048, device="cuda", dtype=torch.bfloat16, requires_grad=True)
