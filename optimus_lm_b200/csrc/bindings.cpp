@@ -323,6 +323,35 @@ void ce_bwd(const at::Tensor& logits, const at::Tensor& labels, const at::Tensor
         "olb_ce_bwd");
 }
 
+void ce_partial_fwd(const at::Tensor& logits, const at::Tensor& labels, int64_t v_start, at::Tensor& part_max,
+                    at::Tensor& part_sum, at::Tensor& part_tgt) {
+  CHECK_CUDA_BF16(logits);
+  TORCH_CHECK(labels.scalar_type() == at::kLong && labels.is_cuda());
+  CHECK_CUDA_F32(part_max);
+  CHECK_CUDA_F32(part_sum);
+  CHECK_CUDA_F32(part_tgt);
+  c10::cuda::CUDAGuard guard(logits.device());
+  check(olb_ce_partial_fwd(logits.data_ptr(), logits.stride(0), reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()),
+                           static_cast<int>(v_start), part_max.data_ptr<float>(), part_sum.data_ptr<float>(),
+                           part_tgt.data_ptr<float>(), static_cast<int>(logits.size(0)), static_cast<int>(logits.size(1)),
+                           cur_stream()),
+        "olb_ce_partial_fwd");
+}
+
+void ce_partial_bwd(const at::Tensor& logits, const at::Tensor& labels, int64_t v_start, int64_t v_total,
+                    const at::Tensor& lse, const at::Tensor& scale_dev, at::Tensor& dlogits) {
+  CHECK_CUDA_BF16(logits);
+  CHECK_CUDA_F32(scale_dev);
+  CHECK_CUDA_F32(lse);
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(dlogits.stride(0) == logits.stride(0));
+  check(olb_ce_partial_bwd(logits.data_ptr(), logits.stride(0), reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()),
+                           static_cast<int>(v_start), static_cast<int>(v_total), lse.data_ptr<float>(),
+                           scale_dev.data_ptr<float>(), dlogits.data_ptr(), static_cast<int>(logits.size(0)),
+                           static_cast<int>(logits.size(1)), cur_stream()),
+        "olb_ce_partial_bwd");
+}
+
 int64_t sumsq_blocks(int64_t n) { return olb_sumsq_blocks(n); }
 
 // out[0] (+)= sum((grad*scale)^2); `partial` is scratch of at least sumsq_blocks(n) floats.
@@ -398,6 +427,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_combine_bwd", &moe_combine_bwd);
   m.def("ce_fwd", &ce_fwd);
   m.def("ce_bwd", &ce_bwd);
+  m.def("ce_partial_fwd", &ce_partial_fwd);
+  m.def("ce_partial_bwd", &ce_partial_bwd);
   m.def("sumsq_blocks", &sumsq_blocks);
   m.def("sumsq", &sumsq);
   m.def("adamw_step", &adamw_step);

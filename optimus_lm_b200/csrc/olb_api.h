@@ -157,6 +157,12 @@ int olb_ce_fwd(const void* logits, long long ldl, const long long* labels, float
 // dlogits = (softmax - onehot) * (*scale_dev); may alias logits.
 int olb_ce_bwd(const void* logits, long long ldl, const long long* labels, const float* lse, const float* scale_dev,
                void* dlogits, int rows, int V, cudaStream_t stream);
+// Vocabulary-parallel cross entropy: statistics of the slice [v_start, v_start + V) per row (maximum, sum of
+// exponentials relative to it, target logit or 0), and the slice's gradient from the merged log-sum-exp.
+int olb_ce_partial_fwd(const void* logits, long long ldl, const long long* labels, int v_start, float* part_max,
+                       float* part_sum, float* part_tgt, int rows, int V, cudaStream_t stream);
+int olb_ce_partial_bwd(const void* logits, long long ldl, const long long* labels, int v_start, int v_total,
+                       const float* lse, const float* scale_dev, void* dlogits, int rows, int V, cudaStream_t stream);
 
 // ---------------------------------------------------------------- optimizer (adamw.cu)
 typedef struct {

@@ -71,3 +71,40 @@ class ParallelLMHead(nn.Module):
 
     def reset_parameters(self):
         nn.init.normal_(self.weight, mean=0, std=1)
+
+
+class VocabParallelLMHead(nn.Module):
+    """LM head split along the *vocabulary*: every rank multiplies the full hidden state by its ``weight [V/TP, H]``
+    and keeps its slice of the logits.  Used with ``ops.functional.vocab_parallel_cross_entropy`` the
+    ``[tokens, vocabulary]`` logits never cross the links - only per-row softmax statistics are all-reduced - whereas
+    ``ParallelLMHead`` (the reference's layout, optimus/models/common/parallel_modules.py:58-89) all-reduces the
+    full logits.  The gradient of the hidden state is summed over the group in the backward."""
+
+    def __init__(self, hidden_size, vocab_size, bias=False, tensor_parallelism=1, tp_ind=0, group=None):
+        super().__init__()
+        assert not bias, "VocabParallelLMHead does not support bias."
+        assert vocab_size % tensor_parallelism == 0
+        self.hidden_size, self.vocab_size = hidden_size, vocab_size
+        self.tensor_parallelism, self.tp_ind, self.group = tensor_parallelism, tp_ind, group
+        self.vocab_size_per_rank = vocab_size // tensor_parallelism
+        self.vocab_start = tp_ind * self.vocab_size_per_rank
+        self.weight = nn.Parameter(torch.empty((self.vocab_size_per_rank, hidden_size)))
+        self.bias = None
+
+    def forward(self, hidden_states):
+        if self.tensor_parallelism > 1:
+            from .comms_ptfunctions import forward_identity_backward_allreduce
+            hidden_states = forward_identity_backward_allreduce.apply(hidden_states, self.group)
+        return OF.linear(hidden_states, self.weight)
+
+    def loss(self, hidden_states, labels, inplace_backward=False):
+        """Shifted mean cross entropy of this head's logits against global ``labels [B, S]``."""
+        return OF.vocab_parallel_cross_entropy(self.forward(hidden_states), labels, self.vocab_start, self.vocab_size,
+                                               self.group if self.tensor_parallelism > 1 else None, inplace_backward)
+
+    @torch.no_grad()
+    def set_parameters_from_full_module(self, module):
+        self.weight.copy_(module.weight[self.vocab_start:self.vocab_start + self.vocab_size_per_rank])
+
+    def reset_parameters(self):
+        nn.init.normal_(self.weight, mean=0, std=1)

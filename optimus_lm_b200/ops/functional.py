@@ -792,6 +792,81 @@ def shifted_cross_entropy(logits, labels, inplace_backward=False):
     return shifted_cross_entropy_reference(logits, labels)
 
 
+# ------------------------------------------------------------------------------------ vocabulary-parallel CE
+def _merge_ce_stats(part_max, part_sum, part_tgt, group):
+    """Merge per-slice softmax statistics over ``group``: returns the global log-sum-exp and target logit per row."""
+    import torch.distributed as dist
+    gmax = part_max.clone()
+    multi = group is not None and dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+    if multi:
+        dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
+    both = torch.stack((part_sum * torch.exp(part_max - gmax), part_tgt))
+    if multi:
+        dist.all_reduce(both, group=group)
+    return gmax + torch.log(both[0]), both[1]
+
+
+class _VocabParallelCEFn(torch.autograd.Function):
+    """Mean cross entropy of rows whose logits are split over the ranks of ``group`` along the vocabulary."""
+
+    @staticmethod
+    def forward(ctx, logits2d, labels1d, v_start, v_total, group, inplace_backward):
+        rows, V = logits2d.shape
+        valid = (labels1d >= 0) & (labels1d < v_total)
+        if _kernel_ok(logits2d) and logits2d.stride(1) == 1 and logits2d.stride(0) % 8 == 0:
+            C = extension()
+            pm, ps, pt = (torch.empty(rows, dtype=torch.float32, device=logits2d.device) for _ in range(3))
+            C.ce_partial_fwd(logits2d, labels1d, v_start, pm, ps, pt)
+            ctx.kernel = True
+        else:
+            lf = logits2d.float()
+            pm = lf.max(dim=1).values
+            ps = torch.exp(lf - pm[:, None]).sum(dim=1)
+            loc = labels1d - v_start
+            mine = valid & (loc >= 0) & (loc < V)
+            pt = torch.where(mine, lf.gather(1, loc.clamp(0, V - 1)[:, None])[:, 0], torch.zeros_like(pm))
+            ctx.kernel = False
+        lse, tgt = _merge_ce_stats(pm, ps, pt, group)
+        n_valid = valid.sum().to(torch.float32)
+        ctx.save_for_backward(logits2d, labels1d, lse, n_valid)
+        ctx.misc = (v_start, v_total, inplace_backward)
+        return torch.where(valid, lse - tgt, torch.zeros_like(lse)).sum() / n_valid
+
+    @staticmethod
+    def backward(ctx, g):
+        logits2d, labels1d, lse, n_valid = ctx.saved_tensors
+        v_start, v_total, inplace = ctx.misc
+        scale = (g.to(torch.float32) / n_valid).reshape(1).contiguous()
+        if ctx.kernel:
+            d = logits2d if inplace else torch.empty_like(logits2d)
+            extension().ce_partial_bwd(logits2d, labels1d, v_start, v_total, lse, scale, d)
+            return d, None, None, None, None, None
+        V = logits2d.shape[1]
+        valid = (labels1d >= 0) & (labels1d < v_total)
+        p = torch.exp(logits2d.float() - lse[:, None])
+        loc = labels1d - v_start
+        mine = valid & (loc >= 0) & (loc < V)
+        p[mine.nonzero()[:, 0], loc[mine]] -= 1.0
+        p = p * (valid[:, None].float() * scale)
+        return p.to(logits2d.dtype), None, None, None, None, None
+
+
+def vocab_parallel_cross_entropy(logits, labels, v_start: int, v_total: int, group=None, inplace_backward=False,
+                                 shifted=True):
+    """Mean cross entropy for logits ``[B, S, V_local]`` that cover the vocabulary slice ``[v_start, v_start +
+    V_local)`` of ``v_total`` entries on this rank of ``group``; ``labels [B, S]`` hold global ids.  With ``shifted``
+    position ``s`` is scored against ``labels[:, s + 1]`` (the loss of
+    optimus/models/olmoe/modeling_olmoe.py:515-524).  Only ``[rows]``-sized statistics are all-reduced."""
+    B, S, V = logits.shape
+    if shifted:
+        tgt = torch.full((B, S), -100, dtype=torch.long, device=logits.device)
+        tgt[:, :-1] = labels[:, 1:]
+    else:
+        tgt = labels.long()
+    return _VocabParallelCEFn.apply(logits.reshape(B * S, V), tgt.reshape(-1), int(v_start), int(v_total), group,
+                                    inplace_backward)
+
+
 # ------------------------------------------------------------------------------------ optimizer kernels
 def adamw_step_reference(grad, master, m, v, param, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0,
                          clip_coef=None, skip_weight_update=False):
