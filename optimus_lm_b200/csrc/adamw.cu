@@ -83,7 +83,12 @@ __global__ void sum_finalize_kernel(const float* __restrict__ partial, int npart
 template <bool GRAD_FP32, bool PARAM_FP32>
 __global__ void __launch_bounds__(256)
 adamw_kernel(const void* __restrict__ grad_, float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
-             void* __restrict__ param_, long long n, olb_adamw_hparams hp, const float* __restrict__ clip_coef_dev) {
+             void* __restrict__ param_, long long n, olb_adamw_hparams hp, const float* __restrict__ clip_coef_dev,
+             float* __restrict__ norm_partial) {
+  // norm_partial (optional, one float per block): sum of squares of the scaled, unclipped gradients this block saw -
+  // the gradient norm as a by-product of the update's own read of the gradients (fixed grid and strides: the same
+  // bits every run), for the steps in which the update does not depend on the norm.
+  float sq = 0.f;
   const float clip = clip_coef_dev ? *clip_coef_dev : 1.f;
   const float gs = hp.grad_scale * clip;
   const float inv_bc1 = 1.f / hp.bias_correction1;
@@ -110,6 +115,7 @@ adamw_kernel(const void* __restrict__ grad_, float* __restrict__ master, float* 
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float gk = g[k] * gs;
+      sq += (g[k] * hp.grad_scale) * (g[k] * hp.grad_scale);
       mp[k] = hp.beta1 * mp[k] + (1.f - hp.beta1) * gk;
       vp[k] = hp.beta2 * vp[k] + (1.f - hp.beta2) * gk * gk;
       if (!hp.skip_weight_update) {
@@ -131,6 +137,10 @@ adamw_kernel(const void* __restrict__ grad_, float* __restrict__ master, float* 
       o.y = pack_bf16(p[2], p[3]);
       reinterpret_cast<uint2*>(param_)[j] = o;
     }
+  }
+  if (norm_partial != nullptr) {
+    const float r = block_sum(sq);
+    if (threadIdx.x == 0) norm_partial[blockIdx.x] = r;
   }
 }
 
@@ -154,9 +164,15 @@ extern "C" int olb_sum_finalize(const float* partial, int nparts, float* out, in
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
+extern "C" int olb_adamw_blocks(long long n) {
+  long long blocks = (n / 4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  return static_cast<int>(blocks < 1 ? 1 : blocks);
+}
+
 extern "C" int olb_adamw_step(const void* grad, int grad_fp32, float* master, float* m, float* v, void* param,
                               int param_fp32, long long n, const olb_adamw_hparams* hp, const float* clip_coef_dev,
-                              cudaStream_t stream) {
+                              float* norm_partial, cudaStream_t stream) {
   if (n <= 0) return 0;
   // shards are multiples of 512 elements and 16-byte aligned
   if (n % 4 || (reinterpret_cast<uintptr_t>(grad) & 7) || (reinterpret_cast<uintptr_t>(master) & 15) ||
@@ -165,16 +181,14 @@ extern "C" int olb_adamw_step(const void* grad, int grad_fp32, float* master, fl
     return -1;
   if (grad_fp32 && (reinterpret_cast<uintptr_t>(grad) & 15)) return -1;
   if (param_fp32 && (reinterpret_cast<uintptr_t>(param) & 15)) return -1;
-  long long blocks = (n / 4 + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
-  const int grid = static_cast<int>(blocks);
+  const int grid = olb_adamw_blocks(n);
   if (grad_fp32 && param_fp32)
-    adamw_kernel<true, true><<<grid, 256, 0, stream>>>(grad, master, m, v, param, n, *hp, clip_coef_dev);
+    adamw_kernel<true, true><<<grid, 256, 0, stream>>>(grad, master, m, v, param, n, *hp, clip_coef_dev, norm_partial);
   else if (grad_fp32)
-    adamw_kernel<true, false><<<grid, 256, 0, stream>>>(grad, master, m, v, param, n, *hp, clip_coef_dev);
+    adamw_kernel<true, false><<<grid, 256, 0, stream>>>(grad, master, m, v, param, n, *hp, clip_coef_dev, norm_partial);
   else if (param_fp32)
-    adamw_kernel<false, true><<<grid, 256, 0, stream>>>(grad, master, m, v, param, n, *hp, clip_coef_dev);
+    adamw_kernel<false, true><<<grid, 256, 0, stream>>>(grad, master, m, v, param, n, *hp, clip_coef_dev, norm_partial);
   else
-    adamw_kernel<false, false><<<grid, 256, 0, stream>>>(grad, master, m, v, param, n, *hp, clip_coef_dev);
+    adamw_kernel<false, false><<<grid, 256, 0, stream>>>(grad, master, m, v, param, n, *hp, clip_coef_dev, norm_partial);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

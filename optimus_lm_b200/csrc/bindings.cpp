@@ -370,9 +370,17 @@ void sumsq(const at::Tensor& grad, double grad_scale, at::Tensor& partial, at::T
 
 void adamw_step(const at::Tensor& grad, at::Tensor& master, at::Tensor& m, at::Tensor& v, at::Tensor& param, double lr,
                 double beta1, double beta2, double eps, double weight_decay, int64_t step, double grad_scale,
-                const c10::optional<at::Tensor>& clip_coef, bool skip_weight_update) {
+                const c10::optional<at::Tensor>& clip_coef, bool skip_weight_update,
+                const c10::optional<at::Tensor>& norm_out) {
   CHECK_CUDA_F32(master);
   c10::cuda::CUDAGuard guard(master.device());
+  // norm_out (optional, 1 fp32 element): += sum((grad * grad_scale)^2), a by-product of the update's pass
+  at::Tensor partial;
+  const int nb = olb_adamw_blocks(master.numel());
+  if (norm_out.has_value()) {
+    CHECK_CUDA_F32(*norm_out);
+    partial = at::empty({nb}, master.options());
+  }
   olb_adamw_hparams hp;
   hp.lr = static_cast<float>(lr);
   hp.beta1 = static_cast<float>(beta1);
@@ -385,8 +393,11 @@ void adamw_step(const at::Tensor& grad, at::Tensor& master, at::Tensor& m, at::T
   hp.skip_weight_update = skip_weight_update;
   check(olb_adamw_step(grad.data_ptr(), grad.scalar_type() == at::kFloat, master.data_ptr<float>(), m.data_ptr<float>(),
                        v.data_ptr<float>(), param.data_ptr(), param.scalar_type() == at::kFloat, master.numel(), &hp,
-                       opt_ptr<const float>(clip_coef), cur_stream()),
+                       opt_ptr<const float>(clip_coef), norm_out.has_value() ? partial.data_ptr<float>() : nullptr,
+                       cur_stream()),
         "olb_adamw_step");
+  if (norm_out.has_value() && master.numel() > 0)
+    check(olb_sum_finalize(partial.data_ptr<float>(), nb, norm_out->data_ptr<float>(), 1, cur_stream()), "olb_sum_finalize");
 }
 
 void stamp_globaltimer(at::Tensor& slot) {

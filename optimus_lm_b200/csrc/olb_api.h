@@ -179,8 +179,11 @@ int olb_sumsq_blocks(long long n);
 int olb_sum_finalize(const float* partial, int nparts, float* out, int accumulate, cudaStream_t stream);
 // AdamW of the reference form on one flat shard: g = grad*grad_scale*(*clip_coef_dev or 1);
 // m,v update; master -= lr*mhat/(sqrt(vhat)+eps); master += master*(-lr*wd); param = cast(master).
-int olb_adamw_step(const void* grad, int grad_fp32, float* master, float* m, float* v, void* param,
-                   int param_fp32, long long n, const olb_adamw_hparams* hp, const float* clip_coef_dev,
+// `norm_partial` (optional): olb_adamw_blocks(n) floats that receive, per block, the sum of squares of the scaled,
+// unclipped gradients - the gradient norm without a pass of its own.
+int olb_adamw_blocks(long long n);
+int olb_adamw_step(const void* grad, int grad_fp32, float* master, float* m, float* v, void* param, int param_fp32,
+                   long long n, const olb_adamw_hparams* hp, const float* clip_coef_dev, float* norm_partial,
                    cudaStream_t stream);
 
 // ---------------------------------------------------------------- peer-memory kernels (comm_p2p.cu)

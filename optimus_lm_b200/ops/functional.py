@@ -869,9 +869,11 @@ def vocab_parallel_cross_entropy(logits, labels, v_start: int, v_total: int, gro
 
 # ------------------------------------------------------------------------------------ optimizer kernels
 def adamw_step_reference(grad, master, m, v, param, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0,
-                         clip_coef=None, skip_weight_update=False):
+                         clip_coef=None, skip_weight_update=False, norm_out=None):
     """The reference update (optimus/optimizers.py:193-205) in plain torch, in place."""
     g = grad.to(torch.float32) * grad_scale
+    if norm_out is not None:
+        norm_out.add_(g.pow(2).sum())
     if clip_coef is not None:
         g = g * clip_coef
     m.mul_(beta1).add_(g, alpha=1 - beta1)
@@ -886,13 +888,15 @@ def adamw_step_reference(grad, master, m, v, param, lr, beta1, beta2, eps, weigh
 
 
 def adamw_step(grad, master, m, v, param, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0,
-               clip_coef=None, skip_weight_update=False):
+               clip_coef=None, skip_weight_update=False, norm_out=None):
+    """In-place AdamW on one flat range.  ``norm_out`` (1 fp32 element): ``+= sum((grad * grad_scale)^2)``, taken from
+    the update's own read of the gradients instead of a separate pass."""
     if master.is_cuda and use_kernels(master) and master.numel() % 4 == 0:
         extension().adamw_step(grad, master, m, v, param, lr, beta1, beta2, eps, weight_decay, step, grad_scale,
-                               clip_coef, skip_weight_update)
+                               clip_coef, skip_weight_update, norm_out)
     else:
         adamw_step_reference(grad, master, m, v, param, lr, beta1, beta2, eps, weight_decay, step, grad_scale,
-                             clip_coef, skip_weight_update)
+                             clip_coef, skip_weight_update, norm_out)
 
 
 def sum_of_squares(t: torch.Tensor, scale: float = 1.0, out: Optional[torch.Tensor] = None, accumulate=False):

@@ -455,13 +455,18 @@ class _FlatAdamWEngine(Optimizer):
 
         with record_pcl_function("4opt-step_grad-clip"):
             early_sq = self._join_early_updates()
-            norm_sq = self._norm_sq_local()
+            # While clipping is inactive the update does not depend on the norm: the AdamW kernel then sums the
+            # squares of the gradients it reads anyway, and the separate pass over the gradients is skipped.
+            norm_in_update = (not self._clipping_active() and not self.skip_optimizer_step
+                              and type(self)._norm_sq_local is _FlatAdamWEngine._norm_sq_local)
+            norm_sq = torch.zeros(1, dtype=torch.float32, device=self.device) if norm_in_update else self._norm_sq_local()
             if early_sq is not None:
                 norm_sq = norm_sq + early_sq
-            grad_norm = self._global_norm(norm_sq).reshape(())
             clip_coef = None
-            if self._clipping_active():
-                clip_coef = torch.clamp(self.max_grad_norm / (grad_norm + 1e-6), max=1.0).reshape(1).float()
+            if not norm_in_update:
+                grad_norm = self._global_norm(norm_sq).reshape(())
+                if self._clipping_active():
+                    clip_coef = torch.clamp(self.max_grad_norm / (grad_norm + 1e-6), max=1.0).reshape(1).float()
 
         if not self.skip_optimizer_step:
             with record_pcl_function("4opt-step_compute"):
@@ -476,7 +481,10 @@ class _FlatAdamWEngine(Optimizer):
                             OF.adamw_step(g[lo:hi], fam.master[s0:s1], fam.exp_avg[s0:s1], fam.exp_avg_sq[s0:s1],
                                           pp[lo:hi], lr, beta1, beta2, eps, wd, self.step_id + 1,
                                           grad_scale=1.0 / fam.spec.grad_divisor, clip_coef=clip_coef,
-                                          skip_weight_update=self.skip_optimizer_step_weight_update)
+                                          skip_weight_update=self.skip_optimizer_step_weight_update,
+                                          norm_out=norm_sq if norm_in_update else None)
+        if norm_in_update:
+            grad_norm = self._global_norm(norm_sq).reshape(())
         self._finish_early_updates()
         with record_pcl_function("3dp-comms-2param_gather-block"):
             for fam in self.families:

@@ -111,13 +111,14 @@ class FusedShardedStep:
                     else:
                         g, pp = fam.grad_part(sl), fam.param_part(sl)
                         for lo, hi in opt._pending_ranges(fam, sl):
-                            if clip_coef is None:
+                            if clip_coef is None and mode == 0:
                                 OF.sum_of_squares(g[lo:hi], scale, out=total_sq, accumulate=True)
-                            if mode == 1:
+                            if mode == 1:   # without clipping the norm is a by-product of the update's pass
                                 OF.adamw_step(g[lo:hi], fam.master[s0 + lo:s0 + hi], fam.exp_avg[s0 + lo:s0 + hi],
                                               fam.exp_avg_sq[s0 + lo:s0 + hi], pp[lo:hi], lr, beta1, beta2, eps, wd,
                                               step_no, grad_scale=scale, clip_coef=clip_coef,
-                                              skip_weight_update=opt.skip_optimizer_step_weight_update)
+                                              skip_weight_update=opt.skip_optimizer_step_weight_update,
+                                              norm_out=total_sq if clip_coef is None else None)
 
         if clipping:
             run(0, None)

@@ -449,6 +449,10 @@ def test_adamw_and_sumsq():
     assert abs(s.item() - (g.float() * 0.5).pow(2).sum().item()) / s.item() < 1e-5
     s2 = OF.sum_of_squares(g, 0.5)
     assert torch.equal(s, s2)
+    # the norm as a by-product of the update's own pass over the gradients (unclipped, scaled)
+    acc = torch.full((1,), 3.0, device="cuda")
+    OF.adamw_step(g, master, m, v, p, 4e-4, 0.9, 0.95, 1e-8, 0.1, 4, grad_scale=0.5, norm_out=acc)
+    assert abs(acc.item() - 3.0 - s.item()) / s.item() < 1e-5
 
 
 def test_kernels_package_entry_points():
