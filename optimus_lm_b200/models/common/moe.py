@@ -141,7 +141,20 @@ class SparseMoeBlock(nn.Module):
         if self.merged:
             wg, wu, wd = self.experts.weights()
             return OF.moe_experts(x, w.float() if x.is_cuda else w, idx, wg, wu, wd, self.expert_start_idx, cap)
+        if self._grouped_per_expert(x):
+            # per-expert parameters on the fast path: stack them (about 0.1 ms of copies per layer) and run the grouped
+            # GEMM pipeline; autograd hands each expert its slice of the stacked weight gradient.  The reference
+            # gives its grouped kernels an array of the experts' weight pointers instead
+            # (optimus/kernels/grouped_linear_forward.py:7-102).
+            wg = torch.stack([e.gate_proj.weight for e in self.experts])
+            wu = torch.stack([e.up_proj.weight for e in self.experts])
+            wd = torch.stack([e.down_proj.weight for e in self.experts])
+            return OF.moe_experts(x, w.float(), idx, wg, wu, wd, self.expert_start_idx, cap)
         return _experts_loop(self.experts, x, w, idx, self.expert_start_idx)
+
+    def _grouped_per_expert(self, x) -> bool:
+        return (getattr(self, "fast", False) and x.is_cuda and x.dtype == torch.bfloat16
+                and self.hidden_size % 64 == 0 and self.intermediate_size % 64 == 0 and OF.use_kernels(x))
 
     def _expert_block(self, hidden2d, idx, w):
         pmap = self.pmap
@@ -161,7 +174,7 @@ class SparseMoeBlock(nn.Module):
         i_all = forward_allgather_backward_split.apply(idx, pmap.ep_ind, ep, g)
         x_all = forward_identity_backward_synchronize.apply(x_all, g)
         cap = None
-        if self.merged and x_all.is_cuda:
+        if x_all.is_cuda and (self.merged or self._grouped_per_expert(x_all)):
             cap = OF.moe_capacity_rows(T * ep, self.num_experts_per_tok, self.num_experts_per_rank, ep,
                                        self.capacity_factor)
         y_all = self._local_experts(x_all, w_all, i_all, cap)
@@ -218,3 +231,4 @@ class FastOlmoeParallelSparseMoeBlock(SparseMoeBlock):
 
     def __init__(self, config, pmap=None):
         super().__init__(config, pmap, merged=bool(config.use_merged_mlp_in_fast_moe))
+        self.fast = True

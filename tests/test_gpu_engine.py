@@ -110,3 +110,20 @@ def test_updates_under_the_backward_match_the_plain_step():
     assert torch.equal(pa, pb)
     for (la, na), (lb, nb) in zip(a, b):
         assert la == lb and abs(na - nb) <= 1e-4 * abs(nb), (a, b)
+
+
+def test_per_expert_fast_path_matches_merged_weights():
+    """``--use_fast_moe`` without merged weights stacks the experts' parameters and runs the same grouped GEMMs: the
+    same losses as the merged layout (initial values depend on a tensor's serial name only)."""
+    def run(merged):
+        torch.manual_seed(0)
+        eng = TrainEngine(EngineArgs(model_choice=MODEL, dtype="bf16", batch_size=2, context_size=256, optimizer="pgshard",
+                                     warmup_steps=100, lr=1e-3, use_fast_moe=True, use_merged_mlp_in_fast_moe=merged,
+                                     config_overrides={"output_router_logits": True}))
+        g = torch.Generator().manual_seed(1)
+        out = [float(eng.train_step(torch.randint(0, 50280, (2, 256), generator=g)).loss) for _ in range(4)]
+        assert eng.check_device_status() == 0
+        return out
+
+    a, b = run(False), run(True)
+    assert all(abs(x - y) < 2e-2 for x, y in zip(a, b)), (a, b)
