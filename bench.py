@@ -16,6 +16,10 @@ with CUDA events around exactly ``--steps`` steps (max over ranks).  ``e2e`` tim
 steps through ``TrainEngine.train_step`` with the per-step host->device copy of the tokens from
 pinned memory and a device->host read of the loss inside the timed region.
 
+``--config`` selects one of the further configurations (OLMoE data parallel, OLMo-1B data parallel with the sharded
+AdamW, OLMoE pipeline x expert parallel with 1F1B, reduced DeepSeek-V3 expert parallel); their JSON line carries their
+own metric name.
+
 ``--impl reference`` runs the reference implementation (installed under baseline/_ref) for the
 same metric; see baseline/run_reference.py.
 """
@@ -37,6 +41,36 @@ SEQ_LEN = 4096
 MICRO_BATCH = 4
 VOCAB = 50304
 METRIC = "OLMoE-1B-7B EP train tokens/s (device-timed, max over ranks)"
+
+
+def named_config(name: str, n: int):
+    """The other training configurations this repository is measured on, selected with ``--config`` (the default,
+    ``olmoe_ep``, is the headline).  Returns (engine keyword arguments, micro-batch, sequence length, vocabulary,
+    metric name, parallelism tag)."""
+    moe = dict(use_fast_moe=True, use_merged_mlp_in_fast_moe=True)
+    if name == "olmoe_ep":
+        return (dict(model_choice=MODEL_CHOICE, expert_parallelism=n, data_parallelism=1, optimizer="pgshard", **moe),
+                MICRO_BATCH, SEQ_LEN, VOCAB, METRIC, f"ep{n}")
+    if name == "olmoe_dp":          # the same model, data parallel only (every GPU holds all 64 experts)
+        return (dict(model_choice=MODEL_CHOICE, expert_parallelism=1, data_parallelism=n, optimizer="pgshard", **moe),
+                MICRO_BATCH, SEQ_LEN, VOCAB, "OLMoE-1B-7B DP train tokens/s (device-timed, max over ranks)", f"dp{n}")
+    if name == "olmo1b_dp":         # OLMo-1B dense, ZeRO-1 sharded AdamW, sequence 2048, micro-batch 8
+        return (dict(model_choice="allenai/OLMo-1B-hf", data_parallelism=n, optimizer="shard"),
+                8, 2048, 50304, "OLMo-1B DP train tokens/s (device-timed, max over ranks)", f"dp{n}")
+    if name == "olmoe_pp_ep":       # 1F1B pipeline over N/2 stages (N at 2 GPUs) x EP pairs, 8 micro-batches of 4 sequences
+        ep = 2 if n >= 4 else 1
+        pp = n // ep
+        assert pp >= 2 and 16 % pp == 0, "olmoe_pp_ep needs 2, 4 or 8 GPUs"
+        return (dict(model_choice=MODEL_CHOICE, pipeline_parallelism=pp, expert_parallelism=ep, data_parallelism=1,
+                     pp_scheme="1f1b", micro_batch_size=MICRO_BATCH, optimizer="pgshard", **moe),
+                8 * MICRO_BATCH, SEQ_LEN, VOCAB, "OLMoE-1B-7B PPxEP 1F1B train tokens/s (device-timed, max over ranks)",
+                f"pp{pp}xep{ep}")
+    if name == "dsv3_reduced_ep":   # 4 layers (1 dense + 3 MoE) of DeepSeek-V3 at full width: 34 G expert parameters
+        assert n == 8, "the reduced DeepSeek-V3 holds 34 G expert parameters: it needs the memory of 8 GPUs"
+        return (dict(model_choice="deepseek-ai/DeepSeek-V3--L4-DL1", expert_parallelism=n, data_parallelism=1,
+                     optimizer="pgshard", init_std=0.006, **moe),
+                1, SEQ_LEN, 129280, "reduced DeepSeek-V3 EP train tokens/s (device-timed, max over ranks)", f"ep{n}")
+    raise SystemExit(f"unknown --config {name}")
 
 
 class ClockSampler:
@@ -113,21 +147,23 @@ def run_ours(opts):
     dev = torch.device("cuda", torch.cuda.current_device())
     proxy = _ext.enable_launch_counting()
 
-    overrides = {"output_router_logits": True}
+    kw, cfg_mb, cfg_seq, vocab, metric, par_tag = named_config(opts.config, n)
+    if opts.config != "olmoe_ep":
+        opts.micro_batch, opts.seq_len = cfg_mb, cfg_seq
+    overrides = {"output_router_logits": True} if "OLMoE" in kw["model_choice"] else {}
     if opts.layers:
         overrides["num_hidden_layers"] = opts.layers  # debugging only; reported in the config
-    args = EngineArgs(model_choice=MODEL_CHOICE, dtype="bf16", expert_parallelism=n, data_parallelism=1,
-                      batch_size=opts.micro_batch, context_size=opts.seq_len,
-                      optimizer="pgshard", warmup_steps=2500, use_fast_moe=True, use_merged_mlp_in_fast_moe=True,
+    args = EngineArgs(dtype="bf16", batch_size=opts.micro_batch, context_size=opts.seq_len, warmup_steps=2500,
                       use_fused_ep_alltoall=not opts.nccl_only, use_fused_optimizer=not opts.nccl_only,
-                      config_overrides=overrides)
+                      config_overrides=overrides, **kw)
     engine = TrainEngine(args)
     tokens_per_step = engine.tokens_per_step()
 
     # synthetic data: one pinned host batch per step, uniform-random token ids, per-rank seed
-    g = torch.Generator().manual_seed(1234 + rank)
+    # (ranks of one pipeline or tensor-parallel group read the same batch: the seed is the data-parallel index)
+    g = torch.Generator().manual_seed(1234 + (rank if opts.config == "olmoe_ep" else engine.pmap.dpep_ind))
     total = opts.warmup + 2 * opts.steps
-    host_batches = [torch.randint(0, VOCAB, (opts.micro_batch, opts.seq_len), generator=g, dtype=torch.int64).pin_memory()
+    host_batches = [torch.randint(0, vocab, (opts.micro_batch, opts.seq_len), generator=g, dtype=torch.int64).pin_memory()
                     for _ in range(total)]
     dev_batches = [b.to(dev) for b in host_batches[:opts.warmup + opts.steps]]
 
@@ -163,14 +199,14 @@ def run_ours(opts):
     barrier()
     dev_ms = ev0.elapsed_time(ev1)
     launches = proxy.launches - launches0
-    last_loss = out.loss.item()
+    last_loss = out.loss.item() if out.loss is not None else None     # pipeline: only the last stage sees the loss
 
     # ---- end-to-end region: H2D of the tokens and D2H of the loss every step
     barrier()
     t0 = time.perf_counter()
     for i in range(opts.steps):
         out = step(host_batches[opts.warmup + opts.steps + i])
-        e2e_loss = out.loss.item()
+        e2e_loss = out.loss.item() if out.loss is not None else float(out.grad_norm)   # a device->host read either way
     barrier()
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else None
@@ -184,7 +220,7 @@ def run_ours(opts):
         # a kernel reported a timeout or a buffer overflow (e.g. more routed rows than the expert-parallel
         # receive buffers hold): the step did not do all of its work, so there is no number to report
         if rank == 0:
-            print(json.dumps({"metric": METRIC, "error": f"device status word = {status} on some rank; run invalid",
+            print(json.dumps({"metric": metric, "error": f"device status word = {status} on some rank; run invalid",
                               "n_gpus": n, "impl": "optimus_lm_b200"}), flush=True)
         if dist.is_initialized():
             dist.barrier()
@@ -195,12 +231,13 @@ def run_ours(opts):
         e2e_value = tokens_per_step * opts.steps / e2e_s
         h2d = opts.micro_batch * opts.seq_len * 8
         res = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": n, "steps": opts.steps,
+            "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": n, "steps": opts.steps,
             "warmup": opts.warmup, "ms_per_step": dev_ms / opts.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"model": "OLMoE-1B-7B" + (f" (reduced to {opts.layers} layers)" if opts.layers else ""),
-                       "global_batch": opts.micro_batch * n, "seq_len": opts.seq_len,
-                       "parallelism": f"ep{n}" if n > 1 else "ep1", "optimizer": "pgshard (fp32 master + moments)",
+            "config": {"model": ("OLMoE-1B-7B" if opts.config == "olmoe_ep" else kw["model_choice"])
+                       + (f" (reduced to {opts.layers} layers)" if opts.layers else ""),
+                       "global_batch": tokens_per_step // opts.seq_len, "seq_len": opts.seq_len,
+                       "parallelism": par_tag, "optimizer": kw["optimizer"] + " (fp32 master + moments)",
                        "micro_batch_per_gpu": opts.micro_batch, "ep_transport": "nccl all-gather/reduce-scatter" if opts.nccl_only else "fused all-to-all",
                        "l2": "activations and weights of every step are far larger than the 126 MB L2; no flush"},
             "clocks": clocks,
@@ -225,6 +262,9 @@ def main():
     ap.add_argument("--seq-len", dest="seq_len", type=int, default=SEQ_LEN)
     ap.add_argument("--micro-batch", dest="micro_batch", type=int, default=MICRO_BATCH)
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers (the result is then not the headline config)")
+    ap.add_argument("--config", type=str, default="olmoe_ep",
+                    choices=["olmoe_ep", "olmoe_dp", "olmo1b_dp", "olmoe_pp_ep", "dsv3_reduced_ep"],
+                    help="olmoe_ep is the headline; the others are the further measured configurations")
     ap.add_argument("--nccl-only", dest="nccl_only", action="store_true",
                     help="use the NCCL all-gather/reduce-scatter EP transport and NCCL optimizer collectives")
     opts = ap.parse_args()
