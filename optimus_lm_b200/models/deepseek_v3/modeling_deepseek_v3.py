@@ -245,6 +245,7 @@ class DeepseekV3ParallelMoE(nn.Module):
     # routed-expert execution and EP transports are shared with the OLMoE block
     _local_experts = SparseMoeBlock._local_experts
     _expert_block = SparseMoeBlock._expert_block
+    _grouped_per_expert = SparseMoeBlock._grouped_per_expert
 
     def _block(self, hidden_states, topk_indices, topk_weights):
         shape = hidden_states.shape
