@@ -1,0 +1,62 @@
+"""Small host-side checks: the named benchmark configurations, the bookkeeping of optimizer updates that ran early,
+and the gradient norm taken as a by-product of the AdamW pass."""
+import importlib.util
+import os
+
+import pytest
+import torch
+
+from optimus_lm_b200.ops import functional as OF
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _bench():
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(ROOT, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_named_configurations():
+    b = _bench()
+    kw, mb, seq, vocab, metric, tag = b.named_config("olmoe_ep", 8)
+    assert (kw["expert_parallelism"], kw["optimizer"], mb, seq, vocab, tag) == (8, "pgshard", 4, 4096, 50304, "ep8")
+    assert metric == b.METRIC
+    kw, mb, seq, vocab, metric, tag = b.named_config("olmo1b_dp", 8)
+    assert (kw["data_parallelism"], kw["optimizer"], mb, seq, tag) == (8, "shard", 8, 2048, "dp8")
+    kw, mb, seq, _, _, tag = b.named_config("olmoe_pp_ep", 8)
+    assert (kw["pipeline_parallelism"], kw["expert_parallelism"], kw["micro_batch_size"], mb, tag) == (4, 2, 4, 32, "pp4xep2")
+    kw, *_ , tag = b.named_config("olmoe_pp_ep", 2)
+    assert (kw["pipeline_parallelism"], kw["expert_parallelism"], tag) == (2, 1, "pp2xep1")
+    with pytest.raises(AssertionError):
+        b.named_config("dsv3_reduced_ep", 2)      # 34 G expert parameters do not fit fewer than 8 GPUs
+    with pytest.raises(SystemExit):
+        b.named_config("nope", 1)
+
+
+def test_pending_ranges_are_the_complement_of_early_updates():
+    from optimus_lm_b200.optimizers import _FlatAdamWEngine, _Slice
+
+    class Fam:
+        pass
+
+    eng = _FlatAdamWEngine.__new__(_FlatAdamWEngine)
+    fam, sl = Fam(), _Slice(0, 1000, 1000, 0)
+    assert eng._pending_ranges(fam, sl) == [(0, 1000)]
+    eng._early_done = {id(fam): [(600, 800), (100, 200)]}
+    assert eng._pending_ranges(fam, sl) == [(0, 100), (200, 600), (800, 1000)]
+    eng._early_done = {id(fam): [(0, 400), (400, 1000)]}
+    assert eng._pending_ranges(fam, sl) == []
+
+
+def test_adamw_norm_by_product_on_the_plain_path():
+    torch.manual_seed(0)
+    n = 64
+    g = torch.randn(n)
+    master, m, v = torch.randn(n), torch.zeros(n), torch.zeros(n)
+    p = master.clone()
+    acc = torch.full((1,), 2.0)
+    OF.adamw_step(g, master, m, v, p, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, grad_scale=0.5, norm_out=acc)
+    assert torch.allclose(acc, 2.0 + (g * 0.5).pow(2).sum().reshape(1))
+    assert torch.equal(p, master)
