@@ -16,7 +16,6 @@ the device; the loss and the gradient norm are returned as device tensors.
 """
 from __future__ import annotations
 
-import dataclasses
 import math
 import os
 from dataclasses import dataclass, field

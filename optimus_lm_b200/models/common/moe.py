@@ -24,7 +24,6 @@ Execution:
 from __future__ import annotations
 
 import torch
-import torch.nn.functional as F
 from torch import nn
 from torch.utils.checkpoint import checkpoint as torch_activation_checkpoint
 

@@ -35,8 +35,8 @@ process group; the owner keeps fp32 master / exp_avg / exp_avg_sq for its slices
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass, field
-from typing import List, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
 
 import torch
 import torch.distributed as dist

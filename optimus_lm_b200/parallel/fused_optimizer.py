@@ -20,10 +20,9 @@ fused pass follows with the coefficient, at the cost of reading the peers' gradi
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict, Optional
 
 import torch
-import torch.distributed as dist
 
 from ..ops import functional as OF
 from ..ops._ext import extension
