@@ -35,6 +35,7 @@ process group; the owner keeps fp32 master / exp_avg / exp_avg_sq for its slices
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import List, Optional, Tuple
 
@@ -45,7 +46,9 @@ from torch.optim import Optimizer
 from .ops import functional as OF
 from .profilers import record_pcl_function
 
-CHUNK_ELEMS = 128 * 1024 * 1024
+# chunk size of the sub-sharded classes and of the chunked all-reduce (reference: 128Mi elements);
+# OLB_OPT_CHUNK_ELEMS overrides it, e.g. to exercise several chunks on a small model
+CHUNK_ELEMS = int(os.environ.get("OLB_OPT_CHUNK_ELEMS", str(128 * 1024 * 1024)))
 
 
 def chunked_allreduce_wrapper(tensor, group=None, barrier=False, chunk=CHUNK_ELEMS):

@@ -8,7 +8,7 @@ import torch
 
 DSV3 = "deepseek-ai/DeepSeek-V3--L3-DL1-N16-K2-MI64-A4-SE1-H128-I256"
 LLAMA = "meta-llama/Llama-3.2-1B--L2-H256-I512"
-OLMO = "allenai/OLMo-1B-hf--L4-H128-I256"
+OLMO = "allenai/OLMo-1B-hf--L4"      # OLMo tags carry no width: it is reduced through config overrides below
 OVR = {"vocab_size": 512, "max_position_embeddings": 64}
 STEPS, MBS, SEQ = 5, 2, 64
 
@@ -21,6 +21,8 @@ def _tokens(n_seq):
 def _engine(model, **kw):
     from optimus_lm_b200.engine import EngineArgs, TrainEngine
     ovr = dict(OVR)
+    if model == OLMO:
+        ovr.update(hidden_size=128, intermediate_size=256, num_attention_heads=4, num_key_value_heads=4)
     ovr.update(kw.pop("config_overrides", {}))
     args = EngineArgs(model_choice=model, dtype="fp32", context_size=SEQ, lr=1e-3, warmup_steps=0,
                       config_overrides=ovr, use_fused_ep_alltoall=False, **kw)

@@ -80,9 +80,12 @@ def _dp_worker(rank, world, optimizer, ref):
 
 
 @pytest.mark.parametrize("optimizer", ["unsharded", "shard", "pgshard", "subshard", "pgsubshard"])
-def test_dp2_matches_serial(optimizer):
+def test_dp2_matches_serial(optimizer, monkeypatch):
     from dist_utils import run_distributed
     ref = _serial_losses(2 * MBS)
+    # the spawned ranks read the chunk size of the sub-sharded classes from the environment: several small chunks
+    # instead of one 128Mi-element chunk that is almost all padding for this model
+    monkeypatch.setenv("OLB_OPT_CHUNK_ELEMS", str(256 * 1024))
     run_distributed(_dp_worker, 2, optimizer, ref)
 
 
