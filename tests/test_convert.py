@@ -14,7 +14,7 @@ from optimus_lm_b200.engine import init_weights
 
 OLMOE = "allenai/OLMoE-1B-7B-0924--L2-SH0.0625-SA0.25-SE0.125-SC0.25-SI0.25"
 LLAMA = "meta-llama/Llama-3.2-1B--L2-H256-I512"
-OLMO = "allenai/OLMo-1B-hf--L2-H128-I256"
+OLMO = "allenai/OLMo-1B-hf--L2"            # OLMo tags carry no width (reference grammar): full-width layers
 DSV3 = "deepseek-ai/DeepSeek-V3--L3-DL1-N16-K2-MI64-A4-SE1-H128-I256"   # MLA, sigmoid group-limited router, YaRN
 
 

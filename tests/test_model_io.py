@@ -17,7 +17,7 @@ from optimus_lm_b200.mapper import ParallelDpPpEpTpMapper
 OLMOE = "allenai/OLMoE-1B-7B-0924--L4-SH0.0625-SA0.25-SE0.125-SC0.25-SI0.25"
 DSV3 = "deepseek-ai/DeepSeek-V3--L3-DL1-N8-K2-MI64-A4-SE1-H128-I256"
 LLAMA = "meta-llama/Llama-3.1-8B--L2-H256-I512"
-OLMO = "allenai/OLMo-1B-hf--L4-H128-I256"
+OLMO = "allenai/OLMo-1B-hf--L2"            # OLMo tags carry no width (reference grammar): full-width layers
 
 LAYOUTS = [
     (OLMOE, dict(pp=2, ep=2, tp=1, vpp=1, merged=False)),
