@@ -231,6 +231,36 @@ class ScalarLog:
                 self.tb.add_scalar(k, float(v), int(step))
 
 
+DEVICE_STATUS_NAMES = {1: "ST_TIMEOUT_FULL (GEMM consumer waited for an operand stage)",
+                       2: "ST_TIMEOUT_EMPTY (GEMM producer waited for a free stage)",
+                       3: "ST_TIMEOUT_ACC_FULL (epilogue waited for an accumulator)",
+                       4: "ST_TIMEOUT_ACC_EMPTY (tensor-core warp waited for a drained accumulator)",
+                       5: "ST_TIMEOUT_PEER (a wait on another GPU's flag ran out: a peer is late or gone)",
+                       6: "ST_OVERFLOW (an expert-parallel receive buffer limited by moe_capacity_factor was too small; "
+                          "moe_capacity_factor 0 sizes the buffers from the routed counts and cannot overflow)",
+                       7: "ST_BAD_ARG"}
+EXIT_DEVICE_STATUS = 3
+
+
+def device_status_failed(engine, rank, pmap, device) -> bool:
+    """Read (and clear) this rank's device status word and agree on it over all ranks.  True when any rank's kernels
+    reported a timeout or an overflow since the last check: the steps since then did not do all of their work, so the
+    caller stops without writing a checkpoint."""
+    mine = engine.check_device_status()
+    worst = torch.tensor([float(mine)], device=device)
+    if dist.is_initialized():
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    if worst.item() == 0:
+        return False
+    if mine:
+        print(f"Device status word {mine} = {DEVICE_STATUS_NAMES.get(mine, 'unknown code')} on rank {rank:4d} "
+              f"(dp_ind {pmap.dp_ind}, pp_ind {pmap.pp_ind}, ep_ind {pmap.ep_ind}, tp_ind {pmap.tp_ind}); "
+              "stopping, no checkpoint is written", flush=True)
+    elif rank == 0:
+        print(f"Device status word {int(worst.item())} reported by another rank; stopping", flush=True)
+    return True
+
+
 def report_soft_failures(flags, pmap, rank, world_size):
     """Append the nodes of the flagged ranks to launch_info/<job>/failed_soft_nodes.txt."""
     if rank != 0:
@@ -360,6 +390,7 @@ def main(argv=None):
     scalar_log = ScalarLog(args.exp_dir) if (args.enable_tb_logging and is_logger and args.exp_dir) else None
     flops_per_seq = model.get_flops(args.context_size) if hasattr(model, "get_flops") else 0
     last_log_time = time.time()
+    exit_code = 0
     while train_step_id < train_steps:
         if train_step_id == args.exit_steps:
             break
@@ -389,8 +420,7 @@ def main(argv=None):
             bad = (~torch.isfinite(lgn.float())).float()
             if loss is not None:
                 bad = torch.maximum(bad, (~torch.isfinite(loss.detach().float())).float())
-            status = engine.check_device_status()
-            flags[rank] = bad.reshape(()) + (1.0 if status else 0.0)
+            flags[rank] = bad.reshape(())
             if dist.is_initialized():
                 dist.all_reduce(flags)
             if flags.sum().item() > 0:
@@ -398,9 +428,14 @@ def main(argv=None):
                     print("Softnode failure detected", flush=True)
                 if flags[rank] > 0:
                     print(f"Node : {pmap.node}, Rank : {rank:4d}, dp_ind : {pmap.dp_ind:3d}, pp_ind : {pmap.pp_ind:3d}, "
-                          f"ep_ind : {pmap.ep_ind:3d}, tp_ind : {pmap.tp_ind:2d}, device status : {status}", flush=True)
+                          f"ep_ind : {pmap.ep_ind:3d}, tp_ind : {pmap.tp_ind:2d}", flush=True)
                 report_soft_failures(flags.cpu(), pmap, rank, world_size)
                 failure = True
+            # A kernel that gave up (bounded wait ran out, capacity-limited buffer too small) says nothing about the
+            # health of this node: it gets its own message and exit code and never enters the soft-failure node list.
+            if device_status_failed(engine, rank, pmap, device):
+                failure = True
+                exit_code = EXIT_DEVICE_STATUS
             if args.enable_bad_grad_check and not torch.isfinite(lgn).item():
                 debug_dir = os.path.join(args.exp_dir, os.getenv("PBS_JOBID", "0"))
                 os.makedirs(debug_dir, exist_ok=True)
@@ -411,6 +446,7 @@ def main(argv=None):
                         if p.grad is not None:
                             fh.write(f"{n:45s}, {p.grad.float().norm().item():.6f}\n")
         if failure:
+            exit_code = exit_code or 2
             break
 
         if logging_step:
@@ -444,14 +480,21 @@ def main(argv=None):
                     profiler.print_timing_table(sort_by_name=True)
 
         # ------------------------------------------------------------------ checkpoints
-        if args.enable_checkpointing and ((train_step_id + 1) % (args.checkpoint_steps * args.opt_grad_acc_steps) == 0):
+        hot_due = args.enable_checkpointing and ((train_step_id + 1) % (args.checkpoint_steps * args.opt_grad_acc_steps) == 0)
+        last_due = args.enable_checkpointing and train_step_id == train_steps - 1
+        if (hot_due or last_due) and not (logging_step or args.enable_bad_grad_check):
+            # the status word is sticky: read it before anything is written (on logging steps it was read above)
+            if device_status_failed(engine, rank, pmap, device):
+                exit_code = EXIT_DEVICE_STATUS
+                break
+        if hot_due:
             ckpt.save_checkpoint(args.exp_dir, model, optimizer, pmap, train_step_id, optimizer_sharded=sharded_opt,
                                  dp_staggered=args.dp_staggered_checkpointing, rank=rank)
             if not args.disable_cold_checkpointing:
                 ckpt.save_checkpoint(args.exp_dir, model, optimizer, pmap, train_step_id, model_only=True,
                                      name=ckpt.cold_checkpoint_name(train_step_id, pmap, args.batch_size, args.context_size),
                                      optimizer_sharded=sharded_opt, dp_staggered=args.dp_staggered_checkpointing, rank=rank)
-        if args.enable_checkpointing and train_step_id == train_steps - 1:
+        if last_due:
             ckpt.save_checkpoint(args.exp_dir, model, optimizer, pmap, train_step_id, name="main",
                                  optimizer_sharded=sharded_opt, dp_staggered=args.dp_staggered_checkpointing, rank=rank)
         train_step_id += 1
@@ -463,7 +506,7 @@ def main(argv=None):
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
-    return 0
+    return exit_code
 
 
 if __name__ == "__main__":

@@ -156,17 +156,20 @@ def load_checkpoint(exp_dir, model, optimizer, pmap, *, name=None, optimizer_sha
             ck = torch.load(model_file(d, pmap), map_location="cpu", weights_only=True)
             model.load_state_dict(ck["state_dict"])
             step_t[0] = int(ck["train_step_id"])
-        elif use_allreduce_in_broadcast:
+        # everything the state dict holds travels: parameters and persistent buffers (DeepSeek-V3's routing bias is a
+        # buffer that training may modify; replicas that kept their own copy would route differently after a resume)
+        tensors = [t for t in model.state_dict().values() if torch.is_tensor(t)]
+        if pmap.dp_ind != 0 and use_allreduce_in_broadcast:
             with torch.no_grad():
-                for p in model.parameters():
-                    p.data.zero_()
+                for t in tensors:
+                    t.zero_()
         if pmap.data_parallelism > 1:
             src = pmap.mp_rank  # global rank of the dp_ind == 0 member of this DP group
-            for p in model.parameters():
+            for t in tensors:
                 if use_allreduce_in_broadcast:
-                    dist.all_reduce(p.data, group=pmap.dp_group)
+                    dist.all_reduce(t, group=pmap.dp_group)
                 else:
-                    dist.broadcast(p.data, src=src, group=pmap.dp_group)
+                    dist.broadcast(t, src=src, group=pmap.dp_group)
             if use_allreduce_in_broadcast:
                 dist.all_reduce(step_t, group=pmap.dp_group)
             else:

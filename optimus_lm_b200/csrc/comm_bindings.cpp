@@ -25,11 +25,11 @@ std::vector<void*> mptrs(const std::vector<int64_t>& v) {
 }
 
 void symm_barrier(const std::vector<int64_t>& pads, int64_t my_rank, int64_t channel, int64_t epoch,
-                  const c10::optional<at::Tensor>& status) {
+                  const c10::optional<at::Tensor>& status, int64_t wait_limit_ns) {
   auto p = mptrs(pads);
   check(olb_symm_barrier(p.data(), static_cast<int>(my_rank), static_cast<int>(p.size()), static_cast<int>(channel),
                          static_cast<unsigned>(epoch), status.has_value() ? status->data_ptr<int>() : nullptr,
-                         cur_stream()),
+                         static_cast<unsigned long long>(wait_limit_ns), cur_stream()),
         "olb_symm_barrier");
 }
 
@@ -255,7 +255,9 @@ void rs_adamw(const std::vector<int64_t>& peer_grad, const std::vector<int64_t>&
 }  // namespace
 
 void register_comm(pybind11::module& m) {
-  m.def("symm_barrier", &symm_barrier);
+  namespace py = pybind11;
+  m.def("symm_barrier", &symm_barrier, py::arg("pads"), py::arg("my_rank"), py::arg("channel"), py::arg("epoch"),
+        py::arg("status"), py::arg("wait_limit_ns") = 0);
   m.def("ep_gather_rows", &ep_gather_rows);
   m.def("ep_resolve_rows", &ep_resolve_rows);
   m.def("ep_combine", &ep_combine);

@@ -43,7 +43,8 @@ __device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* addr) {
 }
 
 // signal layout on every rank: pad[channel * MAX_PEERS + src_rank]
-__global__ void symm_barrier_kernel(PeerPtrsMut pads, int my_rank, int n, int channel, unsigned epoch, int* status) {
+__global__ void symm_barrier_kernel(PeerPtrsMut pads, int my_rank, int n, int channel, unsigned epoch, int* status,
+                                    unsigned long long wait_limit_ns) {
   const int peer = threadIdx.x;
   if (peer >= n) return;
   __threadfence_system();
@@ -53,11 +54,13 @@ __global__ void symm_barrier_kernel(PeerPtrsMut pads, int my_rank, int n, int ch
   const unsigned long long t0 = globaltimer_ns();
   unsigned spins = 0;
   // epochs only grow; a peer may already be one barrier ahead
+  const unsigned long long limit = wait_limit_ns ? wait_limit_ns : WAIT_LIMIT_NS;
   while (static_cast<int>(ld_acquire_sys_u32(mine) - epoch) < 0) {
-    if ((++spins & 1023u) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+    if ((++spins & 63u) == 0 && globaltimer_ns() - t0 > limit) {
       if (status) atomicCAS(status, 0, ST_TIMEOUT_PEER);
       break;
     }
+    __nanosleep(spins < 64u ? 20u : 200u);  // back off: the polls cross NVLink or at least the L2
   }
 }
 
@@ -289,10 +292,24 @@ static inline PeerPtrsMut to_peers_mut(void* const* ptrs, int n) {
   return p;
 }
 
+// Streaming multiprocessors of the current device (the side-stream kernels size their grids from it).
+static int sm_count() {
+  constexpr int MAX_DEVICES = 64;
+  static int cached[MAX_DEVICES] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 extern "C" int olb_symm_barrier(void* const* pads, int my_rank, int n, int channel, unsigned epoch, int* status,
-                                cudaStream_t stream) {
+                                unsigned long long wait_limit_ns, cudaStream_t stream) {
   if (n > MAX_PEERS || n < 1) return -1;
-  symm_barrier_kernel<<<1, 32, 0, stream>>>(to_peers_mut(pads, n), my_rank, n, channel, epoch, status);
+  symm_barrier_kernel<<<1, 32, 0, stream>>>(to_peers_mut(pads, n), my_rank, n, channel, epoch, status, wait_limit_ns);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -300,7 +317,7 @@ extern "C" int olb_ep_gather_rows(const void* const* peer_x, int n, int T, const
                                   const int* blk_range, void* out, int cap, int cols, cudaStream_t stream) {
   if (n > MAX_PEERS || cols % 8) return -1;
   int grid = (cap + 7) / 8;
-  if (grid > 148 * 3) grid = 148 * 3;  // leaves room for a GEMM CTA on every SM
+  if (grid > sm_count() * 3) grid = sm_count() * 3;  // leaves room for a GEMM CTA on every SM
   if (grid <= 0) return 0;
   ep_gather_rows_kernel<<<grid, 256, 0, stream>>>(to_peers(peer_x, n), T, src_of, meta, blk_range,
                                                   static_cast<__nv_bfloat16*>(out), cap, cols);
@@ -322,7 +339,7 @@ extern "C" int olb_ep_combine(const void* const* peer_y, int n, const int* rows,
   if (n > MAX_PEERS || cols % 8 || K > 32) return -1;
   if (T <= 0) return 0;
   // at most three 256-thread blocks per SM: leaves room for a GEMM CTA running on the main stream meanwhile
-  const int grid = T < 148 * 3 ? T : 148 * 3;
+  const int grid = T < sm_count() * 3 ? T : sm_count() * 3;
   ep_combine_kernel<<<grid, 256, 0, stream>>>(to_peers(peer_y, n), rows, idx, T, K, E_loc,
                                               static_cast<__nv_bfloat16*>(out), cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -343,7 +360,7 @@ extern "C" int olb_pull_reduce_rows(const void* const* peer_partial, int n, long
   if (n > MAX_PEERS || cols % 8 || ld % 8) return -1;
   if (rows <= 0) return 0;
   long long blocks = (static_cast<long long>(rows) * (cols / 8) + 255) / 256;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > sm_count() * 8) blocks = sm_count() * 8;
   pull_reduce_rows_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(to_peers(peer_partial, n), n, row0, rows, cols,
                                                                         ld, static_cast<__nv_bfloat16*>(out));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;

@@ -7,6 +7,8 @@
 // Reference semantics (optimus/models/olmoe/modeling_olmoe.py:93-104): the normalised value
 // is rounded to the input dtype before it is multiplied by the weight; OLMo's LayerNorm has
 // no affine parameters and eps 1e-5 (optimus/models/olmo/modeling_olmo.py:19-30).
+#include <mutex>
+
 #include "olb_api.h"
 #include "ptx.cuh"
 
@@ -287,6 +289,37 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   }
 }
 
+// The shared-memory opt-in of rmsnorm_bwd_kernel is a per-device attribute: raise it once on each device that
+// runs a wide row (the caller's device is current).
+static bool raise_bwd_smem_limit() {
+  constexpr int MAX_DEVICES = 64;
+  static std::mutex mu;
+  static bool raised[MAX_DEVICES] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!raised[dev]) {
+    if (cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    raised[dev] = true;
+  }
+  return true;
+}
+
+// Launch the register-resident backward when `cols` is one of its widths.  Returns false when it is not.
+static bool launch_bwd_reg(const __nv_bfloat16* pdy, const __nv_bfloat16* px, const __nv_bfloat16* pw, const float* rstd,
+                           __nv_bfloat16* pdx, float* dw_partial, int rows, int cols, int nb, cudaStream_t stream) {
+  switch (cols) {
+    case 256: rmsnorm_bwd_reg_kernel<1><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); return true;
+    case 512: rmsnorm_bwd_reg_kernel<2><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); return true;
+    case 1024: rmsnorm_bwd_reg_kernel<4><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); return true;
+    case 2048: rmsnorm_bwd_reg_kernel<8><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); return true;
+    default: return false;
+  }
+}
+
 }  // namespace olb
 
 using namespace olb;
@@ -311,31 +344,13 @@ extern "C" int olb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
   if (cols % 8) return -1;
   if (rows <= 0) return 0;
   const int nb = olb_rmsnorm_bwd_blocks(rows);
-  {
-    const __nv_bfloat16* pdy = static_cast<const __nv_bfloat16*>(dy);
-    const __nv_bfloat16* px = static_cast<const __nv_bfloat16*>(x);
-    const __nv_bfloat16* pw = static_cast<const __nv_bfloat16*>(w);
-    __nv_bfloat16* pdx = static_cast<__nv_bfloat16*>(dx);
-    bool launched = true;
-    switch (cols) {  // register-resident rows
-      case 256: rmsnorm_bwd_reg_kernel<1><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); break;
-      case 512: rmsnorm_bwd_reg_kernel<2><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); break;
-      case 1024: rmsnorm_bwd_reg_kernel<4><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); break;
-      case 2048: rmsnorm_bwd_reg_kernel<8><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); break;
-      default: launched = false;
-    }
-    if (launched) return cudaGetLastError() == cudaSuccess ? 0 : -2;
-  }
+  if (launch_bwd_reg(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+                     static_cast<const __nv_bfloat16*>(w), rstd, static_cast<__nv_bfloat16*>(dx), dw_partial, rows, cols,
+                     nb, stream))
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
   const size_t smem = dw_partial ? sizeof(float) * NORM_WARPS * cols : 0;
   if (smem > 200 * 1024) return -3;
-  if (smem > 48 * 1024) {
-    static size_t configured = 0;
-    if (smem > configured) {
-      if (cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
-        return -4;
-      configured = 200 * 1024;
-    }
-  }
+  if (smem > 48 * 1024 && !raise_bwd_smem_limit()) return -4;
   rmsnorm_bwd_kernel<<<nb, NORM_THREADS, smem, stream>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
       rstd, static_cast<__nv_bfloat16*>(dx), dw_partial, rows, cols);
@@ -370,8 +385,6 @@ extern "C" int olb_layernorm_bwd(const void* dy, const void* x, const float* mea
 // ---------------------------------------------------------------------------------------------
 // Allocation-free variant of the RMSNorm backward (see olb_noalloc.h).  The per-block partial
 // sums of the weight gradient go to a device array that is part of the library image.
-#include <mutex>
-
 #include "olb_noalloc.h"
 
 namespace olb {
@@ -393,7 +406,6 @@ __global__ void colsum_finalize_static_kernel(int nparts, int cols, void* dw, in
 constexpr int NOALLOC_MAX_DEVICES = 64;
 struct NoallocDeviceState {
   float* scratch = nullptr;  // device address of g_noalloc_dw_partial on this device
-  bool smem_raised = false;
 };
 static NoallocDeviceState g_noalloc_state[NOALLOC_MAX_DEVICES];
 static std::mutex g_noalloc_mutex;
@@ -411,14 +423,7 @@ static int noalloc_setup(int dev, bool need_big_smem, float** scratch) {
     }
     st.scratch = ptr;
   }
-  if (need_big_smem && !st.smem_raised) {
-    if (cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
-        cudaSuccess) {
-      cudaGetLastError();
-      return OLB_NOALLOC_ERR_SYMBOL;
-    }
-    st.smem_raised = true;
-  }
+  if (need_big_smem && !raise_bwd_smem_limit()) return OLB_NOALLOC_ERR_SYMBOL;
   *scratch = st.scratch;
   return OLB_NOALLOC_OK;
 }
@@ -433,6 +438,7 @@ extern "C" const char* olb_noalloc_strerror(int code) {
     case OLB_NOALLOC_ERR_TOO_LARGE: return "cols exceeds OLB_NOALLOC_MAX_COLS (8192): the built-in scratch array is too small";
     case OLB_NOALLOC_ERR_SYMBOL: return "could not resolve the device address of the built-in scratch array";
     case OLB_NOALLOC_ERR_DEVICE: return "no usable current CUDA device";
+    case OLB_NOALLOC_ERR_NULL: return "dy, x, rstd, dx and dw must not be null";
     default: return "unknown error";
   }
 }
@@ -442,16 +448,21 @@ extern "C" int olb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
   if (cols % 8) return OLB_NOALLOC_ERR_BAD_COLS;
   if (cols > OLB_NOALLOC_MAX_COLS) return OLB_NOALLOC_ERR_TOO_LARGE;
   if (rows <= 0) return OLB_NOALLOC_OK;
+  if (!dy || !x || !rstd || !dx || !dw) return OLB_NOALLOC_ERR_NULL;  // the kernels would store through them
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return OLB_NOALLOC_ERR_DEVICE;
   const int nb = olb_rmsnorm_bwd_blocks(rows);  // <= OLB_NOALLOC_MAX_PARTS
+  const bool reg = cols == 256 || cols == 512 || cols == 1024 || cols == 2048;  // widths of the register-resident kernel
   const size_t smem = sizeof(float) * NORM_WARPS * cols;
   float* scratch = nullptr;
-  const int rc = noalloc_setup(dev, smem > 48 * 1024, &scratch);
+  const int rc = noalloc_setup(dev, !reg && smem > 48 * 1024, &scratch);
   if (rc != OLB_NOALLOC_OK) return rc;
-  rmsnorm_bwd_kernel<<<nb, NORM_THREADS, smem, stream>>>(
-      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
-      rstd, static_cast<__nv_bfloat16*>(dx), scratch, rows, cols);
+  if (!launch_bwd_reg(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+                      static_cast<const __nv_bfloat16*>(w), rstd, static_cast<__nv_bfloat16*>(dx), scratch, rows, cols, nb,
+                      stream))
+    rmsnorm_bwd_kernel<<<nb, NORM_THREADS, smem, stream>>>(
+        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+        rstd, static_cast<__nv_bfloat16*>(dx), scratch, rows, cols);
   if (cudaGetLastError() != cudaSuccess) return OLB_NOALLOC_ERR_LAUNCH;
   colsum_finalize_static_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(nb, cols, dw, dw_fp32);
   return cudaGetLastError() == cudaSuccess ? OLB_NOALLOC_OK : OLB_NOALLOC_ERR_LAUNCH;

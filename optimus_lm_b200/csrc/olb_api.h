@@ -189,9 +189,10 @@ int olb_adamw_step(const void* grad, int grad_fp32, float* master, float* m, flo
 // ---------------------------------------------------------------- peer-memory kernels (comm_p2p.cu)
 // Host arrays of n (<= 16) device pointers, one per rank of the group, into symmetric buffers.
 // Rendezvous of all ranks through signal words pads[rank][channel*16 + src]; `epoch` must grow by one
-// per use of a channel.  Bounded wait; a timeout is reported in *status.
+// per use of a channel.  Bounded wait (`wait_limit_ns`, 0 = the library's default of 4 s); a timeout sets *status to
+// ST_TIMEOUT_PEER (5) and the kernel returns, so the context stays usable.
 int olb_symm_barrier(void* const* pads, int my_rank, int n, int channel, unsigned epoch, int* status,
-                     cudaStream_t stream);
+                     unsigned long long wait_limit_ns, cudaStream_t stream);
 // out[row,:] = peer_x[g / T][g % T, :], g = src_of[row] (global token id), rows < meta[0]*128; padding -> 0.
 int olb_ep_gather_rows(const void* const* peer_x, int n, int T, const int* src_of, const int* meta,
                        const int* blk_range, void* out, int cap, int cols, cudaStream_t stream);

@@ -40,6 +40,7 @@ enum {
   OLB_NOALLOC_ERR_TOO_LARGE = -20,    // cols > OLB_NOALLOC_MAX_COLS
   OLB_NOALLOC_ERR_SYMBOL = -21,       // cudaGetSymbolAddress / attribute set-up failed
   OLB_NOALLOC_ERR_DEVICE = -22,       // no current device / device index out of range
+  OLB_NOALLOC_ERR_NULL = -23,         // dy, x, rstd, dx or dw is null while rows > 0
 };
 
 // dx [rows, cols] (bf16) = RMSNorm input gradient; dw [cols] (bf16, or fp32 when dw_fp32) = weight

@@ -29,6 +29,17 @@ from ..ops._ext import extension
 from .symm import SymmGroup, SymmTensor, peer_access_ok
 
 
+def slices_aligned(families) -> bool:
+    """The fused kernel moves 16-byte vectors of bf16 gradients and parameters and float4 vectors of the fp32 state:
+    every slice a rank owns must start at, and cover, a multiple of 8 elements, in the flat buffer and in the state."""
+    for fam in families:
+        for sl in fam.slices:
+            lo, _ = fam._part_range(sl)
+            if sl.part % 8 or lo % 8 or sl.state_start % 8:
+                return False
+    return True
+
+
 class FusedShardedStep:
     def __init__(self, opt):
         self.opt = opt
@@ -70,6 +81,8 @@ class FusedShardedStep:
             return None  # the "shard" class weights replicated gradients in the norm; keep the NCCL path
         if any(f.spec.num_shards > 16 for f in fams):
             return None
+        if not slices_aligned(fams):
+            return None  # e.g. sub-sharded chunks at DP 3, 5, 6, 7: the NCCL path has no alignment rule
         if not all(peer_access_ok(f.spec.group) for f in fams):
             return None
         return FusedShardedStep(opt)

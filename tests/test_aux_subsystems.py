@@ -127,6 +127,27 @@ def test_sharded_optimizer_state_resumes_under_data_parallelism(tmp_path):
     run_distributed(_dp_resume_worker, 2, str(tmp_path), ref)
 
 
+def _buffer_broadcast_worker(rank, world, exp):
+    """A persistent buffer (the stand-in for DeepSeek-V3's routing bias) must reach the replicas that do not read
+    the model file when the parameters travel over the data-parallel group."""
+    import torch.distributed as dist
+    for allreduce in (False, True):
+        e = _engine(optimizer="pgshard", data_parallelism=world)
+        e.model.register_buffer("routing_bias", torch.full((4,), 0.25 if rank == 0 else -1.0))
+        # every rank writes its part of the checkpoint through the regular path; only dp_ind 0's model file is read
+        ckpt.save_checkpoint(exp, e.model, e.optimizer, e.pmap, 0, rank=rank, verbose=False)
+        e2 = _engine(optimizer="pgshard", data_parallelism=world, seed=5)
+        e2.model.register_buffer("routing_bias", torch.full((4,), 7.0))
+        ckpt.load_checkpoint(exp, e2.model, e2.optimizer, e2.pmap, rank=rank, use_broadcast=True,
+                             use_allreduce_in_broadcast=allreduce, verbose=False)
+        assert torch.equal(e2.model.routing_bias, torch.full((4,), 0.25)), (rank, allreduce, e2.model.routing_bias)
+
+
+def test_broadcast_load_carries_persistent_buffers(tmp_path):
+    from dist_utils import run_distributed
+    run_distributed(_buffer_broadcast_worker, 2, str(tmp_path))
+
+
 # ---------------------------------------------------------------- datasets
 
 

@@ -60,3 +60,21 @@ def test_adamw_norm_by_product_on_the_plain_path():
     OF.adamw_step(g, master, m, v, p, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, grad_scale=0.5, norm_out=acc)
     assert torch.allclose(acc, 2.0 + (g * 0.5).pow(2).sum().reshape(1))
     assert torch.equal(p, master)
+
+
+@pytest.mark.parametrize("dp", [2, 3, 4, 5, 6, 7, 8])
+def test_fused_step_alignment_predicate(dp):
+    """The fused reduce-scatter + AdamW kernel moves 16-byte vectors: sub-sharded chunks whose per-rank part is not a
+    multiple of 8 elements (DP 3, 5, 6, 7 with a power-of-two chunk limit) must be left to the NCCL path."""
+    from optimus_lm_b200.optimizers import _Family, _FamilySpec
+    from optimus_lm_b200.parallel.fused_optimizer import slices_aligned
+
+    params = [torch.nn.Parameter(torch.zeros(4096)), torch.nn.Parameter(torch.zeros(1000))]
+    sub = _Family(_FamilySpec("", params, None, dp, dp - 1, 1.0, chunk_limit=2048, chunk_round=1), torch.bfloat16, "cpu",
+                  512, keep_state=False)
+    part = (2048 // dp * dp) // dp
+    assert slices_aligned([sub]) == (part % 8 == 0 and ((dp - 1) * part) % 8 == 0)
+    # the plain sharded layout rounds every shard to 512 elements and is always aligned
+    params = [torch.nn.Parameter(torch.zeros(4096)), torch.nn.Parameter(torch.zeros(1000))]
+    plain = _Family(_FamilySpec("", params, None, dp, dp - 1, 1.0), torch.bfloat16, "cpu", 512, keep_state=False)
+    assert slices_aligned([plain])

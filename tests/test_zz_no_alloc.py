@@ -66,7 +66,8 @@ def test_noalloc_matches_regular_entry_point_twice():
     lib, fn = _lib()
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     # two different problems back to back: the second must not see leftovers of the first
-    for rows, cols, seed in ((1000, 2048, 1), (333, 512, 2)):
+    # (2048 and 512 take the register-resident kernel, 7168 and 8192 the shared-memory one with its opt-in limit)
+    for rows, cols, seed in ((1000, 2048, 1), (333, 512, 2), (64, 7168, 3), (64, 8192, 4)):
         x, dy, w = _case(rows, cols, seed)
         rstd, dx_ref, dw_ref = _regular(x, dy, w)
         dx = torch.empty_like(x)
@@ -98,3 +99,9 @@ def test_noalloc_rejects_oversize_and_bad_cols():
     assert rc == -20 and b"8192" in lib.olb_noalloc_strerror(rc)
     rc = fn(t.data_ptr(), t.data_ptr(), t.data_ptr(), r.data_ptr(), t.data_ptr(), t.data_ptr(), 0, 1, 12, stream)
     assert rc == -1
+    # a null output with work to do is refused before any launch
+    rc = fn(t.data_ptr(), t.data_ptr(), t.data_ptr(), r.data_ptr(), None, t.data_ptr(), 0, 1, 8, stream)
+    assert rc == -23 and b"null" in lib.olb_noalloc_strerror(rc)
+    rc = fn(t.data_ptr(), t.data_ptr(), t.data_ptr(), r.data_ptr(), t.data_ptr(), None, 0, 1, 8, stream)
+    assert rc == -23
+    torch.cuda.synchronize()
