@@ -140,8 +140,9 @@ def build_parser():
     p.add_argument("--disable_fused_optimizer", action="store_true", help="Use NCCL collectives in the optimizer step")
     p.add_argument("--router_z_loss_coef", type=float, default=0.0)
     p.add_argument("--moe_capacity_factor", type=float, default=None,
-                   help="Rows of the expert-parallel receive buffers as a multiple of the balanced share "
-                        "(0 = worst case, can never overflow); a rank that receives more raises an error")
+                   help="0 (default): expert-parallel activation buffers sized from each layer's routed counts, nothing "
+                        "is ever dropped; > 0: fixed buffers of that multiple of the balanced share (no host read per "
+                        "layer), a rank that receives more stops the run with ST_OVERFLOW")
     p.add_argument("--enable_tb_logging", action="store_true",
                    help="Write loss / grad norm / lr / throughput scalars to <exp_dir>/scalars.jsonl and, when "
                         "tensorboard is installed, to <exp_dir>/tb")

@@ -33,6 +33,28 @@ void symm_barrier(const std::vector<int64_t>& pads, int64_t my_rank, int64_t cha
         "olb_symm_barrier");
 }
 
+void ep_publish_meta(const std::vector<int64_t>& idx_all, const std::vector<int64_t>& w_all, const at::Tensor& idx,
+                     const at::Tensor& w, int64_t off) {
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kInt && w.scalar_type() == at::kFloat && idx.is_contiguous() &&
+              w.is_contiguous() && idx.numel() == w.numel() && idx_all.size() == w_all.size());
+  c10::cuda::CUDAGuard guard(idx.device());
+  auto pi = mptrs(idx_all);
+  auto pw = mptrs(w_all);
+  check(olb_ep_publish_meta(pi.data(), pw.data(), static_cast<int>(pi.size()), idx.data_ptr<int>(), w.data_ptr<float>(),
+                            off, idx.numel(), cur_stream()),
+        "olb_ep_publish_meta");
+}
+
+void sum_slots(const at::Tensor& recv, at::Tensor& out) {
+  TORCH_CHECK(recv.is_cuda() && recv.scalar_type() == at::kBFloat16 && recv.dim() == 3 && recv.is_contiguous() &&
+              out.scalar_type() == at::kBFloat16 && out.is_contiguous() && out.size(0) == recv.size(0) &&
+              out.size(1) == recv.size(2));
+  c10::cuda::CUDAGuard guard(recv.device());
+  check(olb_sum_slots(recv.data_ptr(), static_cast<int>(recv.size(0)), static_cast<int>(recv.size(1)),
+                      static_cast<int>(recv.size(2)), out.data_ptr(), cur_stream()),
+        "olb_sum_slots");
+}
+
 void ep_gather_rows(const std::vector<int64_t>& peer_x, int64_t T, const at::Tensor& src_of, const at::Tensor& meta,
                     at::Tensor& out, const c10::optional<at::Tensor>& blk_range) {
   c10::cuda::CUDAGuard guard(out.device());
@@ -183,7 +205,8 @@ void gemm_push(const at::Tensor& a, const at::Tensor& b, const c10::optional<at:
 void gemm_ep_push(const at::Tensor& a, const at::Tensor& w2d, at::Tensor& c, const std::vector<int64_t>& c_peers,
                   const at::Tensor& meta, const at::Tensor& src_of, const at::Tensor& k_of, int64_t M, int64_t N, int64_t K,
                   int64_t b_expert_rows, int64_t num_experts, int64_t tokens, int64_t topk, int64_t my_peer,
-                  at::Tensor& flags, const c10::optional<at::Tensor>& status) {
+                  at::Tensor& flags, const c10::optional<at::Tensor>& status, bool b_mn_major,
+                  const c10::optional<at::Tensor>& w2d_2, int64_t k_split) {
   TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && w2d.scalar_type() == at::kBFloat16 &&
                   c.scalar_type() == at::kBFloat16,
               "bf16 CUDA operands expected");
@@ -210,6 +233,12 @@ void gemm_ep_push(const at::Tensor& a, const at::Tensor& w2d, at::Tensor& c, con
   d.N = static_cast<int>(N);
   d.K = static_cast<int>(K);
   d.mode = OLB_GEMM_RAGGED_M;
+  d.b_mn_major = b_mn_major;
+  if (w2d_2.has_value() && k_split > 0) {   // K-concatenated B: a[:, :k_split] @ w2d + a[:, k_split:] @ w2d_2
+    TORCH_CHECK(w2d_2->scalar_type() == at::kBFloat16 && w2d_2->sizes() == w2d.sizes() && w2d_2->strides() == w2d.strides());
+    d.B2 = w2d_2->data_ptr();
+    d.k_split = static_cast<int>(k_split);
+  }
   d.meta = meta.data_ptr<int>();
   d.num_experts = static_cast<int>(num_experts);
   d.b_expert_rows = static_cast<int>(b_expert_rows);
@@ -223,6 +252,122 @@ void gemm_ep_push(const at::Tensor& a, const at::Tensor& w2d, at::Tensor& c, con
   d.ep_tokens = static_cast<int>(tokens);
   d.ep_topk = static_cast<int>(topk);
   check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (expert-parallel combine variant)");
+}
+
+// Gate and up projection of a SwiGLU MLP in one launch: h[:, :I] = x Wg^T, h[:, I:] = x Wu^T and
+// act = w(row) * silu(h[:, :I]) * h[:, I:] written by the GEMM's epilogue.  `wg2d` / `wu2d` are [E * I, K] (E = 1 for a
+// dense MLP).  With `meta` the rows are grouped by expert (ragged-M) and `src_of` / `k_of` / `weights` [tokens, topk]
+// give the routing weight of every row.  With `x_peers` (addresses of every rank's token buffer [tokens, K], row
+// stride `x_ld`) the operand `xp` is filled inside the kernel: extra warps fetch row u = token src_of[u] from its
+// owner (the expert-parallel dispatch; with one entry, the local permutation) while earlier tiles already run.
+void gemm_gateup_swiglu(at::Tensor& xp, const at::Tensor& wg2d, const at::Tensor& wu2d, at::Tensor& h, at::Tensor& act,
+                        int64_t M, int64_t I, int64_t K, const c10::optional<at::Tensor>& meta,
+                        const c10::optional<at::Tensor>& src_of, const c10::optional<at::Tensor>& k_of,
+                        const c10::optional<at::Tensor>& weights, int64_t num_experts,
+                        const std::vector<int64_t>& x_peers, int64_t x_ld, int64_t tokens,
+                        const c10::optional<at::Tensor>& flags, const c10::optional<at::Tensor>& status) {
+  TORCH_CHECK(xp.is_cuda() && xp.scalar_type() == at::kBFloat16 && wg2d.scalar_type() == at::kBFloat16 &&
+                  wu2d.scalar_type() == at::kBFloat16 && h.scalar_type() == at::kBFloat16 &&
+                  act.scalar_type() == at::kBFloat16,
+              "bf16 CUDA operands expected");
+  TORCH_CHECK(xp.dim() == 2 && wg2d.dim() == 2 && h.dim() == 2 && act.dim() == 2 && xp.stride(1) == 1 &&
+              wg2d.stride(1) == 1 && h.stride(1) == 1 && act.stride(1) == 1);
+  TORCH_CHECK(wu2d.sizes() == wg2d.sizes() && wu2d.strides() == wg2d.strides(), "gate and up weights must share a layout");
+  TORCH_CHECK(xp.size(0) >= M && h.size(0) >= M && act.size(0) >= M && h.size(1) == 2 * I && act.size(1) == I);
+  c10::cuda::CUDAGuard guard(xp.device());
+  olb_gemm_desc d{};
+  d.A = xp.data_ptr();
+  d.B = wg2d.data_ptr();
+  d.B2 = wu2d.data_ptr();
+  d.C = h.data_ptr();
+  d.C2 = act.data_ptr();
+  d.lda = xp.stride(0);
+  d.ldb = wg2d.stride(0);
+  d.ldc = h.stride(0);
+  d.ldc2 = act.stride(0);
+  d.a_rows = xp.size(0);
+  d.b_rows = wg2d.size(0);
+  d.M = static_cast<int>(M);
+  d.N = static_cast<int>(I);
+  d.K = static_cast<int>(K);
+  d.epilogue = OLB_EPI_SWIGLU;
+  d.num_experts = static_cast<int>(num_experts);
+  d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
+  if (meta.has_value()) {
+    d.mode = OLB_GEMM_RAGGED_M;
+    d.meta = meta->data_ptr<int>();
+    d.b_expert_rows = static_cast<int>(I);
+  } else {
+    d.mode = OLB_GEMM_DENSE;
+  }
+  if (src_of.has_value() && weights.has_value()) {
+    TORCH_CHECK(k_of.has_value() && src_of->scalar_type() == at::kInt && k_of->scalar_type() == at::kInt &&
+                weights->scalar_type() == at::kFloat && weights->dim() == 2 && weights->is_contiguous() &&
+                src_of->numel() >= M && k_of->numel() >= M);
+    d.row_src_of = src_of->data_ptr<int>();
+    d.row_k_of = k_of->data_ptr<int>();
+    d.row_weights = weights->data_ptr<float>();
+    d.row_topk = static_cast<int>(weights->size(1));
+  }
+  std::vector<const void*> xs;
+  if (!x_peers.empty()) {
+    TORCH_CHECK(meta.has_value() && src_of.has_value() && flags.has_value() && x_peers.size() <= 8 && tokens > 0);
+    TORCH_CHECK(flags->scalar_type() == at::kInt && flags->is_contiguous() && flags->numel() >= (M + 127) / 128,
+                "flags: one int per 128-row block");
+    flags->zero_();
+    xs = cptrs(x_peers);
+    d.n_peers = static_cast<int>(xs.size());
+    d.A_peers = xs.data();
+    d.a_src_ld = x_ld;
+    d.stage_flags = flags->data_ptr<int>();
+    d.ep_src_of = src_of->data_ptr<int>();
+    d.ep_tokens = static_cast<int>(tokens);
+  }
+  check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (gate|up + SwiGLU)");
+}
+
+// Grouped GEMM whose operand rows are gathered inside the kernel (see gemm_gateup_swiglu): c[u, :] = xp[u, :] W[e(u)]^T
+// (or xp W with `b_mn_major`) with xp[u] = x_peers[src_of[u] / tokens][src_of[u] % tokens].  `xp` is left filled.
+void gemm_ep_gather(at::Tensor& xp, const at::Tensor& w2d, at::Tensor& c, int64_t M, int64_t N, int64_t K, bool b_mn_major,
+                    const at::Tensor& meta, const at::Tensor& src_of, int64_t b_expert_rows, int64_t num_experts,
+                    const std::vector<int64_t>& x_peers, int64_t x_ld, int64_t tokens, at::Tensor& flags,
+                    const c10::optional<at::Tensor>& status) {
+  TORCH_CHECK(xp.is_cuda() && xp.scalar_type() == at::kBFloat16 && w2d.scalar_type() == at::kBFloat16 &&
+                  c.scalar_type() == at::kBFloat16,
+              "bf16 CUDA operands expected");
+  TORCH_CHECK(xp.dim() == 2 && w2d.dim() == 2 && c.dim() == 2 && xp.stride(1) == 1 && w2d.stride(1) == 1 && c.stride(1) == 1);
+  TORCH_CHECK(xp.size(0) >= M && c.size(0) >= M && src_of.scalar_type() == at::kInt && src_of.numel() >= M);
+  TORCH_CHECK(!x_peers.empty() && x_peers.size() <= 8 && tokens > 0);
+  TORCH_CHECK(flags.scalar_type() == at::kInt && flags.is_contiguous() && flags.numel() >= (M + 127) / 128,
+              "flags: one int per 128-row block");
+  c10::cuda::CUDAGuard guard(xp.device());
+  flags.zero_();
+  auto xs = cptrs(x_peers);
+  olb_gemm_desc d{};
+  d.A = xp.data_ptr();
+  d.B = w2d.data_ptr();
+  d.C = c.data_ptr();
+  d.lda = xp.stride(0);
+  d.ldb = w2d.stride(0);
+  d.ldc = c.stride(0);
+  d.a_rows = xp.size(0);
+  d.b_rows = w2d.size(0);
+  d.M = static_cast<int>(M);
+  d.N = static_cast<int>(N);
+  d.K = static_cast<int>(K);
+  d.b_mn_major = b_mn_major;
+  d.mode = OLB_GEMM_RAGGED_M;
+  d.meta = meta.data_ptr<int>();
+  d.num_experts = static_cast<int>(num_experts);
+  d.b_expert_rows = static_cast<int>(b_expert_rows);
+  d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
+  d.n_peers = static_cast<int>(xs.size());
+  d.A_peers = xs.data();
+  d.a_src_ld = x_ld;
+  d.stage_flags = flags.data_ptr<int>();
+  d.ep_src_of = src_of.data_ptr<int>();
+  d.ep_tokens = static_cast<int>(tokens);
+  check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (expert-parallel dispatch variant)");
 }
 
 int64_t rs_adamw_blocks(int64_t n) { return olb_rs_adamw_blocks(n); }
@@ -258,6 +403,8 @@ void register_comm(pybind11::module& m) {
   namespace py = pybind11;
   m.def("symm_barrier", &symm_barrier, py::arg("pads"), py::arg("my_rank"), py::arg("channel"), py::arg("epoch"),
         py::arg("status"), py::arg("wait_limit_ns") = 0);
+  m.def("ep_publish_meta", &ep_publish_meta);
+  m.def("sum_slots", &sum_slots);
   m.def("ep_gather_rows", &ep_gather_rows);
   m.def("ep_resolve_rows", &ep_resolve_rows);
   m.def("ep_combine", &ep_combine);
@@ -265,7 +412,12 @@ void register_comm(pybind11::module& m) {
   m.def("pull_reduce_rows", &pull_reduce_rows);
   m.def("gemm_peer", &gemm_peer);
   m.def("gemm_push", &gemm_push);
-  m.def("gemm_ep_push", &gemm_ep_push);
+  m.def("gemm_ep_push", &gemm_ep_push, py::arg("a"), py::arg("w2d"), py::arg("c"), py::arg("c_peers"), py::arg("meta"),
+        py::arg("src_of"), py::arg("k_of"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("b_expert_rows"),
+        py::arg("num_experts"), py::arg("tokens"), py::arg("topk"), py::arg("my_peer"), py::arg("flags"),
+        py::arg("status"), py::arg("b_mn_major") = false, py::arg("w2d_2") = py::none(), py::arg("k_split") = 0);
+  m.def("gemm_gateup_swiglu", &gemm_gateup_swiglu);
+  m.def("gemm_ep_gather", &gemm_ep_gather);
   m.def("rs_adamw_blocks", &rs_adamw_blocks);
   m.def("rs_adamw", &rs_adamw);
 }

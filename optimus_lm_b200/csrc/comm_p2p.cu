@@ -64,6 +64,58 @@ __global__ void symm_barrier_kernel(PeerPtrsMut pads, int my_rank, int n, int ch
   }
 }
 
+// All-gather of the routing metadata by stores: this rank's [count] indices and weights go to slot `off` of every
+// peer's gathered arrays (a few hundred KB per rank and layer; the barrier that follows publishes them together with
+// the token rows).
+__global__ void ep_publish_meta_kernel(PeerPtrsMut idx_all, PeerPtrsMut w_all, const int* __restrict__ idx,
+                                       const float* __restrict__ w, int n, long long off, long long count) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < count;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int v = idx[i];
+    const float f = w[i];
+    for (int p = 0; p < n; ++p) {
+      static_cast<int*>(idx_all.p[p])[off + i] = v;
+      static_cast<float*>(w_all.p[p])[off + i] = f;
+    }
+  }
+}
+
+// out[t,:] = sum_k recv[t,k,:] in fp32, fixed k order: the owner's side of the combine after the expert outputs
+// were pushed into its receive buffer.
+__global__ void __launch_bounds__(256)
+sum_slots_kernel(const __nv_bfloat16* __restrict__ recv, int T, int K, int cols, __nv_bfloat16* __restrict__ out) {
+  const long long nvec = static_cast<long long>(T) * (cols / 8);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / (cols / 8);
+    const int c = static_cast<int>(i - t * (cols / 8)) * 8;
+    const __nv_bfloat16* base = recv + (t * K) * cols + c;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        v[j] = (k0 + j < K) ? *reinterpret_cast<const uint4*>(base + static_cast<long long>(k0 + j) * cols) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float2 a;
+        a = unpack_bf16(v[j].x); acc[0] += a.x; acc[1] += a.y;
+        a = unpack_bf16(v[j].y); acc[2] += a.x; acc[3] += a.y;
+        a = unpack_bf16(v[j].z); acc[4] += a.x; acc[5] += a.y;
+        a = unpack_bf16(v[j].w); acc[6] += a.x; acc[7] += a.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16(acc[0], acc[1]);
+    o.y = pack_bf16(acc[2], acc[3]);
+    o.z = pack_bf16(acc[4], acc[5]);
+    o.w = pack_bf16(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + t * cols + c) = o;
+  }
+}
+
 // out[row,:] = peer_x[g / T][(g % T), :] with g = src_of[row]; padding rows -> 0.  One warp per row; a lane keeps up
 // to eight 16-byte loads in flight, so that few resident warps saturate NVLink and the kernel can run underneath a
 // GEMM (the grid is capped well below the SMs' thread capacity).  `blk_range` (optional, device) restricts the rows to
@@ -310,6 +362,27 @@ extern "C" int olb_symm_barrier(void* const* pads, int my_rank, int n, int chann
                                 unsigned long long wait_limit_ns, cudaStream_t stream) {
   if (n > MAX_PEERS || n < 1) return -1;
   symm_barrier_kernel<<<1, 32, 0, stream>>>(to_peers_mut(pads, n), my_rank, n, channel, epoch, status, wait_limit_ns);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int olb_ep_publish_meta(void* const* idx_all, void* const* w_all, int n, const int* idx, const float* w,
+                                   long long off, long long count, cudaStream_t stream) {
+  if (n > MAX_PEERS || n < 1) return -1;
+  if (count <= 0) return 0;
+  long long blocks = (count + 255) / 256;
+  if (blocks > sm_count() * 4) blocks = sm_count() * 4;
+  ep_publish_meta_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(to_peers_mut(idx_all, n), to_peers_mut(w_all, n), idx,
+                                                                       w, n, off, count);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int olb_sum_slots(const void* recv, int T, int K, int cols, void* out, cudaStream_t stream) {
+  if (cols % 8 || K < 1) return -1;
+  if (T <= 0) return 0;
+  long long blocks = (static_cast<long long>(T) * (cols / 8) + 255) / 256;
+  if (blocks > sm_count() * 8) blocks = sm_count() * 8;
+  sum_slots_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(recv), T, K, cols,
+                                                                 static_cast<__nv_bfloat16*>(out));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -8,10 +8,14 @@
 //   * warp 0   : TMA producer - tiled bulk tensor loads into a 128B-swizzled smem ring
 //   * warp 1   : one elected thread issues tcgen05.mma (UMMA 128 x BLOCK_N x 16) into one of
 //                two TMEM accumulators and commits to mbarriers
-//   * warps 2-5: epilogue - tcgen05.ld the accumulator (each warp owns 32 TMEM lanes),
-//                convert and store / accumulate into C while the next tile's main loop runs
-//   * warps 6-9: only in the variants with a fused collective (PeerArg<true>): copy the other GPUs' rows of A into the local
-//                gathered copy over NVLink while the tiles of the local rows are computed
+//   * warps 2-5: epilogue - tcgen05.ld the accumulator (each warp owns 32 TMEM lanes), convert, stage the warp's
+//                32 rows in 128B-swizzled shared memory and write them with cp.async.bulk.tensor stores (full
+//                128-byte lines) while the next tile's main loop runs; accumulating epilogues (C += A*B) use
+//                plain loads and stores.  With EPI_SWIGLU the tile holds 128 gate and 128 up columns of the same
+//                expert and the epilogue writes gate | up (for the backward) and w(row) * silu(gate) * up.
+//   * warps 6-9: only in the variants with a fused transfer (PeerArg<true>): all-gather of A's rows from the other
+//                GPUs, gather of the routed token rows into the expert-grouped operand (expert-parallel dispatch, or
+//                the local permutation on one GPU), or push of finished rows of C to their owners
 // Each operand may be K-major (rows of K contiguous) or MN-major (rows of M/N contiguous),
 // which gives NT / NN / TN / TT products without a transpose pass:
 //   forward   Y  = X  W^T    A K-major,  B K-major
@@ -62,7 +66,17 @@ struct GemmParams {
   int m_rotate_blocks;         // row-block rotation of the tile order (start on the rows this GPU owns)
   const int* blk_range;        // ragged-M only, optional (device): restrict to row blocks [blk_range[0], blk_range[1])
   int* status;
+  int c_tma;                   // epilogue writes C through tensor-map stores (tma_c); 0 = plain stores
+  // EPI_SWIGLU: N is the width of act (= I); the tile's B rows come from tma_b (gate) and tma_b2 (up), tma_c covers
+  // h [rows, 2 * N] (gate | up) and tma_c2 act [rows, N].  Row weights: weights[src_of[row] * topk + k_of[row]],
+  // 0 for padding rows (src_of < 0); all three null = weight 1.
+  const int* row_src_of;
+  const int* row_k_of;
+  const float* row_weights;
+  int row_topk;
 };
+
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
 
 // All-gather fused into the GEMM: the outer rows of A live in the memories of up to 8 GPUs.  Four extra warps per
 // CTA ("stagers") copy the other GPUs' rows into this GPU's gathered copy of A with plain loads over NVLink and
@@ -91,19 +105,29 @@ struct PeerArg<true> {
   // Expert-parallel combine transport (push == 2, ragged-M mode): row u of C is the expert output of the routed pair
   // (token src_of[u] of the group's T-token-per-rank numbering, choice k_of[u]); it goes to the token owner's
   // receive buffer [T, topk, N] at push_dst[owner] + (t * topk + k) * ld.  Padding rows (src_of < 0) are not sent.
+  // Expert-parallel dispatch (push == 3, ragged-M mode): row u of A is token src_of[u] (rank src_of[u] / T, local
+  // index src_of[u] % T) of src[rank] (row stride src_ld); the stagers copy it into dst + u * ld (zeros for padding
+  // rows) and count the rows per 128-row block in `flags`; the producer waits for 128 before it loads a block.
   const int* src_of;
   const int* k_of;
   int T, topk;
+  long long src_ld;
 };
 constexpr int STAGER_WARPS = 4;
 constexpr int NUM_THREADS_STAGED = NUM_THREADS + 32 * STAGER_WARPS;
+
+// Epilogue staging: each of the four epilogue warps owns two buffers of 32 rows x 128 bytes (what one tensor-map
+// store of its rows takes), laid out with the 128-byte swizzle the store expects.
+constexpr int EPI_BUF_BYTES = 32 * 128;
+constexpr int EPI_STAGING_BYTES = 4 * 2 * EPI_BUF_BYTES;
 
 template <int BLOCK_N>
 struct SmemLayout {
   static constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 2;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int STAGES = (BLOCK_N == 256) ? 4 : (BLOCK_N == 128 ? 6 : 8);
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EPI_STAGING_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + slack for 1024B alignment
 };
 
@@ -114,9 +138,10 @@ struct TileInfo {
 };
 
 // Map a linear tile id to its coordinates.  Returns false when `t` is past the last tile.
-template <int BLOCK_N>
+template <int BLOCK_N, int EPI = EPI_PLAIN>
 __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int num_m_blocks, int blk0, TileInfo& ti) {
-  const int num_n_blocks = (p.N + BLOCK_N - 1) / BLOCK_N;
+  constexpr int TILE_N = EPI == EPI_SWIGLU ? BLOCK_N / 2 : BLOCK_N;  // output columns per tile
+  const int num_n_blocks = (p.N + TILE_N - 1) / TILE_N;
   if (p.mode == OLB_GEMM_RAGGED_K) {
     const int per_expert = num_m_blocks * num_n_blocks;
     if (t >= per_expert * p.num_experts) return false;
@@ -124,7 +149,7 @@ __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int num_m_b
     const int r = t - e * per_expert;
     ti.expert = e;
     ti.m0 = (r / num_n_blocks) * BLOCK_M;
-    ti.n0 = (r % num_n_blocks) * BLOCK_N;
+    ti.n0 = (r % num_n_blocks) * TILE_N;
     ti.kb_begin = p.meta[e] / BLOCK_K;
     ti.kb_end = p.meta[e + 1] / BLOCK_K;
     return true;
@@ -143,7 +168,7 @@ __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, int num_m_b
   const int n_blk = r / rows_in_band;
   m_blk += blk0;  // first row block of the requested range
   ti.m0 = m_blk * BLOCK_M;
-  ti.n0 = n_blk * BLOCK_N;
+  ti.n0 = n_blk * TILE_N;
   ti.kb_begin = 0;
   ti.kb_end = (p.K + BLOCK_K - 1) / BLOCK_K;
   ti.expert = (p.mode == OLB_GEMM_RAGGED_M) ? p.meta[1 + m_blk] : 0;
@@ -187,14 +212,41 @@ __device__ __forceinline__ void copy_row_ldcg(const uint4* s, uint4* d, int vecs
   }
 }
 
-template <int BLOCK_N, bool PEER>
+// One warp stores its 32 rows x 128 bytes through a tensor-map store: the lane's row (`v`, 32 words) goes to the
+// staging buffer in the swizzled layout, then lane 0 issues the store.  Buffers alternate; before a buffer is
+// rewritten the store that used it two turns ago must have finished reading it.
+struct EpiStage {
+  uint32_t base;   // shared-memory address of this warp's two buffers
+  int turn;
+};
+__device__ __forceinline__ void epi_store_chunk(EpiStage& es, const CUtensorMap* map, const uint32_t (&v)[32], int lane,
+                                                int x, int y) {
+  const uint32_t buf = es.base + (es.turn & 1) * EPI_BUF_BYTES;
+  es.turn++;
+  if (lane == 0) tma_store_wait_read_n<1>();
+  __syncwarp();
+  const uint32_t row = buf + lane * 128;
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    st_shared_v4(row + ((j ^ (lane & 7)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(map, buf, x, y);
+    tma_store_commit();
+  }
+}
+
+template <int BLOCK_N, bool PEER, int EPI>
 __global__ void __launch_bounds__(PEER ? NUM_THREADS_STAGED : NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 const __grid_constant__ CUtensorMap tma_b2, const __grid_constant__ PeerArg<PEER> peers,
+                 const __grid_constant__ CUtensorMap tma_b2, const __grid_constant__ CUtensorMap tma_c,
+                 const __grid_constant__ CUtensorMap tma_c2, const __grid_constant__ PeerArg<PEER> peers,
                  const GemmParams p) {
   using L = SmemLayout<BLOCK_N>;
   constexpr int STAGES = L::STAGES;
   constexpr uint32_t TMEM_COLS = (2 * BLOCK_N < 32) ? 32 : 2 * BLOCK_N;
+  static_assert(EPI == EPI_PLAIN || BLOCK_N == 256, "the SwiGLU epilogue pairs 128 gate with 128 up columns");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -224,6 +276,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     fence_barrier_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    if (p.c_tma) tma_prefetch_desc(&tma_c);
   }
   if (warp == 2) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -252,11 +305,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       TileInfo ti;
-      for (int t = blockIdx.x; ok && get_tile<BLOCK_N>(p, t, num_m_blocks, blk0, ti); t += gridDim.x) {
+      for (int t = blockIdx.x; ok && get_tile<BLOCK_N, EPI>(p, t, num_m_blocks, blk0, ti); t += gridDim.x) {
         if constexpr (PEER) {
-          // rows of another GPU: wait until the stagers have brought the whole row block into the local copy
-          if (!peers.push && ti.m0 / peers.rows != peers.me) {
-            if (!wait_count(peers.flags + ti.m0 / BLOCK_M, min(BLOCK_M, p.M - ti.m0), p.status, abort_flag)) {
+          // rows that the stagers bring in: wait until the whole row block is in the local operand
+          bool wait_rows = false;
+          int need = 0;
+          if (peers.push == 0 && ti.m0 / peers.rows != peers.me) {
+            wait_rows = true;
+            need = min(BLOCK_M, p.M - ti.m0);
+          } else if (peers.push == 3) {
+            wait_rows = true;
+            need = BLOCK_M;
+          }
+          if (wait_rows) {
+            if (!wait_count(peers.flags + ti.m0 / BLOCK_M, need, p.status, abort_flag)) {
               ok = false;
               break;
             }
@@ -279,16 +341,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
             for (int j = 0; j < BLOCK_M / 64; ++j) tma_load_2d(sa + j * MN_BOX_BYTES, &tma_a, fb, ti.m0 + j * 64, k0);
           }
-          // K-concatenated B: the second half of the K range comes from a second tensor of the same layout
-          const bool second = p.kb_split > 0 && kb >= p.kb_split;
-          const CUtensorMap* tmb = second ? &tma_b2 : &tma_b;
-          const int kB = second ? k0 - p.kb_split * BLOCK_K : k0;
-          if (!p.b_mn_major) {
-            tma_load_2d(sb, tmb, fb, kB, ti.expert * p.b_expert_rows + ti.n0);
+          if constexpr (EPI == EPI_SWIGLU) {
+            // 128 rows of the gate weight and the same 128 rows of the up weight: accumulator columns 0-127 | 128-255
+            const int brow = ti.expert * p.b_expert_rows + ti.n0;
+            tma_load_2d(sb, &tma_b, fb, k0, brow);
+            tma_load_2d(sb + (BLOCK_N / 2) * BLOCK_K * 2, &tma_b2, fb, k0, brow);
           } else {
-            const int krow = (p.mode == OLB_GEMM_RAGGED_M ? ti.expert * p.b_expert_rows : 0) + kB;
+            // K-concatenated B: the second half of the K range comes from a second tensor of the same layout
+            const bool second = p.kb_split > 0 && kb >= p.kb_split;
+            const CUtensorMap* tmb = second ? &tma_b2 : &tma_b;
+            const int kB = second ? k0 - p.kb_split * BLOCK_K : k0;
+            if (!p.b_mn_major) {
+              tma_load_2d(sb, tmb, fb, kB, ti.expert * p.b_expert_rows + ti.n0);
+            } else {
+              const int krow = (p.mode == OLB_GEMM_RAGGED_M ? ti.expert * p.b_expert_rows : 0) + kB;
 #pragma unroll
-            for (int j = 0; j < BLOCK_N / 64; ++j) tma_load_2d(sb + j * MN_BOX_BYTES, tmb, fb, ti.n0 + j * 64, krow);
+              for (int j = 0; j < BLOCK_N / 64; ++j) tma_load_2d(sb + j * MN_BOX_BYTES, tmb, fb, ti.n0 + j * 64, krow);
+            }
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -318,7 +387,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t acc_phase = 0;
       bool ok = true;
       TileInfo ti;
-      for (int t = blockIdx.x; ok && get_tile<BLOCK_N>(p, t, num_m_blocks, blk0, ti); t += gridDim.x) {
+      for (int t = blockIdx.x; ok && get_tile<BLOCK_N, EPI>(p, t, num_m_blocks, blk0, ti); t += gridDim.x) {
         if (ti.kb_end <= ti.kb_begin) continue;  // empty expert: the epilogue writes zeros
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, p.status, ST_TIMEOUT_ACC_EMPTY, abort_flag)) break;
         tc_fence_after();
@@ -359,16 +428,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     int acc = 0;
     uint32_t acc_phase = 0;
     TileInfo ti;
-    for (int t = blockIdx.x; get_tile<BLOCK_N>(p, t, num_m_blocks, blk0, ti); t += gridDim.x) {
+    EpiStage es{smem_base + L::EPI_OFFSET + lane_group * 2 * EPI_BUF_BYTES, 0};
+    for (int t = blockIdx.x; get_tile<BLOCK_N, EPI>(p, t, num_m_blocks, blk0, ti); t += gridDim.x) {
       const int row = ti.m0 + lane_group * 32 + lane;
       const bool row_ok = row < p.M;
       const bool has_k = ti.kb_end > ti.kb_begin;
-      char* c_row;
-      {
-        long long off = static_cast<long long>(row) * p.ldc + ti.n0;
-        if (p.mode == OLB_GEMM_RAGGED_K) off += static_cast<long long>(ti.expert) * p.c_expert_stride;
-        c_row = static_cast<char*>(p.C) + off * (p.out_fp32 ? 4 : 2);
-      }
       if (has_k) {
         if (!mbar_wait(acc_full_bar(acc), acc_phase, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) break;
         tc_fence_after();
@@ -376,61 +440,159 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         continue;  // nothing to add
       }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + acc * BLOCK_N;
-#pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        uint32_t r[32];
-        if (has_k) {
-          tmem_ld_32x32b_x32(taddr + c * 32, r);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
+      if constexpr (EPI == EPI_SWIGLU) {
+        // columns [0,128) of the accumulator are gate, [128,256) up, both for act columns [n0, n0 + 128)
+        float w = 1.f;
+        if (p.row_src_of) {
+          const int src = row_ok ? p.row_src_of[row] : -1;
+          w = src >= 0 ? p.row_weights[static_cast<long long>(src) * p.row_topk + p.row_k_of[row]] : 0.f;
         }
-        if (row_ok) {
-          const int col0 = ti.n0 + c * 32;
-          if (p.out_fp32) {
-            float4* dst = reinterpret_cast<float4*>(c_row + c * 32 * 4);
+        const int y = ti.m0 + lane_group * 32;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {  // 64 act columns per turn
+          uint32_t hg[32], hu[32];
+          {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32b_x32(taddr + c * 64, r0);
+            tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
+            tmem_ld_wait();
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              if (col0 + g * 4 < p.N) {
-                float4 v = make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
-                                       __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
-                if (p.accumulate) {
-                  float4 o = dst[g];
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                }
-                dst[g] = v;
-              }
+            for (int i = 0; i < 16; ++i) {
+              hg[i] = pack_bf16(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+              hg[16 + i] = pack_bf16(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
             }
+          }
+          const int x = ti.n0 + c * 64;
+          if (y < p.M && x < p.N) epi_store_chunk(es, &tma_c, hg, lane, x, y);
+          {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32b_x32(taddr + 128 + c * 64, r0);
+            tmem_ld_32x32b_x32(taddr + 128 + c * 64 + 32, r1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              hu[i] = pack_bf16(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+              hu[16 + i] = pack_bf16(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+            }
+          }
+          if (y < p.M && x < p.N) epi_store_chunk(es, &tma_c, hu, lane, p.N + x, y);
+          // the activation from the rounded values, as the backward recomputes it from the saved gate | up
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float2 g = unpack_bf16(hg[i]), u = unpack_bf16(hu[i]);
+            hg[i] = pack_bf16(w * (g.x / (1.f + __expf(-g.x))) * u.x, w * (g.y / (1.f + __expf(-g.y))) * u.y);
+          }
+          if (y < p.M && x < p.N) epi_store_chunk(es, &tma_c2, hg, lane, x, y);
+        }
+      } else if (p.c_tma) {
+        // ---- staged tensor-map stores: 128 bytes of every row per turn (64 bf16 or 32 fp32 columns)
+        long long y = ti.m0 + lane_group * 32;
+        const bool rows_ok = y < p.M;
+        if (p.mode == OLB_GEMM_RAGGED_K) y += static_cast<long long>(ti.expert) * p.M;
+        if (p.out_fp32) {
+#pragma unroll 1
+          for (int c = 0; c < BLOCK_N / 32; ++c) {
+            uint32_t r[32];
+            if (has_k) {
+              tmem_ld_32x32b_x32(taddr + c * 32, r);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = 0u;
+            }
+            const int x = ti.n0 + c * 32;
+            if (rows_ok && x < p.N) epi_store_chunk(es, &tma_c, r, lane, x, static_cast<int>(y));
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < BLOCK_N / 64; ++c) {
+            uint32_t v[32];
+            if (has_k) {
+              uint32_t r0[32], r1[32];
+              tmem_ld_32x32b_x32(taddr + c * 64, r0);
+              tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                v[i] = pack_bf16(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+                v[16 + i] = pack_bf16(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = 0u;
+            }
+            const int x = ti.n0 + c * 64;
+            if (rows_ok && x < p.N) epi_store_chunk(es, &tma_c, v, lane, x, static_cast<int>(y));
+          }
+        }
+      } else {
+        // ---- plain loads / stores (accumulating epilogues, layouts a tensor map cannot describe)
+        char* c_row;
+        {
+          long long off = static_cast<long long>(row) * p.ldc + ti.n0;
+          if (p.mode == OLB_GEMM_RAGGED_K) off += static_cast<long long>(ti.expert) * p.c_expert_stride;
+          c_row = static_cast<char*>(p.C) + off * (p.out_fp32 ? 4 : 2);
+        }
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N / 32; ++c) {
+          uint32_t r[32];
+          if (has_k) {
+            tmem_ld_32x32b_x32(taddr + c * 32, r);
+            tmem_ld_wait();
           } else {
-            uint4* dst = reinterpret_cast<uint4*>(c_row + c * 32 * 2);
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (col0 + g * 8 < p.N) {
-                float f[8];
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          if (row_ok) {
+            const int col0 = ti.n0 + c * 32;
+            if (p.out_fp32) {
+              float4* dst = reinterpret_cast<float4*>(c_row + c * 32 * 4);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[8 * g + i]);
-                if (p.accumulate) {
-                  uint4 o = dst[g];
-                  float2 a;
-                  a = unpack_bf16(o.x); f[0] += a.x; f[1] += a.y;
-                  a = unpack_bf16(o.y); f[2] += a.x; f[3] += a.y;
-                  a = unpack_bf16(o.z); f[4] += a.x; f[5] += a.y;
-                  a = unpack_bf16(o.w); f[6] += a.x; f[7] += a.y;
+              for (int g = 0; g < 8; ++g) {
+                if (col0 + g * 4 < p.N) {
+                  float4 v = make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
+                                         __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
+                  if (p.accumulate) {
+                    float4 o = dst[g];
+                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                  }
+                  dst[g] = v;
                 }
-                uint4 v;
-                v.x = pack_bf16(f[0], f[1]);
-                v.y = pack_bf16(f[2], f[3]);
-                v.z = pack_bf16(f[4], f[5]);
-                v.w = pack_bf16(f[6], f[7]);
-                dst[g] = v;
+              }
+            } else {
+              uint4* dst = reinterpret_cast<uint4*>(c_row + c * 32 * 2);
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                if (col0 + g * 8 < p.N) {
+                  float f[8];
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[8 * g + i]);
+                  if (p.accumulate) {
+                    uint4 o = dst[g];
+                    float2 a;
+                    a = unpack_bf16(o.x); f[0] += a.x; f[1] += a.y;
+                    a = unpack_bf16(o.y); f[2] += a.x; f[3] += a.y;
+                    a = unpack_bf16(o.z); f[4] += a.x; f[5] += a.y;
+                    a = unpack_bf16(o.w); f[6] += a.x; f[7] += a.y;
+                  }
+                  uint4 v;
+                  v.x = pack_bf16(f[0], f[1]);
+                  v.y = pack_bf16(f[2], f[3]);
+                  v.z = pack_bf16(f[4], f[5]);
+                  v.w = pack_bf16(f[6], f[7]);
+                  dst[g] = v;
+                }
               }
             }
           }
         }
       }
       if constexpr (PEER) {
-        if (peers.push) {  // this warp's 32 rows of the tile are stored: let the stagers know
+        if (peers.push == 1 || peers.push == 2) {  // this warp's 32 rows of the tile are stored: let the stagers know
+          if (p.c_tma || EPI == EPI_SWIGLU) {
+            if (lane == 0) tma_store_wait_all();   // the stores issued by this lane are complete, not only read
+            fence_proxy_async_all();
+          }
           __threadfence();
           __syncwarp();
           if (lane == 0) atomicAdd(peers.flags + ti.m0 / BLOCK_M, 1);
@@ -446,20 +608,52 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
       }
     }
+    if (lane == 0) tma_store_wait_read();  // the staging buffers must outlive the stores that read them
   }
 
   if constexpr (PEER) {
     if (warp >= 6) {
-      // ---------------------------------------------------------- stagers (warps 6..9): the all-gather
-      // Remote rows in the order the tiles need them: the peer after this one first.  Every CTA's stagers take rows
-      // of the same block at the same time, so blocks complete one after the other.  The gather waits for nothing;
-      // the push waits (bounded) for this GPU's own epilogues.
-      const long long total = peers.push == 2 ? min(static_cast<long long>(num_m_blocks) * BLOCK_M, static_cast<long long>(p.M))
-                                              : static_cast<long long>(peers.n - 1) * peers.rows;
+      // ---------------------------------------------------------- stagers (warps 6..9)
+      // Remote rows in the order the tiles need them.  Every CTA's stagers take rows of the same block at the same
+      // time, so blocks complete one after the other.  The gathers wait for nothing; the pushes wait (bounded) for
+      // this GPU's own epilogues.
+      const long long total = (peers.push == 2 || peers.push == 3)
+                                  ? min(static_cast<long long>(num_m_blocks) * BLOCK_M, static_cast<long long>(p.M))
+                                  : static_cast<long long>(peers.n - 1) * peers.rows;
       int ready_blk = -1;
       bool ok = true;
       for (long long u = blockIdx.x * STAGER_WARPS + (warp - 6); ok && u < total;
            u += static_cast<long long>(gridDim.x) * STAGER_WARPS) {
+        if (peers.push == 3) {
+          // -------- expert-parallel dispatch: the routed token row comes from its owner into the grouped operand
+          const int g = peers.src_of[u];
+          uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.dst) + u * peers.ld * 2);
+          if (g >= 0) {
+            const int owner = g / peers.T;
+            const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.src[owner]) +
+                                                            static_cast<long long>(g - owner * peers.T) * peers.src_ld * 2);
+            for (int c0 = 0; c0 < peers.row_vecs; c0 += 256) {
+              uint4 v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int c = c0 + i * 32 + lane;
+                if (c < peers.row_vecs) v[i] = s[c];
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int c = c0 + i * 32 + lane;
+                if (c < peers.row_vecs) d[c] = v[i];
+              }
+            }
+          } else {
+            for (int c = lane; c < peers.row_vecs; c += 32) d[c] = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_all();
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) atomicAdd(peers.flags + u / BLOCK_M, 1);
+          continue;
+        }
         if (peers.push == 2) {
           // -------- expert-parallel combine transport: a finished row goes to the owner of its token
           const int blk = static_cast<int>(u / BLOCK_M);
@@ -549,19 +743,59 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2D bf16 tensor map with 128B swizzle.  dims/box are {inner, outer}.
-int make_tmap_2d_bf16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
-                      uint32_t box_inner, uint32_t box_outer) {
+// 2D tensor maps with 128B swizzle are pure functions of (base, extents, stride, box, element type).  A training
+// step asks for the same few hundred of them every iteration (weights, flat gradient buffer, activations that the
+// caching allocator hands back at the same addresses), so they are kept in a small per-thread table instead of being
+// encoded two to five times per launch.
+struct TmapKey {
+  const void* base;
+  uint64_t inner, outer, stride;
+  uint32_t box_inner, box_outer, fp32;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && inner == o.inner && outer == o.outer && stride == o.stride && box_inner == o.box_inner &&
+           box_outer == o.box_outer && fp32 == o.fp32;
+  }
+};
+struct TmapSlot {
+  TmapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int TMAP_CACHE_SLOTS = 2048;
+
+static int make_tmap_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                        uint32_t box_inner, uint32_t box_outer, bool fp32) {
+  static thread_local TmapSlot* table = nullptr;
+  if (!table) table = new TmapSlot[TMAP_CACHE_SLOTS]();
+  const TmapKey key{base, inner, outer, row_stride_bytes, box_inner, box_outer, fp32 ? 1u : 0u};
+  uint64_t h = reinterpret_cast<uintptr_t>(base) * 0x9E3779B97F4A7C15ull;
+  h ^= (inner * 0xC2B2AE3D27D4EB4Full) ^ (outer * 0x165667B19E3779F9ull) ^ (row_stride_bytes << 17) ^
+       (static_cast<uint64_t>(box_inner) << 40) ^ (static_cast<uint64_t>(box_outer) << 52) ^ (fp32 ? 0x8000u : 0u);
+  TmapSlot& slot = table[(h >> 20) % TMAP_CACHE_SLOTS];
+  if (slot.used && slot.key == key) {
+    *map = slot.map;
+    return 0;
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {row_stride_bytes};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t elem_strides[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -2;
+  CUresult r = fn(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -2;
+  slot.key = key;
+  slot.map = *map;
+  slot.used = true;
+  return 0;
+}
+
+// 2D bf16 tensor map with 128B swizzle.  dims/box are {inner, outer}.
+int make_tmap_2d_bf16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                      uint32_t box_inner, uint32_t box_outer) {
+  return make_tmap_2d(map, base, inner, outer, row_stride_bytes, box_inner, box_outer, false);
 }
 
 // 4D bf16 tensor map with 128B swizzle (attention: dims {D, H, S, B} over a strided [B, S, H, D] view).
@@ -584,42 +818,73 @@ int make_tmap_4d_bf16(CUtensorMap* map, const void* base, const uint64_t dims[4]
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-template <int BLOCK_N, bool PEER>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const PeerArg<PEER>& peers,
-                  const GemmParams& p, int num_sms, cudaStream_t stream) {
+struct TensorMaps {
+  CUtensorMap a, b, b2, c, c2;
+};
+
+template <int BLOCK_N, bool PEER, int EPI>
+static int launch(const TensorMaps& tm, const PeerArg<PEER>& peers, const GemmParams& p, int num_sms, cudaStream_t stream) {
   using L = SmemLayout<BLOCK_N>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BLOCK_N, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+  // the shared-memory opt-in is an attribute of the function on one device
+  constexpr int MAX_DEVICES = 64;
+  static bool configured[MAX_DEVICES] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -3;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BLOCK_N, PEER, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return -3;
-    configured = true;
+    configured[dev] = true;
   }
-  long long tiles;
-  const long long nm = (p.M + BLOCK_M - 1) / BLOCK_M, nn = (p.N + BLOCK_N - 1) / BLOCK_N;
-  tiles = nm * nn * (p.mode == OLB_GEMM_RAGGED_K ? p.num_experts : 1);
+  constexpr int TILE_N = EPI == EPI_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
+  const long long nm = (p.M + BLOCK_M - 1) / BLOCK_M, nn = (p.N + TILE_N - 1) / TILE_N;
+  const long long tiles = nm * nn * (p.mode == OLB_GEMM_RAGGED_K ? p.num_experts : 1);
   int grid = static_cast<int>(tiles < num_sms ? tiles : num_sms);
   if (grid <= 0) return 0;
-  gemm_bf16_kernel<BLOCK_N, PEER><<<grid, PEER ? NUM_THREADS_STAGED : NUM_THREADS, L::TOTAL, stream>>>(ta, tb, tb2, peers, p);
+  gemm_bf16_kernel<BLOCK_N, PEER, EPI><<<grid, PEER ? NUM_THREADS_STAGED : NUM_THREADS, L::TOTAL, stream>>>(
+      tm.a, tm.b, tm.b2, tm.c, tm.c2, peers, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+template <bool PEER>
+static int dispatch(int block_n, int epi, const TensorMaps& tm, const PeerArg<PEER>& peers, const GemmParams& p, int sms,
+                    cudaStream_t stream) {
+  if (epi == EPI_SWIGLU) return block_n == 256 ? launch<256, PEER, EPI_SWIGLU>(tm, peers, p, sms, stream) : -12;
+  switch (block_n) {
+    case 256: return launch<256, PEER, EPI_PLAIN>(tm, peers, p, sms, stream);
+    case 128: return launch<128, PEER, EPI_PLAIN>(tm, peers, p, sms, stream);
+    case 64: return launch<64, PEER, EPI_PLAIN>(tm, peers, p, sms, stream);
+    default: return -12;
+  }
+}
+
+static int device_sm_count() {
+  constexpr int MAX_DEVICES = 64;
+  static int cached[MAX_DEVICES] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return 0;
+  if (cached[dev] == 0) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+  return cached[dev];
 }
 
 }  // namespace olb
 
 extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   using namespace olb;
-  static const bool debug = getenv("OLB_DEBUG_GEMM") != nullptr;
-  if (debug) {
-    fprintf(stderr, "[olb_gemm] M=%d N=%d K=%d a_mn=%d b_mn=%d mode=%d lda=%lld ldb=%lld ldc=%lld a_rows=%lld b_rows=%lld "
-            "acc=%d fp32=%d A=%p B=%p C=%p meta=%p\n", d->M, d->N, d->K, d->a_mn_major, d->b_mn_major, d->mode, d->lda,
-            d->ldb, d->ldc, d->a_rows, d->b_rows, d->accumulate, d->out_fp32, d->A, d->B, d->C, (const void*)d->meta);
-    fflush(stderr);
-  }
   if (d->M <= 0 || d->N <= 0) return 0;
   if ((d->lda % 8) || (d->ldb % 8) || (d->ldc % 8) || (d->N % 8) || (reinterpret_cast<uintptr_t>(d->A) & 15) ||
       (reinterpret_cast<uintptr_t>(d->B) & 15) || (reinterpret_cast<uintptr_t>(d->C) & 15))
     return -10;
+  const int epi = d->epilogue;
   int block_n = d->block_n;
-  if (block_n == 0) {
+  if (epi == OLB_EPI_SWIGLU) {
+    // N = width of act; B / B2 = gate / up weights (K-major, same layout); C = gate | up [rows, 2 N]; C2 = act [rows, N]
+    if (d->N % 128 || d->B2 == nullptr || d->C2 == nullptr || d->b_mn_major || d->a_mn_major || d->accumulate ||
+        d->out_fp32 || d->mode == OLB_GEMM_RAGGED_K || d->k_split || (d->ldc2 % 8) ||
+        (reinterpret_cast<uintptr_t>(d->B2) & 15) || (reinterpret_cast<uintptr_t>(d->C2) & 15) ||
+        ((d->row_src_of != nullptr) != (d->row_weights != nullptr)) || ((d->row_src_of != nullptr) != (d->row_k_of != nullptr)))
+      return -15;
+    block_n = 256;
+  } else if (block_n == 0) {
     if (d->mode != OLB_GEMM_DENSE) {
       block_n = (d->N % 256 == 0) ? 256 : (d->N % 128 == 0 ? 128 : 64);
       if (d->N % 64) return -11;
@@ -627,12 +892,8 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
       block_n = d->N > 128 ? 256 : (d->N > 64 ? 128 : 64);
     }
   }
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-  }
+  const int num_sms = device_sm_count();
+  if (num_sms <= 0) return -3;
 
   // cuTensorMapEncodeTiled is a driver call and needs a current context in the calling thread.
   // A thread that has only been handed tensors (an autograd worker whose first CUDA work is this
@@ -642,42 +903,44 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
     cudaFree(nullptr);
     context_bound = true;
   }
-  CUtensorMap ta, tb;
+  TensorMaps tm;
   int rc;
   // A: K-major -> global [a_rows, K] (inner K); MN-major -> global [K rows, M] (inner M).
   if (!d->a_mn_major)
-    rc = make_tmap_2d_bf16(&ta, d->A, d->K, d->a_rows, d->lda * 2, BLOCK_K, BLOCK_M);
+    rc = make_tmap_2d_bf16(&tm.a, d->A, d->K, d->a_rows, d->lda * 2, BLOCK_K, BLOCK_M);
   else
-    rc = make_tmap_2d_bf16(&ta, d->A, d->M, d->a_rows, d->lda * 2, 64, BLOCK_K);
+    rc = make_tmap_2d_bf16(&tm.a, d->A, d->M, d->a_rows, d->lda * 2, 64, BLOCK_K);
   if (rc) return rc;
-  if (!d->b_mn_major)
-    rc = make_tmap_2d_bf16(&tb, d->B, d->K, d->b_rows, d->ldb * 2, BLOCK_K, block_n);
-  else
-    rc = make_tmap_2d_bf16(&tb, d->B, d->N, d->b_rows, d->ldb * 2, 64, BLOCK_K);
-  if (rc) return rc;
-  // optional second B (same layout) for the K range [k_split, K)
-  CUtensorMap tb2 = tb;
   int kb_split = 0;
-  if (d->B2 != nullptr && d->k_split > 0) {
-    if (d->k_split % BLOCK_K || d->k_split >= d->K || d->mode == OLB_GEMM_RAGGED_K || (reinterpret_cast<uintptr_t>(d->B2) & 15))
-      return -13;
-    const int k1 = d->k_split, k2 = d->K - d->k_split;
-    // each map covers only its own K extent, so that reads past it are zero-filled as usual
-    if (!d->b_mn_major) {
-      rc = make_tmap_2d_bf16(&tb, d->B, k1, d->b_rows, d->ldb * 2, BLOCK_K, block_n);
-      if (!rc) rc = make_tmap_2d_bf16(&tb2, d->B2, k2, d->b_rows, d->ldb * 2, BLOCK_K, block_n);
-    } else {
-      rc = make_tmap_2d_bf16(&tb2, d->B2, d->N, d->b_rows, d->ldb * 2, 64, BLOCK_K);
-    }
+  if (epi == OLB_EPI_SWIGLU) {
+    rc = make_tmap_2d_bf16(&tm.b, d->B, d->K, d->b_rows, d->ldb * 2, BLOCK_K, 128);
+    if (!rc) rc = make_tmap_2d_bf16(&tm.b2, d->B2, d->K, d->b_rows, d->ldb * 2, BLOCK_K, 128);
     if (rc) return rc;
-    kb_split = d->k_split / BLOCK_K;
+  } else {
+    if (!d->b_mn_major)
+      rc = make_tmap_2d_bf16(&tm.b, d->B, d->K, d->b_rows, d->ldb * 2, BLOCK_K, block_n);
+    else
+      rc = make_tmap_2d_bf16(&tm.b, d->B, d->N, d->b_rows, d->ldb * 2, 64, BLOCK_K);
+    if (rc) return rc;
+    // optional second B (same layout) for the K range [k_split, K)
+    tm.b2 = tm.b;
+    if (d->B2 != nullptr && d->k_split > 0) {
+      if (d->k_split % BLOCK_K || d->k_split >= d->K || d->mode == OLB_GEMM_RAGGED_K || (reinterpret_cast<uintptr_t>(d->B2) & 15))
+        return -13;
+      const int k1 = d->k_split, k2 = d->K - d->k_split;
+      // each map covers only its own K extent, so that reads past it are zero-filled as usual
+      if (!d->b_mn_major) {
+        rc = make_tmap_2d_bf16(&tm.b, d->B, k1, d->b_rows, d->ldb * 2, BLOCK_K, block_n);
+        if (!rc) rc = make_tmap_2d_bf16(&tm.b2, d->B2, k2, d->b_rows, d->ldb * 2, BLOCK_K, block_n);
+      } else {
+        rc = make_tmap_2d_bf16(&tm.b2, d->B2, d->N, d->b_rows, d->ldb * 2, 64, BLOCK_K);
+      }
+      if (rc) return rc;
+      kb_split = d->k_split / BLOCK_K;
+    }
   }
 
-  if (debug) {
-    fprintf(stderr, "[olb_gemm] tensor maps ok, block_n=%d\n", block_n);
-    fflush(stderr);
-  }
-  GemmParams p;
+  GemmParams p{};
   p.C = d->C;
   p.ldc = d->ldc;
   p.M = d->M;
@@ -696,40 +959,81 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   p.m_rotate_blocks = 0;
   p.blk_range = d->mode == OLB_GEMM_RAGGED_M ? d->blk_range : nullptr;
   p.status = d->status;
+  p.row_src_of = d->row_src_of;
+  p.row_k_of = d->row_k_of;
+  p.row_weights = d->row_weights;
+  p.row_topk = d->row_topk;
+
+  // Output through tensor-map stores whenever a 2D map describes it: no read-modify-write, and for the per-expert
+  // weight gradients experts that tile exactly (a box must not run into the next expert's rows).
+  tm.c = tm.a;
+  tm.c2 = tm.a;
+  p.c_tma = 0;
+  if (epi == OLB_EPI_SWIGLU) {
+    rc = make_tmap_2d(&tm.c, d->C, 2ull * d->N, d->M, d->ldc * 2, 64, 32, false);
+    if (!rc) rc = make_tmap_2d(&tm.c2, d->C2, d->N, d->M, d->ldc2 * 2, 64, 32, false);
+    if (rc) return rc;
+    p.c_tma = 1;
+  } else if (!d->accumulate) {
+    const uint64_t esz = d->out_fp32 ? 4 : 2;
+    uint64_t rows = d->M;
+    bool ok = (d->ldc * esz) % 16 == 0;
+    if (d->mode == OLB_GEMM_RAGGED_K) {
+      ok = ok && d->M % BLOCK_M == 0 && d->c_expert_stride == static_cast<long long>(d->M) * d->ldc;
+      rows = static_cast<uint64_t>(d->M) * d->num_experts;
+    }
+    if (ok) {
+      rc = make_tmap_2d(&tm.c, d->C, d->N, rows, d->ldc * esz, d->out_fp32 ? 32 : 64, 32, d->out_fp32 != 0);
+      if (rc) return rc;
+      p.c_tma = 1;
+    }
+  }
+
   const int sms = d->max_ctas > 0 && d->max_ctas < num_sms ? d->max_ctas : num_sms;
   if (d->n_peers > 0) {
-    // All-gather of A's rows fused into the GEMM (see PeerArg<true>).
     const bool push = d->C_peers != nullptr;
     if (d->mode == OLB_GEMM_RAGGED_M) {
-      // Expert-parallel combine transport: finished rows of C go to the owners of their tokens.
-      if (!push || d->n_peers > 8 || d->stage_flags == nullptr || d->ep_src_of == nullptr || d->ep_k_of == nullptr ||
-          d->ep_tokens <= 0 || d->ep_topk <= 0 || d->out_fp32 || d->accumulate || d->blk_range != nullptr || d->N % 8)
-        return -14;
       PeerArg<true> peers{};
-      for (int r = 0; r < 8; ++r) {
-        peers.push_dst[r] = d->C_peers[r < d->n_peers ? r : 0];
-        if (reinterpret_cast<uintptr_t>(peers.push_dst[r]) & 15) return -14;
-      }
       peers.flags = d->stage_flags;
       peers.n = d->n_peers;
       peers.me = d->my_peer;
-      peers.push = 2;
-      peers.flags_full = 4 * ((d->N + block_n - 1) / block_n);
-      peers.c_base = d->C;
-      peers.ldc = d->ldc;
-      peers.ld = d->N;
-      peers.row_vecs = d->N / 8;
       peers.src_of = d->ep_src_of;
       peers.k_of = d->ep_k_of;
       peers.T = d->ep_tokens;
       peers.topk = d->ep_topk;
-      switch (block_n) {
-        case 256: return launch<256, true>(ta, tb, tb2, peers, p, sms, stream);
-        case 128: return launch<128, true>(ta, tb, tb2, peers, p, sms, stream);
-        case 64: return launch<64, true>(ta, tb, tb2, peers, p, sms, stream);
-        default: return -12;
+      if (d->n_peers > 8 || d->stage_flags == nullptr || d->ep_src_of == nullptr || d->ep_tokens <= 0 ||
+          d->blk_range != nullptr)
+        return -14;
+      if (push) {
+        // Expert-parallel combine transport: finished rows of C go to the owners of their tokens.
+        if (epi != OLB_EPI_PLAIN || d->ep_k_of == nullptr || d->ep_topk <= 0 || d->out_fp32 || d->accumulate || d->N % 8)
+          return -14;
+        for (int r = 0; r < 8; ++r) {
+          peers.push_dst[r] = d->C_peers[r < d->n_peers ? r : 0];
+          if (reinterpret_cast<uintptr_t>(peers.push_dst[r]) & 15) return -14;
+        }
+        peers.push = 2;
+        peers.flags_full = 4 * ((d->N + block_n - 1) / block_n);
+        peers.c_base = d->C;
+        peers.ldc = d->ldc;
+        peers.ld = d->N;
+        peers.row_vecs = d->N / 8;
+      } else {
+        // Expert-parallel dispatch: the routed token rows are gathered into A from their owners' buffers.
+        if (d->A_peers == nullptr || d->a_mn_major || d->K % 8 || d->a_src_ld % 8 || d->a_src_ld < d->K) return -14;
+        for (int r = 0; r < 8; ++r) {
+          peers.src[r] = d->A_peers[r < d->n_peers ? r : 0];
+          if (reinterpret_cast<uintptr_t>(peers.src[r]) & 15) return -14;
+        }
+        peers.push = 3;
+        peers.dst = const_cast<void*>(d->A);
+        peers.ld = d->lda;
+        peers.src_ld = d->a_src_ld;
+        peers.row_vecs = d->K / 8;
       }
+      return dispatch<true>(block_n, epi, tm, peers, p, sms, stream);
     }
+    if (epi != OLB_EPI_PLAIN) return -14;
     if (d->n_peers > 8 || d->mode != OLB_GEMM_DENSE || d->stage_flags == nullptr || d->a_peer_rows <= 0 ||
         d->a_peer_rows % BLOCK_M || d->my_peer < 0 || d->my_peer >= d->n_peers || d->M != d->n_peers * d->a_peer_rows)
       return -14;
@@ -762,18 +1066,8 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
       peers.row_vecs = d->K / 8;
       p.m_rotate_blocks = (d->my_peer * d->a_peer_rows) / BLOCK_M;  // own rows first
     }
-    switch (block_n) {
-      case 256: return launch<256, true>(ta, tb, tb2, peers, p, sms, stream);
-      case 128: return launch<128, true>(ta, tb, tb2, peers, p, sms, stream);
-      case 64: return launch<64, true>(ta, tb, tb2, peers, p, sms, stream);
-      default: return -12;
-    }
+    return dispatch<true>(block_n, epi, tm, peers, p, sms, stream);
   }
   PeerArg<false> nopeers{};
-  switch (block_n) {
-    case 256: return launch<256, false>(ta, tb, tb2, nopeers, p, sms, stream);
-    case 128: return launch<128, false>(ta, tb, tb2, nopeers, p, sms, stream);
-    case 64: return launch<64, false>(ta, tb, tb2, nopeers, p, sms, stream);
-    default: return -12;
-  }
+  return dispatch<false>(block_n, epi, tm, nopeers, p, sms, stream);
 }

@@ -11,6 +11,7 @@ extern "C" {
 
 // ---------------------------------------------------------------- GEMM (gemm_tcgen05.cu)
 enum { OLB_GEMM_DENSE = 0, OLB_GEMM_RAGGED_M = 1, OLB_GEMM_RAGGED_K = 2 };
+enum { OLB_EPI_PLAIN = 0, OLB_EPI_SWIGLU = 1 };
 
 typedef struct {
   const void* A;  // bf16. K-major: [a_rows, K] with row stride lda; MN-major: [a_rows (=K extent), M]
@@ -57,6 +58,25 @@ typedef struct {
   const int* ep_k_of;
   int ep_tokens, ep_topk;
   const int* blk_range;      // RAGGED_M, optional (device memory): only row blocks [blk_range[0], blk_range[1])
+  // Expert-parallel dispatch fused into the GEMM (RAGGED_M mode with n_peers > 0, A_peers set, C_peers null): row u of
+  // A is token ep_src_of[u] of the group-wide numbering (ep_tokens per rank); extra warps copy it from
+  // A_peers[token / ep_tokens] + (token % ep_tokens) * a_src_ld into A + u * lda (zeros for padding rows) and count the
+  // rows per 128-row block in stage_flags (zero at launch); the TMA producer waits for a block before it loads it.
+  // With n_peers == 1 this is the local permutation of the tokens into expert-grouped rows.
+  long long a_src_ld;
+  // Fused gate|up projection (epilogue == OLB_EPI_SWIGLU; DENSE or RAGGED_M, K-major operands): B / B2 are the gate /
+  // up weights ([b_rows, K], b_expert_rows rows per expert), N the width of one of them per expert.  One tile holds
+  // 128 gate and the matching 128 up columns; the epilogue writes gate | up to C [M, 2 N] (row stride ldc) and
+  // w(row) * silu(gate) * up to C2 [M, N] (row stride ldc2), computed from the bf16-rounded gate and up values.
+  // w(row) = row_weights[row_src_of[row] * row_topk + row_k_of[row]], 0 where row_src_of[row] < 0; 1 when the three
+  // pointers are null.
+  int epilogue;
+  void* C2;
+  long long ldc2;
+  const int* row_src_of;
+  const int* row_k_of;
+  const float* row_weights;
+  int row_topk;
 } olb_gemm_desc;
 
 int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream);
@@ -193,6 +213,11 @@ int olb_adamw_step(const void* grad, int grad_fp32, float* master, float* m, flo
 // ST_TIMEOUT_PEER (5) and the kernel returns, so the context stays usable.
 int olb_symm_barrier(void* const* pads, int my_rank, int n, int channel, unsigned epoch, int* status,
                      unsigned long long wait_limit_ns, cudaStream_t stream);
+// idx_all[p][off + i] = idx[i], w_all[p][off + i] = w[i] for every peer p and i < count (all-gather by stores).
+int olb_ep_publish_meta(void* const* idx_all, void* const* w_all, int n, const int* idx, const float* w, long long off,
+                        long long count, cudaStream_t stream);
+// out[t, :] = sum_k recv[t, k, :] (bf16 [T, K, cols] -> bf16 [T, cols], fp32 accumulation, fixed order).
+int olb_sum_slots(const void* recv, int T, int K, int cols, void* out, cudaStream_t stream);
 // out[row,:] = peer_x[g / T][g % T, :], g = src_of[row] (global token id), rows < meta[0]*128; padding -> 0.
 int olb_ep_gather_rows(const void* const* peer_x, int n, int T, const int* src_of, const int* meta,
                        const int* blk_range, void* out, int cap, int cols, cudaStream_t stream);

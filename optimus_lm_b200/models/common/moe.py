@@ -110,7 +110,7 @@ class SparseMoeBlock(nn.Module):
         self.force_uniform_routing = getattr(config, "force_uniform_routing", False)
         self.mask = None
         self.use_allreduce_for_reducescatter = False
-        self.capacity_factor = float(getattr(config, "moe_capacity_factor", 4.0))
+        self.capacity_factor = float(getattr(config, "moe_capacity_factor", 0.0))
         self.ep_transport = "alltoall" if getattr(config, "use_fused_ep_alltoall", True) else "allgather"
         self._a2a = None  # lazily built fused dispatcher
         self.last_router_stats = None
@@ -136,10 +136,10 @@ class SparseMoeBlock(nn.Module):
         return router_logits, w, idx
 
     # ------------------------------------------------------------------ experts
-    def _local_experts(self, x, w, idx, cap=None):
+    def _local_experts(self, x, w, idx, cap=None, exact=False):
         if self.merged:
             wg, wu, wd = self.experts.weights()
-            return OF.moe_experts(x, w.float() if x.is_cuda else w, idx, wg, wu, wd, self.expert_start_idx, cap)
+            return OF.moe_experts(x, w.float() if x.is_cuda else w, idx, wg, wu, wd, self.expert_start_idx, cap, exact)
         if self._grouped_per_expert(x):
             # per-expert parameters on the fast path: stack them (about 0.1 ms of copies per layer) and run the grouped
             # GEMM pipeline; autograd hands each expert its slice of the stacked weight gradient.  The reference
@@ -148,7 +148,7 @@ class SparseMoeBlock(nn.Module):
             wg = torch.stack([e.gate_proj.weight for e in self.experts])
             wu = torch.stack([e.up_proj.weight for e in self.experts])
             wd = torch.stack([e.down_proj.weight for e in self.experts])
-            return OF.moe_experts(x, w.float(), idx, wg, wu, wd, self.expert_start_idx, cap)
+            return OF.moe_experts(x, w.float(), idx, wg, wu, wd, self.expert_start_idx, cap, exact)
         return _experts_loop(self.experts, x, w, idx, self.expert_start_idx)
 
     def _grouped_per_expert(self, x) -> bool:
@@ -176,7 +176,7 @@ class SparseMoeBlock(nn.Module):
         if x_all.is_cuda and (self.merged or self._grouped_per_expert(x_all)):
             cap = OF.moe_capacity_rows(T * ep, self.num_experts_per_tok, self.num_experts_per_rank, ep,
                                        self.capacity_factor)
-        y_all = self._local_experts(x_all, w_all, i_all, cap)
+        y_all = self._local_experts(x_all, w_all, i_all, cap, exact=not self.capacity_factor)
         forward_synchronize_backward_identity.apply(g)
         return forward_reducescatter_backward_allgather.apply(y_all, pmap.ep_ind, ep, g,
                                                               self.use_allreduce_for_reducescatter, False)

@@ -235,7 +235,7 @@ class DeepseekV3ParallelMoE(nn.Module):
             config=config, intermediate_size=config.moe_intermediate_size * config.n_shared_experts)
         self.use_allreduce_for_reducescatter = False
         self.ckpt = bool(config.use_activation_checkpointing and (config.activation_checkpointing_level & 1))
-        self.capacity_factor = float(getattr(config, "moe_capacity_factor", 4.0))
+        self.capacity_factor = float(getattr(config, "moe_capacity_factor", 0.0))
         self.ep_transport = "alltoall" if getattr(config, "use_fused_ep_alltoall", True) else "allgather"
         self._a2a = None
         if self.merged:

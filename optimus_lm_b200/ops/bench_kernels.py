@@ -136,7 +136,7 @@ def profile_case(name: str, launches: int = 4):
         go = torch.randn(T, H, device="cuda").to(torch.bfloat16)
 
         def fn():
-            y = _FusedEPMoEFn.apply(x, tw, idx, wg, wu, wd, sg, 0, cap)
+            y = _FusedEPMoEFn.apply(x, tw, idx, wg, wu, wd, sg, 0, cap, False)
             y.backward(go)
     elif name in ("gemm-allgather", "gemm-push"):
         # The GEMM variants with a collective inside, with the four "peers" standing in this GPU's memory: the stager

@@ -602,14 +602,32 @@ def moe_capacity_rows(T: int, K: int, E_loc: int, ep: int = 1, capacity_factor: 
 
 
 _PART_CUTS = {}
+_FLAG_SCRATCH = {}
+ROW_GRANULE = 2048    # exact-sized expert buffers are rounded up to this many rows (fewer distinct allocation sizes)
+
+
+def stage_flags(device, rows: int) -> torch.Tensor:
+    """Per-device int32 scratch with one counter per 128-row block, for the GEMM variants whose extra warps move rows
+    (the bindings zero it before the launch).  Launches on one stream follow each other, so one buffer serves all."""
+    need = rows // 128 + 2
+    t = _FLAG_SCRATCH.get(device)
+    if t is None or t.numel() < need:
+        t = _FLAG_SCRATCH[device] = torch.empty(max(need, 1024), dtype=torch.int32, device=device)
+    return t
 
 
 class MoEIndex:
-    """Device-resident permutation of routed (token, k) pairs into expert-grouped rows."""
+    """Device-resident permutation of routed (token, k) pairs into expert-grouped rows.
 
-    __slots__ = ("row_of", "src_of", "k_of", "meta", "offsets", "counts", "cap", "E_loc", "K")
+    ``cap`` bounds the index arrays.  ``rows`` is what the activation buffers of this layer hold: ``cap`` itself, or,
+    with ``exact``, the number of 128-row blocks the routing actually produced (one 4-byte read of the device-side
+    count, rounded up to ``ROW_GRANULE``).  With expert parallelism the worst case is every token of every rank
+    choosing this rank's experts; sizing the saved activations for that would not fit, sizing them for a fixed
+    multiple of the balanced share can overflow, so the count is read instead and no routed pair is ever dropped."""
 
-    def __init__(self, topk_idx: torch.Tensor, e_start: int, E_loc: int, cap: int):
+    __slots__ = ("row_of", "src_of", "k_of", "meta", "offsets", "counts", "cap", "rows", "E_loc", "K")
+
+    def __init__(self, topk_idx: torch.Tensor, e_start: int, E_loc: int, cap: int, exact: bool = False):
         C = extension()
         T, K = topk_idx.shape
         dev = topk_idx.device
@@ -623,6 +641,10 @@ class MoEIndex:
         self.cap, self.E_loc, self.K = cap, E_loc, K
         C.moe_build_index(topk_idx.contiguous(), e_start, E_loc, cap, ws, self.row_of, self.src_of, self.k_of,
                           self.meta, self.offsets, self.counts, status_word(dev))
+        self.rows = cap
+        if exact:
+            used = int(self.meta[0].item()) * 128
+            self.rows = min(cap, max(ROW_GRANULE, -(-used // ROW_GRANULE) * ROW_GRANULE))
 
     def part_ranges(self, parts: int) -> torch.Tensor:
         """``[parts, 2]`` int32 (device): first and one-past-last 128-row block of each group of consecutive local
@@ -640,14 +662,14 @@ class MoEIndex:
 def grouped_linear_fwd(xp, w, index: MoEIndex, out=None, blk_range=None):
     """``y[rows of e] = xp[rows of e] @ w[e].T`` for merged weights ``w [E, N, K]``."""
     E, N, K = w.shape
-    return gemm(xp, w.view(E * N, K), index.cap, N, K, mode=GEMM_RAGGED_M, meta=index.meta, b_expert_rows=N, out=out,
+    return gemm(xp, w.view(E * N, K), index.rows, N, K, mode=GEMM_RAGGED_M, meta=index.meta, b_expert_rows=N, out=out,
                 blk_range=blk_range)
 
 
 def grouped_linear_dgrad(dy, w, index: MoEIndex, out=None, accumulate=False, blk_range=None):
     """``dx[rows of e] (+)= dy[rows of e] @ w[e]``."""
     E, N, K = w.shape
-    return gemm(dy, w.view(E * N, K), index.cap, K, N, b_mn_major=True, mode=GEMM_RAGGED_M, meta=index.meta,
+    return gemm(dy, w.view(E * N, K), index.rows, K, N, b_mn_major=True, mode=GEMM_RAGGED_M, meta=index.meta,
                 b_expert_rows=N, out=out, accumulate=accumulate, blk_range=blk_range)
 
 
@@ -656,7 +678,7 @@ def grouped_linear_dgrad_pair(dh, w1, w2, index: MoEIndex, out=None):
     gradient of the gate and up projections, whose output gradients sit side by side in ``dh``)."""
     E, N, K = w1.shape
     assert w2.shape == w1.shape and dh.shape[1] == 2 * N
-    return gemm(dh, w1.view(E * N, K), index.cap, K, 2 * N, b_mn_major=True, mode=GEMM_RAGGED_M, meta=index.meta,
+    return gemm(dh, w1.view(E * N, K), index.rows, K, 2 * N, b_mn_major=True, mode=GEMM_RAGGED_M, meta=index.meta,
                 b_expert_rows=N, out=out, b2=w2.view(E * N, K), k_split=N)
 
 
@@ -664,36 +686,69 @@ def grouped_linear_wgrad(dy, xp, index: MoEIndex, N: int, K: int, holder: Option
     """``dw[e] = dy[rows of e].T @ xp[rows of e]`` -> [E, N, K].  With a ``DirectGrad`` holder the result goes
     (or is added) into the holder's buffer and ``None`` is returned."""
     if holder is not None:
-        gemm(dy, xp, N, K, index.cap, a_mn_major=True, b_mn_major=True, mode=GEMM_RAGGED_K, meta=index.offsets,
+        gemm(dy, xp, N, K, index.rows, a_mn_major=True, b_mn_major=True, mode=GEMM_RAGGED_K, meta=index.offsets,
              num_experts=index.E_loc, c_expert_stride=N * K, out=holder.buf, accumulate=holder.ready)
         holder.ready = True
         return None
-    return gemm(dy, xp, N, K, index.cap, a_mn_major=True, b_mn_major=True, mode=GEMM_RAGGED_K, meta=index.offsets,
+    return gemm(dy, xp, N, K, index.rows, a_mn_major=True, b_mn_major=True, mode=GEMM_RAGGED_K, meta=index.offsets,
                 num_experts=index.E_loc, c_expert_stride=N * K)
+
+
+def grouped_gateup_swiglu(x_ptrs, x_ld: int, tokens: int, weights, wg, wu, index: MoEIndex):
+    """Gate and up projections of the local experts with the dispatch in front and the activation behind, one launch:
+    extra warps of the GEMM fetch token ``src_of[u]`` from ``x_ptrs[src_of[u] // tokens]`` into row ``u`` of the
+    expert-grouped operand (over NVLink when the token lives on another GPU), the tensor-core warps start on the first
+    row blocks while later ones are still arriving, and the epilogue writes ``gate | up`` and
+    ``weights[src, k] * silu(gate) * up``.  Returns ``(xp, h, act)``."""
+    C = extension()
+    E, I, H = wg.shape
+    dev = wg.device
+    rows = index.rows
+    xp = torch.empty((rows, H), dtype=wg.dtype, device=dev)
+    h = torch.empty((rows, 2 * I), dtype=wg.dtype, device=dev)
+    act = torch.empty((rows, I), dtype=wg.dtype, device=dev)
+    if I % 128:
+        # widths the paired gate|up tile does not cover: separate launches (gather, two projections, activation)
+        C.ep_gather_rows(list(x_ptrs), tokens, index.src_of, index.meta, xp, None)
+        grouped_linear_fwd(xp, wg, index, out=h[:, :I])
+        grouped_linear_fwd(xp, wu, index, out=h[:, I:])
+        C.swiglu_rowscale_fwd(h[:, :I], h[:, I:], index.src_of, index.k_of, weights, index.meta, act)
+        return xp, h, act
+    C.gemm_gateup_swiglu(xp, wg.view(E * I, H), wu.view(E * I, H), h, act, rows, I, H, index.meta, index.src_of,
+                         index.k_of, weights, E, list(x_ptrs), x_ld, tokens, stage_flags(dev, rows), status_word(dev))
+    return xp, h, act
+
+
+def grouped_gather_dgrad(y_ptrs, y_ld: int, tokens: int, w, index: MoEIndex):
+    """``dyp[u] = dout[src_of[u]]`` gathered inside the launch that computes ``dact = dyp @ w[e]`` (input gradient of
+    the down projection, ``w [E, H, I]``).  Returns ``(dyp, dact)``."""
+    C = extension()
+    E, H, I = w.shape
+    dev = w.device
+    rows = index.rows
+    dyp = torch.empty((rows, H), dtype=w.dtype, device=dev)
+    dact = torch.empty((rows, I), dtype=w.dtype, device=dev)
+    C.gemm_ep_gather(dyp, w.view(E * H, I), dact, rows, I, H, True, index.meta, index.src_of, H, E, list(y_ptrs), y_ld,
+                     tokens, stage_flags(dev, rows), status_word(dev))
+    return dyp, dact
 
 
 class _MoEExpertsFn(torch.autograd.Function):
     """Local expert computation on expert-grouped rows:
-    index build -> gather -> grouped gate/up GEMMs -> weighted SwiGLU -> grouped down GEMM ->
+    index build -> [gather + grouped gate|up GEMM + weighted SwiGLU] (one launch) -> grouped down GEMM ->
     unweighted combine.  The routing weight is folded into the activation, so the backward
     needs neither the expert outputs nor a weighted scatter."""
 
     @staticmethod
-    def forward(ctx, x, topk_w, topk_idx, wg, wu, wd, e_start, cap, holders=(None, None, None)):
+    def forward(ctx, x, topk_w, topk_idx, wg, wu, wd, e_start, cap, holders=(None, None, None), exact=False):
         C = extension()
         T, H = x.shape
         E_loc, I, _ = wg.shape
         ctx.holders = holders
         x = x.contiguous()
         topk_w = topk_w.contiguous().float()
-        index = MoEIndex(topk_idx, e_start, E_loc, cap)
-        xp = torch.empty((cap, H), dtype=x.dtype, device=x.device)
-        C.moe_gather_rows(x, index.src_of, index.meta, xp)
-        h = torch.empty((cap, 2 * I), dtype=x.dtype, device=x.device)
-        grouped_linear_fwd(xp, wg, index, out=h[:, :I])
-        grouped_linear_fwd(xp, wu, index, out=h[:, I:])
-        act = torch.empty((cap, I), dtype=x.dtype, device=x.device)
-        C.swiglu_rowscale_fwd(h[:, :I], h[:, I:], index.src_of, index.k_of, topk_w, index.meta, act)
+        index = MoEIndex(topk_idx, e_start, E_loc, cap, exact)
+        xp, h, act = grouped_gateup_swiglu([x.data_ptr()], H, T, topk_w, wg, wu, index)
         y = grouped_linear_fwd(act, wd, index)
         out = torch.empty((T, H), dtype=x.dtype, device=x.device)
         C.moe_combine(y, index.row_of, None, out)
@@ -708,14 +763,11 @@ class _MoEExpertsFn(torch.autograd.Function):
         xp, h, act, topk_w, wg, wu, wd = ctx.saved_tensors
         index = ctx.index
         T, H, I, E_loc = ctx.dims
-        cap = index.cap
         dout = dout.contiguous()
-        # d(y) = gather of dout (the combine was an unweighted sum)
-        dyp = torch.empty((cap, H), dtype=dout.dtype, device=dout.device)
-        C.moe_gather_rows(dout, index.src_of, index.meta, dyp)
+        # d(y) = gather of dout (the combine was an unweighted sum), inside the down projection's input-gradient launch
+        dyp, dact = grouped_gather_dgrad([dout.data_ptr()], H, T, wd, index)
         hg, hu, hd = ctx.holders
         dwd = grouped_linear_wgrad(dyp, act, index, H, I, hd) if ctx.needs_input_grad[5] else None
-        dact = grouped_linear_dgrad(dyp, wd, index)
         del dyp
         dh = torch.empty_like(h)
         dtopk = torch.zeros_like(topk_w)
@@ -724,27 +776,25 @@ class _MoEExpertsFn(torch.autograd.Function):
         del dact
         dwg = grouped_linear_wgrad(dh[:, :I], xp, index, I, H, hg) if ctx.needs_input_grad[3] else None
         dwu = grouped_linear_wgrad(dh[:, I:], xp, index, I, H, hu) if ctx.needs_input_grad[4] else None
-        if I % 64 == 0:
-            dxp = grouped_linear_dgrad_pair(dh, wg, wu, index)
-        else:
-            dxp = grouped_linear_dgrad(dh[:, :I], wg, index)
-            grouped_linear_dgrad(dh[:, I:], wu, index, out=dxp, accumulate=True)
+        dxp = grouped_linear_dgrad_pair(dh, wg, wu, index)
         dx = torch.empty((T, H), dtype=dout.dtype, device=dout.device)
         C.moe_combine(dxp, index.row_of, None, dx)
-        return dx, dtopk, None, dwg, dwu, dwd, None, None, None
+        return dx, dtopk, None, dwg, dwu, dwd, None, None, None, None
 
 
-def moe_experts(x, topk_w, topk_idx, wg, wu, wd, e_start=0, cap: Optional[int] = None):
+def moe_experts(x, topk_w, topk_idx, wg, wu, wd, e_start=0, cap: Optional[int] = None, exact: bool = False):
     """Partial MoE output of the local experts for tokens ``x [T,H]``.
 
     ``topk_idx`` holds global expert ids; pairs routed to other ranks' experts are skipped.
     ``wg/wu [E_loc, I, H]``, ``wd [E_loc, H, I]`` (the merged-MLP layout of the reference,
-    optimus/models/common/moe.py:379-405)."""
+    optimus/models/common/moe.py:379-405).  ``exact``: ``cap`` is a worst case that is rarely reached (tokens of a
+    whole expert-parallel group); size the activation buffers from the routed count instead (see ``MoEIndex``)."""
     E_loc, I, H = wg.shape
     if _kernel_ok(x, wg, wu, wd) and topk_idx.dtype == torch.int32 and H % 64 == 0 and I % 64 == 0 and E_loc <= 256:
         if cap is None:
             cap = moe_capacity_rows(x.shape[0], topk_idx.shape[1], E_loc)
-        return _MoEExpertsFn.apply(x, topk_w, topk_idx, wg, wu, wd, e_start, cap, (_holder(wg), _holder(wu), _holder(wd)))
+        return _MoEExpertsFn.apply(x, topk_w, topk_idx, wg, wu, wd, e_start, cap,
+                                   (_holder(wg), _holder(wu), _holder(wd)), exact)
     return moe_experts_reference(x, topk_w, topk_idx.long(), wg, wu, wd, e_start)
 
 

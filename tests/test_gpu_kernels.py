@@ -272,6 +272,124 @@ def test_grouped_gemm_with_fused_combine_push(n, T, E_loc, K, H, I):
     assert torch.isnan(torch.stack(recv).float()).all(dim=-1).eq(~written).all()   # nothing else was touched
 
 
+@pytest.mark.parametrize("n,T,E_loc,K,H,I", [(1, 700, 8, 2, 256, 512), (2, 256, 4, 2, 256, 128), (4, 512, 8, 4, 512, 256)])
+def test_gateup_swiglu_launch_with_fused_dispatch(n, T, E_loc, K, H, I):
+    """One launch = gather of the routed rows (from n token buffers standing in this GPU's memory) + gate and up
+    projections + routing-weighted SwiGLU.  Checked bit for bit against the separate kernels, and element-wise against
+    fp32 torch."""
+    E = n * E_loc
+    e_start = E_loc if n > 1 else 0
+    g = torch.Generator(device="cuda").manual_seed(5)
+    idx_all = torch.stack([torch.randperm(E, device="cuda", generator=g)[:K] for _ in range(n * T)]).to(torch.int32)
+    w_all = torch.rand(n * T, K, device="cuda", generator=g)
+    xs = [bf(T, H, seed=40 + r) for r in range(n)]
+    wg, wu = bf(E_loc, I, H, seed=2, scale=0.05), bf(E_loc, I, H, seed=3, scale=0.05)
+    cap = OF.moe_capacity_rows(n * T, K, E_loc)
+    ix = OF.MoEIndex(idx_all, e_start, E_loc, cap)
+    xp, h, act = OF.grouped_gateup_swiglu([t.data_ptr() for t in xs], H, T, w_all, wg, wu, ix)
+    used = int(ix.meta[0].item()) * 128
+    src = ix.src_of[:used].long()
+    x_cat = torch.cat(xs)
+    want_xp = torch.where((src >= 0)[:, None], x_cat[src.clamp(min=0)], torch.zeros((), dtype=torch.bfloat16, device="cuda"))
+    assert torch.equal(xp[:used], want_xp)
+    hg = OF.grouped_linear_fwd(xp, wg, ix)
+    hu = OF.grouped_linear_fwd(xp, wu, ix)
+    assert torch.equal(h[:used, :I], hg[:used]) and torch.equal(h[:used, I:], hu[:used])
+    act2 = torch.empty_like(act)
+    from optimus_lm_b200.ops import extension
+    extension().swiglu_rowscale_fwd(h[:, :I], h[:, I:], ix.src_of, ix.k_of, w_all, ix.meta, act2)
+    assert (act[:used].float() - act2[:used].float()).abs().max().item() <= 1e-2 * act2[:used].float().abs().max().item() + 1e-6
+    assert rel_err(act[:used], act2[:used]) < 2e-3
+    # against fp32 torch, element by element
+    rows = torch.nonzero(src >= 0).flatten()
+    e_of = ix.meta[1:1 + used // 128].long().repeat_interleave(128)[rows]
+    xr = x_cat[src[rows]].float()
+    gr = torch.einsum("rh,rih->ri", xr, wg.float()[e_of])
+    ur = torch.einsum("rh,rih->ri", xr, wu.float()[e_of])
+    wr = w_all[src[rows], ix.k_of[:used].long()[rows]]
+    want = wr[:, None] * F.silu(gr) * ur
+    got = act[rows].float()
+    assert rel_err(got, want) < 1e-2
+    assert (got - want).abs().max().item() < 0.05 * want.abs().max().item() + 1e-3
+    assert act[:used][src < 0].abs().max().item() == 0 if (src < 0).any() else True
+
+
+def test_dense_gateup_swiglu_launch():
+    """The same epilogue on a dense MLP (no routing weights, no gather)."""
+    from optimus_lm_b200.ops import extension
+    M, H, I = 1000, 256, 384
+    x, wg, wu = bf(M, H, seed=1), bf(I, H, seed=2, scale=0.05), bf(I, H, seed=3, scale=0.05)
+    h = torch.empty(M, 2 * I, dtype=torch.bfloat16, device="cuda")
+    act = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
+    extension().gemm_gateup_swiglu(x, wg, wu, h, act, M, I, H, None, None, None, None, 1, [], 0, 0, None,
+                                   OF.status_word("cuda"))
+    assert torch.equal(h[:, :I], OF.gemm(x, wg, M, I, H)) and torch.equal(h[:, I:], OF.gemm(x, wu, M, I, H))
+    want = F.silu(h[:, :I].float()) * h[:, I:].float()
+    assert (act.float() - want).abs().max().item() < 1e-2 * want.abs().max().item() + 1e-6
+    ref = F.silu(x.float() @ wg.float().t()) * (x.float() @ wu.float().t())
+    assert rel_err(act, ref) < 1e-2
+
+
+@pytest.mark.parametrize("n,T,E_loc,K,H,I", [(1, 700, 8, 2, 256, 512), (4, 512, 8, 4, 512, 256)])
+def test_down_dgrad_launch_with_fused_gather(n, T, E_loc, K, H, I):
+    E = n * E_loc
+    e_start = E_loc if n > 1 else 0
+    g = torch.Generator(device="cuda").manual_seed(6)
+    idx_all = torch.stack([torch.randperm(E, device="cuda", generator=g)[:K] for _ in range(n * T)]).to(torch.int32)
+    ds = [bf(T, H, seed=50 + r) for r in range(n)]
+    wd = bf(E_loc, H, I, seed=4, scale=0.05)
+    ix = OF.MoEIndex(idx_all, e_start, E_loc, OF.moe_capacity_rows(n * T, K, E_loc))
+    dyp, dact = OF.grouped_gather_dgrad([t.data_ptr() for t in ds], H, T, wd, ix)
+    used = int(ix.meta[0].item()) * 128
+    src = ix.src_of[:used].long()
+    want_dyp = torch.where((src >= 0)[:, None], torch.cat(ds)[src.clamp(min=0)],
+                           torch.zeros((), dtype=torch.bfloat16, device="cuda"))
+    assert torch.equal(dyp[:used], want_dyp)
+    assert torch.equal(dact[:used], OF.grouped_linear_dgrad(dyp, wd, ix)[:used])
+
+
+def test_gate_up_dgrad_launch_with_fused_combine_push():
+    """Backward combine: the K-concatenated input-gradient launch sends its rows to the token owners' buffers."""
+    from optimus_lm_b200.ops import extension
+    n, T, E_loc, K, H, I = 4, 512, 8, 4, 512, 256
+    E, e_start = n * E_loc, E_loc
+    g = torch.Generator(device="cuda").manual_seed(8)
+    idx_all = torch.stack([torch.randperm(E, device="cuda", generator=g)[:K] for _ in range(n * T)]).to(torch.int32)
+    cap = OF.moe_capacity_rows(n * T, K, E_loc)
+    ix = OF.MoEIndex(idx_all, e_start, E_loc, cap)
+    dh = bf(cap, 2 * I, seed=61)
+    wg, wu = bf(E_loc, I, H, seed=2, scale=0.05), bf(E_loc, I, H, seed=3, scale=0.05)
+    dxp = torch.empty(cap, H, dtype=torch.bfloat16, device="cuda")
+    recv = [torch.full((T, K, H), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(n)]
+    extension().gemm_ep_push(dh, wg.view(E_loc * I, H), dxp, [t.data_ptr() for t in recv], ix.meta, ix.src_of, ix.k_of,
+                             cap, H, 2 * I, I, E_loc, T, K, 0, OF.stage_flags(dh.device, cap), OF.status_word("cuda"),
+                             True, wu.view(E_loc * I, H), I)
+    want = OF.grouped_linear_dgrad_pair(dh, wg, wu, ix)
+    used = int(ix.meta[0].item()) * 128
+    src = ix.src_of[:used].long()
+    rows = torch.nonzero(src >= 0).flatten()
+    assert torch.equal(dxp[rows], want[rows])
+    owner, tok, k = src[rows] // T, src[rows] % T, ix.k_of[:used].long()[rows]
+    assert torch.equal(torch.stack(recv)[owner, tok, k], dxp[rows])
+    out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+    filled = torch.nan_to_num(recv[1], nan=0.0)
+    extension().sum_slots(filled, out)
+    assert (out.float() - filled.float().sum(1)).abs().max().item() <= 2e-2 * filled.float().sum(1).abs().max().item()
+
+
+def test_exact_row_count_sizes_the_expert_buffers():
+    """With ``exact`` the activation buffers follow the routed count, not the worst case, and nothing is dropped."""
+    n, T, E_loc, K = 8, 1024, 4, 2
+    E = n * E_loc
+    g = torch.Generator(device="cuda").manual_seed(9)
+    idx_all = torch.stack([torch.randperm(E, device="cuda", generator=g)[:K] for _ in range(n * T)]).to(torch.int32)
+    cap = OF.moe_capacity_rows(n * T, K, E_loc)
+    ix = OF.MoEIndex(idx_all, 0, E_loc, cap, exact=True)
+    mine = int((idx_all < E_loc).sum().item())
+    assert mine <= ix.rows < cap and ix.rows % OF.ROW_GRANULE == 0 and ix.rows >= int(ix.meta[0].item()) * 128
+    assert int((ix.row_of >= 0).sum().item()) == mine
+
+
 @pytest.mark.parametrize("T,E,K,H,I,e_start,E_loc", [(512, 8, 2, 256, 512, 0, 8), (1000, 16, 4, 128, 256, 4, 8),
                                                      (2048, 64, 8, 512, 256, 0, 64)])
 def test_moe_experts_fwd_bwd(T, E, K, H, I, e_start, E_loc):
