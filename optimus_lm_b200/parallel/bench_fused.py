@@ -87,7 +87,7 @@ def bench_ep():
     pmap = ParallelDpPpEpTpMapper(1, 1, world, 1, rank=rank, create_groups=True)
     cfg = OlmoeParallelConfig(hidden_size=H, intermediate_size=I, num_experts=E, num_experts_per_tok=K,
                               expert_parallelism=world, use_fast_moe=True, use_merged_mlp_in_fast_moe=True,
-                              output_router_logits=True, moe_capacity_factor=4.0)
+                              output_router_logits=True)
     torch.manual_seed(0)
     blk = FastOlmoeParallelSparseMoeBlock(cfg, pmap).cuda().to(torch.bfloat16)
     with torch.no_grad():

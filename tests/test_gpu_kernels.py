@@ -377,6 +377,37 @@ def test_gate_up_dgrad_launch_with_fused_combine_push():
     assert (out.float() - filled.float().sum(1)).abs().max().item() <= 2e-2 * filled.float().sum(1).abs().max().item()
 
 
+def test_index_overflow_sets_the_status_word():
+    """A capacity-limited index that is too small reports ST_OVERFLOW (6); the host reads and clears it."""
+    _, idx = _routing(1024, 8, 2)
+    OF.MoEIndex(idx, 0, 8, 1024)                 # 2048 routed pairs cannot fit 1024 rows
+    torch.cuda.synchronize()
+    assert OF.check_status("cuda") == 6
+    assert OF.check_status("cuda") == 0          # cleared by the read
+    ix = OF.MoEIndex(idx, 0, 8, OF.moe_capacity_rows(1024, 2, 8))
+    assert int(ix.counts.sum().item()) == 2048 and OF.check_status("cuda") == 0
+
+
+def test_bounded_peer_wait_times_out_without_hanging():
+    """A rendezvous whose partner never signals gives up after its limit, records ST_TIMEOUT_PEER (5) and returns:
+    the context stays usable.  The partner's signal word is a word of this GPU's memory that nothing writes."""
+    from optimus_lm_b200.ops import extension
+    pads = [torch.zeros(16 * 64, dtype=torch.int32, device="cuda") for _ in range(2)]
+    st = OF.status_word("cuda")
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    extension().symm_barrier([p.data_ptr() for p in pads], 0, 3, 1, st, 20_000_000)    # 20 ms limit
+    t1.record()
+    torch.cuda.synchronize()
+    assert 10.0 < t0.elapsed_time(t1) < 2000.0
+    assert OF.check_status("cuda") == 5
+    assert int(pads[1][3 * 16 + 0].item()) == 1      # this rank did signal its partner
+    x = torch.arange(1024, device="cuda").float()
+    assert float(x.sum().item()) == 1023 * 1024 / 2   # the GPU still answers
+    assert OF.check_status("cuda") == 0
+
+
 def test_exact_row_count_sizes_the_expert_buffers():
     """With ``exact`` the activation buffers follow the routed count, not the worst case, and nothing is dropped."""
     n, T, E_loc, K = 8, 1024, 4, 2

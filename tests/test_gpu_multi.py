@@ -1,5 +1,5 @@
-"""Multi-GPU tests (2 ranks, one process per GPU, NCCL): the fused peer-memory paths against the
-NCCL-only paths of the same computation.  Skipped when fewer than 2 GPUs are visible."""
+"""Multi-GPU tests (2, 4 and 8 ranks, one process per GPU, NCCL): the fused peer-memory paths against the
+NCCL-only paths of the same computation.  A case is skipped when fewer GPUs are visible than it needs."""
 import os
 import socket
 import traceback
@@ -62,6 +62,16 @@ def _rel(a, b):
     return ((a - b).norm() / (b.norm() + 1e-12)).item()
 
 
+def _max_err(a, b):
+    """Largest element-wise difference relative to the reference's largest element: a few wrong rows show up here
+    even when the norm-wise error stays small."""
+    a, b = a.float(), b.float()
+    return ((a - b).abs().max() / (b.abs().max() + 1e-12)).item()
+
+
+WORLDS = [2, 4, 8]
+
+
 # ----------------------------------------------------------------------------- workers
 def w_symm_barrier_and_pull(rank, world):
     import torch.distributed as dist
@@ -87,7 +97,7 @@ def w_fused_ep_vs_allgather(rank, world):
     from optimus_lm_b200.models.common.moe import FastOlmoeParallelSparseMoeBlock
     from optimus_lm_b200.ops import functional as OF
     pmap = ParallelDpPpEpTpMapper(1, 1, world, 1, rank=rank, create_groups=True)
-    cfg = OlmoeParallelConfig(hidden_size=256, intermediate_size=512, num_experts=8, num_experts_per_tok=2,
+    cfg = OlmoeParallelConfig(hidden_size=256, intermediate_size=512, num_experts=16, num_experts_per_tok=4,
                               expert_parallelism=world, use_fast_moe=True, use_merged_mlp_in_fast_moe=True,
                               output_router_logits=True, moe_capacity_factor=0.0)
     torch.manual_seed(0)
@@ -111,9 +121,44 @@ def w_fused_ep_vs_allgather(rank, world):
     yb, xb, gb = res["alltoall"]
     assert _rel(yb, ya) < 2e-2, _rel(yb, ya)
     assert _rel(xb, xa) < 2e-2, _rel(xb, xa)
+    assert _max_err(yb, ya) < 5e-2, _max_err(yb, ya)
+    assert _max_err(xb, xa) < 5e-2, _max_err(xb, xa)
     for n in ga:
         assert _rel(gb[n], ga[n]) < 3e-2, (n, _rel(gb[n], ga[n]))
+        assert _max_err(gb[n], ga[n]) < 8e-2, (n, _max_err(gb[n], ga[n]))
     assert OF.check_status("cuda") == 0
+
+
+def w_capacity_overflow_is_reported(rank, world):
+    """A fixed capacity below the routed load must raise ST_OVERFLOW (6) in the status word of the overloaded rank and
+    leave the GPU usable; with the default (capacity factor 0) the same routing runs clean."""
+    import torch.distributed as dist
+    from optimus_lm_b200.mapper import ParallelDpPpEpTpMapper
+    from optimus_lm_b200.models.olmoe.configuration_olmoe import OlmoeParallelConfig
+    from optimus_lm_b200.models.common.moe import FastOlmoeParallelSparseMoeBlock
+    from optimus_lm_b200.ops import functional as OF
+    pmap = ParallelDpPpEpTpMapper(1, 1, world, 1, rank=rank, create_groups=True)
+    seen = {}
+    for factor in (0.25, 0.0):
+        cfg = OlmoeParallelConfig(hidden_size=256, intermediate_size=512, num_experts=16, num_experts_per_tok=4,
+                                  expert_parallelism=world, use_fast_moe=True, use_merged_mlp_in_fast_moe=True,
+                                  output_router_logits=True, moe_capacity_factor=factor)
+        torch.manual_seed(0)
+        blk = FastOlmoeParallelSparseMoeBlock(cfg, pmap).cuda().to(torch.bfloat16)
+        with torch.no_grad():
+            for name, p in blk.named_parameters():
+                g = torch.Generator(device="cuda").manual_seed(hash(name) % 1000)
+                p.copy_(torch.randn(p.shape, device="cuda", generator=g) * 0.05)
+        g = torch.Generator(device="cuda").manual_seed(100 + rank)
+        x = torch.randn(4, 512, 256, device="cuda", generator=g).to(torch.bfloat16)
+        y, _ = blk(x)
+        torch.cuda.synchronize()
+        st = torch.tensor([float(OF.check_status("cuda"))], device="cuda")
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        seen[factor] = int(st.item())
+        assert torch.isfinite(y.float()).all() or factor > 0
+    assert seen[0.25] == 6, seen        # a quarter of the balanced share cannot hold the routed rows
+    assert seen[0.0] == 0, seen
 
 
 def w_fused_optimizer_vs_nccl(rank, world):
@@ -209,20 +254,28 @@ def w_family_layout(rank, world, name):
 
 
 # ----------------------------------------------------------------------------- tests
-def test_symm_barrier_and_pull_reduce():
-    _run("w_symm_barrier_and_pull", 2)
+@pytest.mark.parametrize("world", WORLDS)
+def test_symm_barrier_and_pull_reduce(world):
+    _run("w_symm_barrier_and_pull", world)
 
 
-def test_fused_ep_moe_matches_allgather_transport():
-    _run("w_fused_ep_vs_allgather", 2)
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_ep_moe_matches_allgather_transport(world):
+    _run("w_fused_ep_vs_allgather", world)
 
 
-def test_fused_engine_matches_nccl_engine():
-    _run("w_fused_optimizer_vs_nccl", 2)
+def test_capacity_overflow_is_reported_and_default_cannot_overflow():
+    _run("w_capacity_overflow_is_reported", 2)
 
 
-def test_tp_fused_mlp_matches_nccl_path():
-    _run("w_tp_fused_mlp_vs_nccl", 2)
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_engine_matches_nccl_engine(world):
+    _run("w_fused_optimizer_vs_nccl", world)
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_tp_fused_mlp_matches_nccl_path(world):
+    _run("w_tp_fused_mlp_vs_nccl", world)
 
 
 @pytest.mark.parametrize("name", list(LAYOUTS))
