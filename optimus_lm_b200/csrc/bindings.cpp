@@ -29,7 +29,7 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, int64_t M, in
           bool b_mn_major, bool accumulate, int64_t mode, const c10::optional<at::Tensor>& meta, int64_t num_experts,
           int64_t b_expert_rows, int64_t c_expert_stride, const c10::optional<at::Tensor>& status, int64_t block_n,
           int64_t max_ctas, const c10::optional<at::Tensor>& b2, int64_t k_split,
-          const c10::optional<at::Tensor>& blk_range) {
+          const c10::optional<at::Tensor>& blk_range, bool pair_rows) {
   CHECK_CUDA_BF16(a);
   CHECK_CUDA_BF16(b);
   TORCH_CHECK(c.is_cuda() && (c.scalar_type() == at::kBFloat16 || c.scalar_type() == at::kFloat), "c must be bf16/fp32");
@@ -67,6 +67,7 @@ void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, int64_t M, in
     d.k_split = static_cast<int>(k_split);
   }
   d.blk_range = opt_ptr<const int>(blk_range);
+  d.pair_rows = pair_rows;
   check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16");
 }
 
@@ -259,14 +260,15 @@ int64_t moe_ws_ints(int64_t T, int64_t E_loc) { return olb_moe_ws_ints(static_ca
 
 void moe_build_index(const at::Tensor& indices, int64_t e_start, int64_t E_loc, int64_t cap, at::Tensor& ws,
                      at::Tensor& row_of, at::Tensor& src_of, at::Tensor& k_of, at::Tensor& meta, at::Tensor& offsets,
-                     at::Tensor& counts, const c10::optional<at::Tensor>& status) {
+                     at::Tensor& counts, const c10::optional<at::Tensor>& status, int64_t row_pad) {
   CHECK_CUDA_I32(indices);
   c10::cuda::CUDAGuard guard(indices.device());
   TORCH_CHECK(ws.numel() >= olb_moe_ws_ints(indices.size(0), E_loc), "workspace too small");
   TORCH_CHECK(meta.numel() >= 1 + cap / 128 && src_of.numel() >= cap && k_of.numel() >= cap, "index buffers too small");
   check(olb_moe_build_index(indices.data_ptr<int>(), static_cast<int>(indices.size(0)),
                             static_cast<int>(indices.size(1)), static_cast<int>(e_start), static_cast<int>(E_loc),
-                            static_cast<int>(cap), ws.data_ptr<int>(), row_of.data_ptr<int>(), src_of.data_ptr<int>(),
+                            static_cast<int>(cap), static_cast<int>(row_pad), ws.data_ptr<int>(), row_of.data_ptr<int>(),
+                            src_of.data_ptr<int>(),
                             k_of.data_ptr<int>(), meta.data_ptr<int>(), offsets.data_ptr<int>(), counts.data_ptr<int>(),
                             opt_ptr<int>(status), cur_stream()),
         "olb_moe_build_index");
@@ -412,7 +414,11 @@ void register_attention(pybind11::module& m);
 void register_comm(pybind11::module& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("gemm", &gemm);
+  m.def("gemm", &gemm, pybind11::arg("a"), pybind11::arg("b"), pybind11::arg("c"), pybind11::arg("M"), pybind11::arg("N"),
+        pybind11::arg("K"), pybind11::arg("a_mn_major"), pybind11::arg("b_mn_major"), pybind11::arg("accumulate"),
+        pybind11::arg("mode"), pybind11::arg("meta"), pybind11::arg("num_experts"), pybind11::arg("b_expert_rows"),
+        pybind11::arg("c_expert_stride"), pybind11::arg("status"), pybind11::arg("block_n"), pybind11::arg("max_ctas"),
+        pybind11::arg("b2"), pybind11::arg("k_split"), pybind11::arg("blk_range"), pybind11::arg("pair_rows") = false);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
@@ -432,7 +438,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("router_sigmoid_group_topk", &router_sigmoid_group_topk);
   m.def("router_sigmoid_bwd", &router_sigmoid_bwd);
   m.def("moe_ws_ints", &moe_ws_ints);
-  m.def("moe_build_index", &moe_build_index);
+  m.def("moe_build_index", &moe_build_index, pybind11::arg("indices"), pybind11::arg("e_start"), pybind11::arg("E_loc"),
+        pybind11::arg("cap"), pybind11::arg("ws"), pybind11::arg("row_of"), pybind11::arg("src_of"), pybind11::arg("k_of"),
+        pybind11::arg("meta"), pybind11::arg("offsets"), pybind11::arg("counts"), pybind11::arg("status"),
+        pybind11::arg("row_pad") = 128);
   m.def("moe_gather_rows", &moe_gather_rows);
   m.def("moe_combine", &moe_combine);
   m.def("moe_combine_bwd", &moe_combine_bwd);

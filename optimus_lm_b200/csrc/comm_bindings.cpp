@@ -206,7 +206,7 @@ void gemm_ep_push(const at::Tensor& a, const at::Tensor& w2d, at::Tensor& c, con
                   const at::Tensor& meta, const at::Tensor& src_of, const at::Tensor& k_of, int64_t M, int64_t N, int64_t K,
                   int64_t b_expert_rows, int64_t num_experts, int64_t tokens, int64_t topk, int64_t my_peer,
                   at::Tensor& flags, const c10::optional<at::Tensor>& status, bool b_mn_major,
-                  const c10::optional<at::Tensor>& w2d_2, int64_t k_split) {
+                  const c10::optional<at::Tensor>& w2d_2, int64_t k_split, bool pair_rows) {
   TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && w2d.scalar_type() == at::kBFloat16 &&
                   c.scalar_type() == at::kBFloat16,
               "bf16 CUDA operands expected");
@@ -251,6 +251,7 @@ void gemm_ep_push(const at::Tensor& a, const at::Tensor& w2d, at::Tensor& c, con
   d.ep_k_of = k_of.data_ptr<int>();
   d.ep_tokens = static_cast<int>(tokens);
   d.ep_topk = static_cast<int>(topk);
+  d.pair_rows = pair_rows;
   check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (expert-parallel combine variant)");
 }
 
@@ -265,7 +266,8 @@ void gemm_gateup_swiglu(at::Tensor& xp, const at::Tensor& wg2d, const at::Tensor
                         const c10::optional<at::Tensor>& src_of, const c10::optional<at::Tensor>& k_of,
                         const c10::optional<at::Tensor>& weights, int64_t num_experts,
                         const std::vector<int64_t>& x_peers, int64_t x_ld, int64_t tokens,
-                        const c10::optional<at::Tensor>& flags, const c10::optional<at::Tensor>& status) {
+                        const c10::optional<at::Tensor>& flags, const c10::optional<at::Tensor>& status,
+                        bool pair_rows) {
   TORCH_CHECK(xp.is_cuda() && xp.scalar_type() == at::kBFloat16 && wg2d.scalar_type() == at::kBFloat16 &&
                   wu2d.scalar_type() == at::kBFloat16 && h.scalar_type() == at::kBFloat16 &&
                   act.scalar_type() == at::kBFloat16,
@@ -323,6 +325,7 @@ void gemm_gateup_swiglu(at::Tensor& xp, const at::Tensor& wg2d, const at::Tensor
     d.ep_src_of = src_of->data_ptr<int>();
     d.ep_tokens = static_cast<int>(tokens);
   }
+  d.pair_rows = pair_rows;
   check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (gate|up + SwiGLU)");
 }
 
@@ -331,7 +334,7 @@ void gemm_gateup_swiglu(at::Tensor& xp, const at::Tensor& wg2d, const at::Tensor
 void gemm_ep_gather(at::Tensor& xp, const at::Tensor& w2d, at::Tensor& c, int64_t M, int64_t N, int64_t K, bool b_mn_major,
                     const at::Tensor& meta, const at::Tensor& src_of, int64_t b_expert_rows, int64_t num_experts,
                     const std::vector<int64_t>& x_peers, int64_t x_ld, int64_t tokens, at::Tensor& flags,
-                    const c10::optional<at::Tensor>& status) {
+                    const c10::optional<at::Tensor>& status, bool pair_rows) {
   TORCH_CHECK(xp.is_cuda() && xp.scalar_type() == at::kBFloat16 && w2d.scalar_type() == at::kBFloat16 &&
                   c.scalar_type() == at::kBFloat16,
               "bf16 CUDA operands expected");
@@ -367,6 +370,7 @@ void gemm_ep_gather(at::Tensor& xp, const at::Tensor& w2d, at::Tensor& c, int64_
   d.stage_flags = flags.data_ptr<int>();
   d.ep_src_of = src_of.data_ptr<int>();
   d.ep_tokens = static_cast<int>(tokens);
+  d.pair_rows = pair_rows;
   check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (expert-parallel dispatch variant)");
 }
 
@@ -415,9 +419,16 @@ void register_comm(pybind11::module& m) {
   m.def("gemm_ep_push", &gemm_ep_push, py::arg("a"), py::arg("w2d"), py::arg("c"), py::arg("c_peers"), py::arg("meta"),
         py::arg("src_of"), py::arg("k_of"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("b_expert_rows"),
         py::arg("num_experts"), py::arg("tokens"), py::arg("topk"), py::arg("my_peer"), py::arg("flags"),
-        py::arg("status"), py::arg("b_mn_major") = false, py::arg("w2d_2") = py::none(), py::arg("k_split") = 0);
-  m.def("gemm_gateup_swiglu", &gemm_gateup_swiglu);
-  m.def("gemm_ep_gather", &gemm_ep_gather);
+        py::arg("status"), py::arg("b_mn_major") = false, py::arg("w2d_2") = py::none(), py::arg("k_split") = 0,
+        py::arg("pair_rows") = false);
+  m.def("gemm_gateup_swiglu", &gemm_gateup_swiglu, py::arg("xp"), py::arg("wg2d"), py::arg("wu2d"), py::arg("h"),
+        py::arg("act"), py::arg("M"), py::arg("I"), py::arg("K"), py::arg("meta"), py::arg("src_of"), py::arg("k_of"),
+        py::arg("weights"), py::arg("num_experts"), py::arg("x_peers"), py::arg("x_ld"), py::arg("tokens"),
+        py::arg("flags"), py::arg("status"), py::arg("pair_rows") = false);
+  m.def("gemm_ep_gather", &gemm_ep_gather, py::arg("xp"), py::arg("w2d"), py::arg("c"), py::arg("M"), py::arg("N"),
+        py::arg("K"), py::arg("b_mn_major"), py::arg("meta"), py::arg("src_of"), py::arg("b_expert_rows"),
+        py::arg("num_experts"), py::arg("x_peers"), py::arg("x_ld"), py::arg("tokens"), py::arg("flags"),
+        py::arg("status"), py::arg("pair_rows") = false);
   m.def("rs_adamw_blocks", &rs_adamw_blocks);
   m.def("rs_adamw", &rs_adamw);
 }

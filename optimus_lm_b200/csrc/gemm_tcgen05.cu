@@ -66,6 +66,7 @@ struct GemmParams {
   int m_rotate_blocks;         // row-block rotation of the tile order (start on the rows this GPU owns)
   const int* blk_range;        // ragged-M only, optional (device): restrict to row blocks [blk_range[0], blk_range[1])
   int* status;
+  int pair_rows;               // ragged-M: expert groups are padded to 256 rows (a CTA pair's tile never spans two)
   int c_tma;                   // epilogue writes C through tensor-map stores (tma_c); 0 = plain stores
   // EPI_SWIGLU: N is the width of act (= I); the tile's B rows come from tma_b (gate) and tma_b2 (up), tma_c covers
   // h [rows, 2 * N] (gate | up) and tma_c2 act [rows, N].  Row weights: weights[src_of[row] * topk + k_of[row]],
@@ -234,6 +235,275 @@ __device__ __forceinline__ void epi_store_chunk(EpiStage& es, const CUtensorMap*
   if (lane == 0) {
     tma_store_2d(map, buf, x, y);
     tma_store_commit();
+  }
+}
+
+// Epilogue of one 128-row accumulator tile without a fused activation: through staged tensor-map stores when the
+// output allows it, else with plain loads / stores (accumulating epilogues, layouts a tensor map cannot describe).
+// `taddr` is the accumulator's TMEM address for this warp's 32 lanes; `ti.m0` the first of the CTA's 128 rows.
+template <int BLOCK_N>
+__device__ __forceinline__ void epilogue_plain(const GemmParams& p, const CUtensorMap* tma_c, EpiStage& es, uint32_t taddr,
+                                               const TileInfo& ti, bool has_k, int lane_group, int lane) {
+  const int row = ti.m0 + lane_group * 32 + lane;
+  const bool row_ok = row < p.M;
+  if (p.c_tma) {
+    // ---- staged tensor-map stores: 128 bytes of every row per turn (64 bf16 or 32 fp32 columns)
+    long long y = ti.m0 + lane_group * 32;
+    const bool rows_ok = y < p.M;
+    if (p.mode == OLB_GEMM_RAGGED_K) y += static_cast<long long>(ti.expert) * p.M;
+    if (p.out_fp32) {
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        uint32_t r[32];
+        if (has_k) {
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        const int x = ti.n0 + c * 32;
+        if (rows_ok && x < p.N) epi_store_chunk(es, tma_c, r, lane, x, static_cast<int>(y));
+      }
+    } else {
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 64; ++c) {
+        uint32_t v[32];
+        if (has_k) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32b_x32(taddr + c * 64, r0);
+          tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            v[i] = pack_bf16(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+            v[16 + i] = pack_bf16(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        const int x = ti.n0 + c * 64;
+        if (rows_ok && x < p.N) epi_store_chunk(es, tma_c, v, lane, x, static_cast<int>(y));
+      }
+    }
+  } else {
+    // ---- plain loads / stores (accumulating epilogues, layouts a tensor map cannot describe)
+    char* c_row;
+    {
+      long long off = static_cast<long long>(row) * p.ldc + ti.n0;
+      if (p.mode == OLB_GEMM_RAGGED_K) off += static_cast<long long>(ti.expert) * p.c_expert_stride;
+      c_row = static_cast<char*>(p.C) + off * (p.out_fp32 ? 4 : 2);
+    }
+#pragma unroll 1
+    for (int c = 0; c < BLOCK_N / 32; ++c) {
+      uint32_t r[32];
+      if (has_k) {
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = 0u;
+      }
+      if (row_ok) {
+        const int col0 = ti.n0 + c * 32;
+        if (p.out_fp32) {
+          float4* dst = reinterpret_cast<float4*>(c_row + c * 32 * 4);
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            if (col0 + g * 4 < p.N) {
+              float4 v = make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
+                                     __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
+              if (p.accumulate) {
+                float4 o = dst[g];
+                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+              }
+              dst[g] = v;
+            }
+          }
+        } else {
+          uint4* dst = reinterpret_cast<uint4*>(c_row + c * 32 * 2);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (col0 + g * 8 < p.N) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[8 * g + i]);
+              if (p.accumulate) {
+                uint4 o = dst[g];
+                float2 a;
+                a = unpack_bf16(o.x); f[0] += a.x; f[1] += a.y;
+                a = unpack_bf16(o.y); f[2] += a.x; f[3] += a.y;
+                a = unpack_bf16(o.z); f[4] += a.x; f[5] += a.y;
+                a = unpack_bf16(o.w); f[6] += a.x; f[7] += a.y;
+              }
+              uint4 v;
+              v.x = pack_bf16(f[0], f[1]);
+              v.y = pack_bf16(f[2], f[3]);
+              v.z = pack_bf16(f[4], f[5]);
+              v.w = pack_bf16(f[6], f[7]);
+              dst[g] = v;
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
+// Epilogue of one 128-row tile of the fused gate|up projection: accumulator columns [0,128) are gate, [128,256) up,
+// both for act columns [ti.n0, ti.n0 + 128).  Writes gate | up (bf16) to tma_c and w(row) * silu(gate) * up to tma_c2.
+__device__ __forceinline__ void epilogue_swiglu(const GemmParams& p, const CUtensorMap* tma_c, const CUtensorMap* tma_c2,
+                                                EpiStage& es, uint32_t taddr, const TileInfo& ti, int lane_group, int lane) {
+  const int row = ti.m0 + lane_group * 32 + lane;
+  const bool row_ok = row < p.M;
+  // columns [0,128) of the accumulator are gate, [128,256) up, both for act columns [n0, n0 + 128)
+  float w = 1.f;
+  if (p.row_src_of) {
+    const int src = row_ok ? p.row_src_of[row] : -1;
+    w = src >= 0 ? p.row_weights[static_cast<long long>(src) * p.row_topk + p.row_k_of[row]] : 0.f;
+  }
+  const int y = ti.m0 + lane_group * 32;
+#pragma unroll 1
+  for (int c = 0; c < 2; ++c) {  // 64 act columns per turn
+    uint32_t hg[32], hu[32];
+    {
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32b_x32(taddr + c * 64, r0);
+      tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        hg[i] = pack_bf16(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+        hg[16 + i] = pack_bf16(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+      }
+    }
+    const int x = ti.n0 + c * 64;
+    if (y < p.M && x < p.N) epi_store_chunk(es, tma_c, hg, lane, x, y);
+    {
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32b_x32(taddr + 128 + c * 64, r0);
+      tmem_ld_32x32b_x32(taddr + 128 + c * 64 + 32, r1);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        hu[i] = pack_bf16(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+        hu[16 + i] = pack_bf16(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+      }
+    }
+    if (y < p.M && x < p.N) epi_store_chunk(es, tma_c, hu, lane, p.N + x, y);
+    // the activation from the rounded values, as the backward recomputes it from the saved gate | up
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float2 g = unpack_bf16(hg[i]), u = unpack_bf16(hu[i]);
+      hg[i] = pack_bf16(w * (g.x / (1.f + __expf(-g.x))) * u.x, w * (g.y / (1.f + __expf(-g.y))) * u.y);
+    }
+    if (y < p.M && x < p.N) epi_store_chunk(es, tma_c2, hg, lane, x, y);
+  }
+}
+
+// The extra warps of the variants with a fused transfer (PeerArg<true>): `swarp` is the warp's index among the CTA's
+// STAGER_WARPS stagers, `num_m_blocks` the number of 128-row blocks of the launch.
+__device__ __forceinline__ void stager_loop(const PeerArg<true>& peers, const GemmParams& p, int num_m_blocks, int swarp,
+                                            int lane, volatile int* abort_flag) {
+  // ---------------------------------------------------------- stagers (warps 6..9)
+  // Remote rows in the order the tiles need them.  Every CTA's stagers take rows of the same block at the same
+  // time, so blocks complete one after the other.  The gathers wait for nothing; the pushes wait (bounded) for
+  // this GPU's own epilogues.
+  const long long total = (peers.push == 2 || peers.push == 3)
+                              ? min(static_cast<long long>(num_m_blocks) * BLOCK_M, static_cast<long long>(p.M))
+                              : static_cast<long long>(peers.n - 1) * peers.rows;
+  int ready_blk = -1;
+  bool ok = true;
+  for (long long u = blockIdx.x * STAGER_WARPS + swarp; ok && u < total;
+       u += static_cast<long long>(gridDim.x) * STAGER_WARPS) {
+    if (peers.push == 3) {
+      // -------- expert-parallel dispatch: the routed token row comes from its owner into the grouped operand
+      const int g = peers.src_of[u];
+      uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.dst) + u * peers.ld * 2);
+      if (g >= 0) {
+        const int owner = g / peers.T;
+        const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.src[owner]) +
+                                                        static_cast<long long>(g - owner * peers.T) * peers.src_ld * 2);
+        for (int c0 = 0; c0 < peers.row_vecs; c0 += 256) {
+          uint4 v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int c = c0 + i * 32 + lane;
+            if (c < peers.row_vecs) v[i] = s[c];
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int c = c0 + i * 32 + lane;
+            if (c < peers.row_vecs) d[c] = v[i];
+          }
+        }
+      } else {
+        for (int c = lane; c < peers.row_vecs; c += 32) d[c] = make_uint4(0, 0, 0, 0);
+      }
+      fence_proxy_async_all();
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) atomicAdd(peers.flags + u / BLOCK_M, 1);
+      continue;
+    }
+    if (peers.push == 2) {
+      // -------- expert-parallel combine transport: a finished row goes to the owner of its token
+      const int blk = static_cast<int>(u / BLOCK_M);
+      if (blk != ready_blk) {
+        if (!wait_count(peers.flags + blk, peers.flags_full, p.status, abort_flag)) {
+          ok = false;
+          break;
+        }
+        ready_blk = blk;
+      }
+      const int g = peers.src_of[u];
+      if (g < 0) continue;
+      const int owner = g / peers.T;
+      const long long slot = static_cast<long long>(g - owner * peers.T) * peers.topk + peers.k_of[u];
+      const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.c_base) + u * peers.ldc * 2);
+      uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.push_dst[owner]) + slot * peers.ld * 2);
+      copy_row_ldcg(s, d, peers.row_vecs, lane);
+      continue;
+    }
+    const int j = static_cast<int>(u / peers.rows);
+    const int r = static_cast<int>(u - static_cast<long long>(j) * peers.rows);
+    const int peer = (peers.me + 1 + j) % peers.n;
+    const long long drow = static_cast<long long>(peer) * peers.rows + r;
+    if (peers.push) {
+      // -------- reduce-scatter transport: row `drow` of C goes to its owner once every tile of its block is stored
+      const int blk = static_cast<int>(drow / BLOCK_M);
+      if (blk != ready_blk) {
+        if (!wait_count(peers.flags + blk, peers.flags_full, p.status, abort_flag)) {
+          ok = false;
+          break;
+        }
+        ready_blk = blk;
+      }
+      const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.c_base) + drow * peers.ldc * 2);
+      uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.push_dst[peer]) + r * peers.ldc * 2);
+      copy_row_ldcg(s, d, peers.row_vecs, lane);
+      continue;
+    }
+    const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.src[peer]) + r * peers.ld * 2);
+    uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.dst) + drow * peers.ld * 2);
+    for (int c0 = 0; c0 < peers.row_vecs; c0 += 256) {
+      uint4 v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int c = c0 + i * 32 + lane;
+        if (c < peers.row_vecs) v[i] = s[c];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int c = c0 + i * 32 + lane;
+        if (c < peers.row_vecs) d[c] = v[i];
+      }
+    }
+    fence_proxy_async_all();
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) atomicAdd(peers.flags + drow / BLOCK_M, 1);
   }
 }
 
@@ -430,8 +700,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     TileInfo ti;
     EpiStage es{smem_base + L::EPI_OFFSET + lane_group * 2 * EPI_BUF_BYTES, 0};
     for (int t = blockIdx.x; get_tile<BLOCK_N, EPI>(p, t, num_m_blocks, blk0, ti); t += gridDim.x) {
-      const int row = ti.m0 + lane_group * 32 + lane;
-      const bool row_ok = row < p.M;
       const bool has_k = ti.kb_end > ti.kb_begin;
       if (has_k) {
         if (!mbar_wait(acc_full_bar(acc), acc_phase, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) break;
@@ -441,151 +709,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + acc * BLOCK_N;
       if constexpr (EPI == EPI_SWIGLU) {
-        // columns [0,128) of the accumulator are gate, [128,256) up, both for act columns [n0, n0 + 128)
-        float w = 1.f;
-        if (p.row_src_of) {
-          const int src = row_ok ? p.row_src_of[row] : -1;
-          w = src >= 0 ? p.row_weights[static_cast<long long>(src) * p.row_topk + p.row_k_of[row]] : 0.f;
-        }
-        const int y = ti.m0 + lane_group * 32;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {  // 64 act columns per turn
-          uint32_t hg[32], hu[32];
-          {
-            uint32_t r0[32], r1[32];
-            tmem_ld_32x32b_x32(taddr + c * 64, r0);
-            tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              hg[i] = pack_bf16(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
-              hg[16 + i] = pack_bf16(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
-            }
-          }
-          const int x = ti.n0 + c * 64;
-          if (y < p.M && x < p.N) epi_store_chunk(es, &tma_c, hg, lane, x, y);
-          {
-            uint32_t r0[32], r1[32];
-            tmem_ld_32x32b_x32(taddr + 128 + c * 64, r0);
-            tmem_ld_32x32b_x32(taddr + 128 + c * 64 + 32, r1);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              hu[i] = pack_bf16(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
-              hu[16 + i] = pack_bf16(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
-            }
-          }
-          if (y < p.M && x < p.N) epi_store_chunk(es, &tma_c, hu, lane, p.N + x, y);
-          // the activation from the rounded values, as the backward recomputes it from the saved gate | up
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float2 g = unpack_bf16(hg[i]), u = unpack_bf16(hu[i]);
-            hg[i] = pack_bf16(w * (g.x / (1.f + __expf(-g.x))) * u.x, w * (g.y / (1.f + __expf(-g.y))) * u.y);
-          }
-          if (y < p.M && x < p.N) epi_store_chunk(es, &tma_c2, hg, lane, x, y);
-        }
-      } else if (p.c_tma) {
-        // ---- staged tensor-map stores: 128 bytes of every row per turn (64 bf16 or 32 fp32 columns)
-        long long y = ti.m0 + lane_group * 32;
-        const bool rows_ok = y < p.M;
-        if (p.mode == OLB_GEMM_RAGGED_K) y += static_cast<long long>(ti.expert) * p.M;
-        if (p.out_fp32) {
-#pragma unroll 1
-          for (int c = 0; c < BLOCK_N / 32; ++c) {
-            uint32_t r[32];
-            if (has_k) {
-              tmem_ld_32x32b_x32(taddr + c * 32, r);
-              tmem_ld_wait();
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) r[i] = 0u;
-            }
-            const int x = ti.n0 + c * 32;
-            if (rows_ok && x < p.N) epi_store_chunk(es, &tma_c, r, lane, x, static_cast<int>(y));
-          }
-        } else {
-#pragma unroll 1
-          for (int c = 0; c < BLOCK_N / 64; ++c) {
-            uint32_t v[32];
-            if (has_k) {
-              uint32_t r0[32], r1[32];
-              tmem_ld_32x32b_x32(taddr + c * 64, r0);
-              tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
-              tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                v[i] = pack_bf16(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
-                v[16 + i] = pack_bf16(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = 0u;
-            }
-            const int x = ti.n0 + c * 64;
-            if (rows_ok && x < p.N) epi_store_chunk(es, &tma_c, v, lane, x, static_cast<int>(y));
-          }
-        }
+        epilogue_swiglu(p, &tma_c, &tma_c2, es, taddr, ti, lane_group, lane);
       } else {
-        // ---- plain loads / stores (accumulating epilogues, layouts a tensor map cannot describe)
-        char* c_row;
-        {
-          long long off = static_cast<long long>(row) * p.ldc + ti.n0;
-          if (p.mode == OLB_GEMM_RAGGED_K) off += static_cast<long long>(ti.expert) * p.c_expert_stride;
-          c_row = static_cast<char*>(p.C) + off * (p.out_fp32 ? 4 : 2);
-        }
-#pragma unroll 1
-        for (int c = 0; c < BLOCK_N / 32; ++c) {
-          uint32_t r[32];
-          if (has_k) {
-            tmem_ld_32x32b_x32(taddr + c * 32, r);
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = 0u;
-          }
-          if (row_ok) {
-            const int col0 = ti.n0 + c * 32;
-            if (p.out_fp32) {
-              float4* dst = reinterpret_cast<float4*>(c_row + c * 32 * 4);
-#pragma unroll
-              for (int g = 0; g < 8; ++g) {
-                if (col0 + g * 4 < p.N) {
-                  float4 v = make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
-                                         __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
-                  if (p.accumulate) {
-                    float4 o = dst[g];
-                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                  }
-                  dst[g] = v;
-                }
-              }
-            } else {
-              uint4* dst = reinterpret_cast<uint4*>(c_row + c * 32 * 2);
-#pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                if (col0 + g * 8 < p.N) {
-                  float f[8];
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[8 * g + i]);
-                  if (p.accumulate) {
-                    uint4 o = dst[g];
-                    float2 a;
-                    a = unpack_bf16(o.x); f[0] += a.x; f[1] += a.y;
-                    a = unpack_bf16(o.y); f[2] += a.x; f[3] += a.y;
-                    a = unpack_bf16(o.z); f[4] += a.x; f[5] += a.y;
-                    a = unpack_bf16(o.w); f[6] += a.x; f[7] += a.y;
-                  }
-                  uint4 v;
-                  v.x = pack_bf16(f[0], f[1]);
-                  v.y = pack_bf16(f[2], f[3]);
-                  v.z = pack_bf16(f[4], f[5]);
-                  v.w = pack_bf16(f[6], f[7]);
-                  dst[g] = v;
-                }
-              }
-            }
-          }
-        }
+        epilogue_plain<BLOCK_N>(p, &tma_c, es, taddr, ti, has_k, lane_group, lane);
       }
       if constexpr (PEER) {
         if (peers.push == 1 || peers.push == 2) {  // this warp's 32 rows of the tile are stored: let the stagers know
@@ -613,110 +739,297 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   if constexpr (PEER) {
     if (warp >= 6) {
-      // ---------------------------------------------------------- stagers (warps 6..9)
-      // Remote rows in the order the tiles need them.  Every CTA's stagers take rows of the same block at the same
-      // time, so blocks complete one after the other.  The gathers wait for nothing; the pushes wait (bounded) for
-      // this GPU's own epilogues.
-      const long long total = (peers.push == 2 || peers.push == 3)
-                                  ? min(static_cast<long long>(num_m_blocks) * BLOCK_M, static_cast<long long>(p.M))
-                                  : static_cast<long long>(peers.n - 1) * peers.rows;
-      int ready_blk = -1;
-      bool ok = true;
-      for (long long u = blockIdx.x * STAGER_WARPS + (warp - 6); ok && u < total;
-           u += static_cast<long long>(gridDim.x) * STAGER_WARPS) {
-        if (peers.push == 3) {
-          // -------- expert-parallel dispatch: the routed token row comes from its owner into the grouped operand
-          const int g = peers.src_of[u];
-          uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.dst) + u * peers.ld * 2);
-          if (g >= 0) {
-            const int owner = g / peers.T;
-            const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.src[owner]) +
-                                                            static_cast<long long>(g - owner * peers.T) * peers.src_ld * 2);
-            for (int c0 = 0; c0 < peers.row_vecs; c0 += 256) {
-              uint4 v[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const int c = c0 + i * 32 + lane;
-                if (c < peers.row_vecs) v[i] = s[c];
-              }
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const int c = c0 + i * 32 + lane;
-                if (c < peers.row_vecs) d[c] = v[i];
-              }
-            }
-          } else {
-            for (int c = lane; c < peers.row_vecs; c += 32) d[c] = make_uint4(0, 0, 0, 0);
-          }
-          fence_proxy_async_all();
-          __threadfence();
-          __syncwarp();
-          if (lane == 0) atomicAdd(peers.flags + u / BLOCK_M, 1);
-          continue;
-        }
-        if (peers.push == 2) {
-          // -------- expert-parallel combine transport: a finished row goes to the owner of its token
-          const int blk = static_cast<int>(u / BLOCK_M);
-          if (blk != ready_blk) {
-            if (!wait_count(peers.flags + blk, peers.flags_full, p.status, abort_flag)) {
-              ok = false;
-              break;
-            }
-            ready_blk = blk;
-          }
-          const int g = peers.src_of[u];
-          if (g < 0) continue;
-          const int owner = g / peers.T;
-          const long long slot = static_cast<long long>(g - owner * peers.T) * peers.topk + peers.k_of[u];
-          const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.c_base) + u * peers.ldc * 2);
-          uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.push_dst[owner]) + slot * peers.ld * 2);
-          copy_row_ldcg(s, d, peers.row_vecs, lane);
-          continue;
-        }
-        const int j = static_cast<int>(u / peers.rows);
-        const int r = static_cast<int>(u - static_cast<long long>(j) * peers.rows);
-        const int peer = (peers.me + 1 + j) % peers.n;
-        const long long drow = static_cast<long long>(peer) * peers.rows + r;
-        if (peers.push) {
-          // -------- reduce-scatter transport: row `drow` of C goes to its owner once every tile of its block is stored
-          const int blk = static_cast<int>(drow / BLOCK_M);
-          if (blk != ready_blk) {
-            if (!wait_count(peers.flags + blk, peers.flags_full, p.status, abort_flag)) {
-              ok = false;
-              break;
-            }
-            ready_blk = blk;
-          }
-          const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.c_base) + drow * peers.ldc * 2);
-          uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.push_dst[peer]) + r * peers.ldc * 2);
-          copy_row_ldcg(s, d, peers.row_vecs, lane);
-          continue;
-        }
-        const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.src[peer]) + r * peers.ld * 2);
-        uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.dst) + drow * peers.ld * 2);
-        for (int c0 = 0; c0 < peers.row_vecs; c0 += 256) {
-          uint4 v[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int c = c0 + i * 32 + lane;
-            if (c < peers.row_vecs) v[i] = s[c];
-          }
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int c = c0 + i * 32 + lane;
-            if (c < peers.row_vecs) d[c] = v[i];
-          }
-        }
-        fence_proxy_async_all();
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) atomicAdd(peers.flags + drow / BLOCK_M, 1);
-      }
+      stager_loop(peers, p, num_m_blocks, warp - 6, lane, abort_flag);
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2): one 256 x 256 output tile per cluster of two CTAs.  CTA r of the pair stages rows
+// [m0 + 128 r, +128) of A and rows [n0 + 128 r, +128) of B; the MMAs (UMMA 256 x 256 x 16), issued by one thread of
+// CTA 0, read both CTAs' shared memory and write rows [128 r, +128) x 256 columns of D into CTA r's TMEM.  Per flop
+// each SM reads half as many B bytes from shared memory as the single-CTA kernel, which is what that kernel runs out
+// of at 128 x 256.  Barriers: the "full" barrier of a stage lives in CTA 0 and counts the bytes of both CTAs' loads;
+// "empty" and "accumulator full" exist in both CTAs and are signalled by the MMA thread's commits to both; "accumulator
+// empty" lives in CTA 0 and collects the eight epilogue warps of the pair.
+struct SmemLayoutPair {
+  static constexpr int B_STAGE_BYTES = 128 * BLOCK_K * 2;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = 6;
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EPI_STAGING_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
+};
+
+template <int EPI>
+__device__ __forceinline__ bool get_tile_pair(const GemmParams& p, int t, int num_m, TileInfo& ti) {
+  // 256-row tiles (two 128-row blocks, one per CTA); same walk as the single-CTA kernel (N fastest inside bands)
+  constexpr int TILE_N = EPI == EPI_SWIGLU ? 128 : 256;
+  const int num_n = (p.N + TILE_N - 1) / TILE_N;
+  if (p.mode == OLB_GEMM_RAGGED_K) {
+    const int per_expert = num_m * num_n;
+    if (t >= per_expert * p.num_experts) return false;
+    const int e = t / per_expert;
+    const int r = t - e * per_expert;
+    ti.expert = e;
+    ti.m0 = (r / num_n) * 256;
+    ti.n0 = (r % num_n) * TILE_N;
+    ti.kb_begin = p.meta[e] / BLOCK_K;
+    ti.kb_end = p.meta[e + 1] / BLOCK_K;
+    return true;
+  }
+  if (t >= num_m * num_n) return false;
+  constexpr int BAND = 8;
+  const int band_tiles = BAND * num_n;
+  const int band = t / band_tiles;
+  const int first_m = band * BAND;
+  const int rows_in_band = min(BAND, num_m - first_m);
+  const int r = t - band * band_tiles;
+  const int m_pair = first_m + r % rows_in_band;
+  ti.m0 = m_pair * 256;
+  ti.n0 = (r / rows_in_band) * TILE_N;
+  ti.kb_begin = 0;
+  ti.kb_end = (p.K + BLOCK_K - 1) / BLOCK_K;
+  // expert groups are padded to 256 rows (p.pair_rows), so both blocks of a pair belong to one expert
+  ti.expert = (p.mode == OLB_GEMM_RAGGED_M) ? p.meta[1 + 2 * m_pair] : 0;
+  return true;
+}
+
+template <bool PEER, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PEER ? NUM_THREADS_STAGED : NUM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                      const __grid_constant__ CUtensorMap tma_b2, const __grid_constant__ CUtensorMap tma_c,
+                      const __grid_constant__ CUtensorMap tma_c2, const __grid_constant__ PeerArg<PEER> peers,
+                      const GemmParams p) {
+  using L = SmemLayoutPair;
+  constexpr int STAGES = L::STAGES;
+  constexpr int BLOCK_N = 256;
+  constexpr uint32_t TMEM_COLS = 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + L::BAR_OFFSET;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFFSET + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFFSET + 8 * (2 * STAGES + 4) + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();      // 0 = the CTA that issues the MMAs
+  const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);     // CTA 0's: its producer's arrive.expect_tx for the bytes of both CTAs
+      mbar_init(empty_bar(s), 1);    // one commit of the MMA thread
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 8);  // CTA 0's: four epilogue warps of each CTA
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+    if (p.c_tma) tma_prefetch_desc(&tma_c);
+  }
+  if (warp == 2) {
+    // every CTA allocates all 512 columns of its own TMEM (one CTA per SM): both get the same base
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  // the peer's barriers must be initialised before anything of this CTA can reach them
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  int num_m_blocks;   // 128-row blocks of the launch (the stagers' unit); tiles take two of them
+  if (p.mode == OLB_GEMM_RAGGED_M)
+    num_m_blocks = min(p.meta[0], (p.M + BLOCK_M - 1) / BLOCK_M);
+  else
+    num_m_blocks = (p.M + BLOCK_M - 1) / BLOCK_M;
+  const int num_m = (num_m_blocks + 1) / 2;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs, each for its own halves)
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      TileInfo ti;
+      for (int t = pair_id; ok && get_tile_pair<EPI>(p, t, num_m, ti); t += num_pairs) {
+        const int m0 = ti.m0 + static_cast<int>(rank) * 128;
+        if constexpr (PEER) {
+          if (peers.push == 3) {
+            // the stagers bring this CTA's 128 rows into the local operand (the other CTA waits for its own)
+            if (!wait_count(peers.flags + m0 / BLOCK_M, BLOCK_M, p.status, abort_flag)) {
+              ok = false;
+              break;
+            }
+            fence_proxy_async_all();
+          }
+        }
+        for (int kb = ti.kb_begin; kb < ti.kb_end; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * L::STAGE_BYTES);
+          const uint32_t fb = mapa_shared(full_bar(stage), 0);
+          const int k0 = kb * BLOCK_K;
+          if (!p.a_mn_major) {
+            tma_load_2d_pair(sa, &tma_a, fb, k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) tma_load_2d_pair(sa + j * MN_BOX_BYTES, &tma_a, fb, m0 + j * 64, k0);
+          }
+          if constexpr (EPI == EPI_SWIGLU) {
+            // CTA 0 stages 128 rows of the gate weight, CTA 1 the same rows of the up weight:
+            // accumulator columns 0-127 | 128-255 in both CTAs
+            tma_load_2d_pair(sb, rank == 0 ? &tma_b : &tma_b2, fb, k0, ti.expert * p.b_expert_rows + ti.n0);
+          } else {
+            const int n0 = ti.n0 + static_cast<int>(rank) * 128;
+            const bool second = p.kb_split > 0 && kb >= p.kb_split;
+            const CUtensorMap* tmb = second ? &tma_b2 : &tma_b;
+            const int kB = second ? k0 - p.kb_split * BLOCK_K : k0;
+            if (!p.b_mn_major) {
+              tma_load_2d_pair(sb, tmb, fb, kB, ti.expert * p.b_expert_rows + n0);
+            } else {
+              const int krow = (p.mode == OLB_GEMM_RAGGED_M ? ti.expert * p.b_expert_rows : 0) + kB;
+#pragma unroll
+              for (int j = 0; j < 2; ++j) tma_load_2d_pair(sb + j * MN_BOX_BYTES, tmb, fb, n0 + j * 64, krow);
+            }
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok || *abort_flag) {
+        // after a timeout: give this CTA's loads in flight time to land before its shared memory goes away
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (one thread of CTA 0 for the pair)
+    if (rank == 0 && elect_one()) {
+      const uint32_t idesc = make_idesc_bf16(256, BLOCK_N, p.a_mn_major, p.b_mn_major);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      TileInfo ti;
+      for (int t = pair_id; ok && get_tile_pair<EPI>(p, t, num_m, ti); t += num_pairs) {
+        if (ti.kb_end <= ti.kb_begin) continue;
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, p.status, ST_TIMEOUT_ACC_EMPTY, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
+        for (int kb = ti.kb_begin; kb < ti.kb_end; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, p.status, ST_TIMEOUT_FULL, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            const uint64_t da = p.a_mn_major ? make_smem_desc(sa + k * (UMMA_K * 128), MN_BOX_BYTES, 1024)
+                                             : make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t db = p.b_mn_major ? make_smem_desc(sb + k * (UMMA_K * 128), MN_BOX_BYTES, 1024)
+                                             : make_smem_desc(sb + k * (UMMA_K * 2), 16, 1024);
+            umma_ss_pair(tmem_d, da, db, idesc, (kb > ti.kb_begin || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(empty_bar(stage), 3);  // both CTAs' stages are free once these MMAs have read them
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(acc_full_bar(acc), 3);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs, own 128 rows)
+    const int lane_group = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    TileInfo ti;
+    EpiStage es{smem_base + L::EPI_OFFSET + lane_group * 2 * EPI_BUF_BYTES, 0};
+    const uint32_t acc_empty_remote0 = mapa_shared(acc_empty_bar(0), 0);
+    const uint32_t acc_empty_remote1 = mapa_shared(acc_empty_bar(1), 0);
+    for (int t = pair_id; get_tile_pair<EPI>(p, t, num_m, ti); t += num_pairs) {
+      const bool has_k = ti.kb_end > ti.kb_begin;
+      if (has_k) {
+        if (!mbar_wait(acc_full_bar(acc), acc_phase, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) break;
+        tc_fence_after();
+      } else if (p.accumulate) {
+        continue;
+      }
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) + acc * BLOCK_N;
+      TileInfo mine = ti;
+      mine.m0 = ti.m0 + static_cast<int>(rank) * 128;
+      if constexpr (EPI == EPI_SWIGLU) {
+        epilogue_swiglu(p, &tma_c, &tma_c2, es, taddr, mine, lane_group, lane);
+      } else {
+        epilogue_plain<BLOCK_N>(p, &tma_c, es, taddr, mine, has_k, lane_group, lane);
+      }
+      if constexpr (PEER) {
+        if (peers.push == 1 || peers.push == 2) {  // this warp's 32 rows of the tile are stored: let the stagers know
+          if (p.c_tma || EPI == EPI_SWIGLU) {
+            if (lane == 0) tma_store_wait_all();
+            fence_proxy_async_all();
+          }
+          __threadfence();
+          __syncwarp();
+          if (lane == 0 && mine.m0 < p.M) atomicAdd(peers.flags + mine.m0 / BLOCK_M, 1);
+        }
+      }
+      if (has_k) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc ? acc_empty_remote1 : acc_empty_remote0);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait_read();
+  }
+  if constexpr (PEER) {
+    if (warp >= 6) stager_loop(peers, p, num_m_blocks, warp - 6, lane, abort_flag);
+  }
+
+  // neither CTA may leave while its partner can still signal its barriers or read its shared memory
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
@@ -845,6 +1158,40 @@ static int launch(const TensorMaps& tm, const PeerArg<PEER>& peers, const GemmPa
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+template <bool PEER, int EPI>
+static int launch_pair(const TensorMaps& tm, const PeerArg<PEER>& peers, const GemmParams& p, int num_sms,
+                       cudaStream_t stream) {
+  using L = SmemLayoutPair;
+  constexpr int MAX_DEVICES = 64;
+  static bool configured[MAX_DEVICES] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -3;
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(gemm_bf16_pair_kernel<PEER, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) !=
+        cudaSuccess)
+      return -3;
+    configured[dev] = true;
+  }
+  constexpr int TILE_N = EPI == EPI_SWIGLU ? 128 : 256;
+  const long long nm = (p.M + 255) / 256, nn = (p.N + TILE_N - 1) / TILE_N;
+  const long long tiles = nm * nn * (p.mode == OLB_GEMM_RAGGED_K ? p.num_experts : 1);
+  const int max_pairs = num_sms / 2;
+  const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
+  if (pairs <= 0) return 0;
+  gemm_bf16_pair_kernel<PEER, EPI><<<2 * pairs, PEER ? NUM_THREADS_STAGED : NUM_THREADS, L::TOTAL, stream>>>(
+      tm.a, tm.b, tm.b2, tm.c, tm.c2, peers, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// OLB_GEMM_PAIR=0 keeps every GEMM on the single-CTA kernel (A/B comparisons, debugging).
+static bool pair_kernel_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("OLB_GEMM_PAIR");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
 template <bool PEER>
 static int dispatch(int block_n, int epi, const TensorMaps& tm, const PeerArg<PEER>& peers, const GemmParams& p, int sms,
                     cudaStream_t stream) {
@@ -894,6 +1241,14 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   }
   const int num_sms = device_sm_count();
   if (num_sms <= 0) return -3;
+  // CTA pairs (256 x 256 tiles) for the plain dense and per-expert weight-gradient products that fill such tiles
+  // (ragged-M: only when the caller padded the expert groups to 256 rows; the dense all-gather / reduce-scatter
+  // variants, whose peers own multiples of 128 rows, stay on the single-CTA kernel)
+  const bool pair_shape = d->block_n == 0 && block_n == 256 && d->blk_range == nullptr && d->M >= 256 && num_sms >= 2 &&
+                          (epi == OLB_EPI_SWIGLU || d->N % 256 == 0 || d->N >= 2048);
+  const bool use_pair = pair_kernel_enabled() && pair_shape &&
+                        (d->mode == OLB_GEMM_RAGGED_M ? (d->pair_rows != 0 && d->M % 256 == 0)
+                                                      : (d->n_peers == 0 && epi == OLB_EPI_PLAIN));
 
   // cuTensorMapEncodeTiled is a driver call and needs a current context in the calling thread.
   // A thread that has only been handed tensors (an autograd worker whose first CUDA work is this
@@ -912,13 +1267,14 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
     rc = make_tmap_2d_bf16(&tm.a, d->A, d->M, d->a_rows, d->lda * 2, 64, BLOCK_K);
   if (rc) return rc;
   int kb_split = 0;
+  const int b_box_rows = use_pair ? 128 : block_n;   // a CTA of a pair stages half of the tile's B rows
   if (epi == OLB_EPI_SWIGLU) {
     rc = make_tmap_2d_bf16(&tm.b, d->B, d->K, d->b_rows, d->ldb * 2, BLOCK_K, 128);
     if (!rc) rc = make_tmap_2d_bf16(&tm.b2, d->B2, d->K, d->b_rows, d->ldb * 2, BLOCK_K, 128);
     if (rc) return rc;
   } else {
     if (!d->b_mn_major)
-      rc = make_tmap_2d_bf16(&tm.b, d->B, d->K, d->b_rows, d->ldb * 2, BLOCK_K, block_n);
+      rc = make_tmap_2d_bf16(&tm.b, d->B, d->K, d->b_rows, d->ldb * 2, BLOCK_K, b_box_rows);
     else
       rc = make_tmap_2d_bf16(&tm.b, d->B, d->N, d->b_rows, d->ldb * 2, 64, BLOCK_K);
     if (rc) return rc;
@@ -930,8 +1286,8 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
       const int k1 = d->k_split, k2 = d->K - d->k_split;
       // each map covers only its own K extent, so that reads past it are zero-filled as usual
       if (!d->b_mn_major) {
-        rc = make_tmap_2d_bf16(&tm.b, d->B, k1, d->b_rows, d->ldb * 2, BLOCK_K, block_n);
-        if (!rc) rc = make_tmap_2d_bf16(&tm.b2, d->B2, k2, d->b_rows, d->ldb * 2, BLOCK_K, block_n);
+        rc = make_tmap_2d_bf16(&tm.b, d->B, k1, d->b_rows, d->ldb * 2, BLOCK_K, b_box_rows);
+        if (!rc) rc = make_tmap_2d_bf16(&tm.b2, d->B2, k2, d->b_rows, d->ldb * 2, BLOCK_K, b_box_rows);
       } else {
         rc = make_tmap_2d_bf16(&tm.b2, d->B2, d->N, d->b_rows, d->ldb * 2, 64, BLOCK_K);
       }
@@ -963,6 +1319,7 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   p.row_k_of = d->row_k_of;
   p.row_weights = d->row_weights;
   p.row_topk = d->row_topk;
+  p.pair_rows = d->pair_rows;
 
   // Output through tensor-map stores whenever a 2D map describes it: no read-modify-write, and for the per-expert
   // weight gradients experts that tile exactly (a box must not run into the next expert's rows).
@@ -1031,6 +1388,9 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
         peers.src_ld = d->a_src_ld;
         peers.row_vecs = d->K / 8;
       }
+      if (use_pair)
+        return epi == OLB_EPI_SWIGLU ? launch_pair<true, EPI_SWIGLU>(tm, peers, p, sms, stream)
+                                     : launch_pair<true, EPI_PLAIN>(tm, peers, p, sms, stream);
       return dispatch<true>(block_n, epi, tm, peers, p, sms, stream);
     }
     if (epi != OLB_EPI_PLAIN) return -14;
@@ -1069,5 +1429,8 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
     return dispatch<true>(block_n, epi, tm, peers, p, sms, stream);
   }
   PeerArg<false> nopeers{};
+  if (use_pair)
+    return epi == OLB_EPI_SWIGLU ? launch_pair<false, EPI_SWIGLU>(tm, nopeers, p, sms, stream)
+                                 : launch_pair<false, EPI_PLAIN>(tm, nopeers, p, sms, stream);
   return dispatch<false>(block_n, epi, tm, nopeers, p, sms, stream);
 }

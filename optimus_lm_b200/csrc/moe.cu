@@ -74,7 +74,7 @@ moe_count_kernel(const int* __restrict__ indices, int T, int K, int e_start, int
 }
 
 // One block; thread e scans expert e over the token blocks, then thread 0 lays out the experts.
-__global__ void moe_scan_kernel(int* __restrict__ ws, int nblocks, int E_loc, int cap, int* __restrict__ meta,
+__global__ void moe_scan_kernel(int* __restrict__ ws, int nblocks, int E_loc, int cap, int row_pad, int* __restrict__ meta,
                                 int* __restrict__ offsets, int* __restrict__ counts, int* __restrict__ status) {
   __shared__ int s_total[MAX_E_LOC];
   __shared__ int s_off[MAX_E_LOC + 1];
@@ -95,10 +95,10 @@ __global__ void moe_scan_kernel(int* __restrict__ ws, int nblocks, int E_loc, in
     bool overflow = false;
     for (int e = 0; e < E_loc; ++e) {
       s_off[e] = off;
-      int padded = (s_total[e] + 127) & ~127;
+      int padded = (s_total[e] + row_pad - 1) / row_pad * row_pad;
       if (off + padded > cap) {
         overflow = true;
-        padded = (cap - off) & ~127;  // clamp: the excess pairs of this expert are dropped
+        padded = (cap - off) / row_pad * row_pad;  // clamp: the excess pairs of this expert are dropped
       }
       off += padded;
     }
@@ -294,15 +294,15 @@ extern "C" long long olb_moe_ws_ints(int T, int E_loc) {
   return 2 * nblocks * E_loc;
 }
 
-extern "C" int olb_moe_build_index(const int* indices, int T, int K, int e_start, int E_loc, int cap, int* ws,
+extern "C" int olb_moe_build_index(const int* indices, int T, int K, int e_start, int E_loc, int cap, int row_pad, int* ws,
                                    int* row_of, int* src_of, int* k_of, int* meta, int* offsets, int* counts,
                                    int* status, cudaStream_t stream) {
-  if (E_loc > MAX_E_LOC || E_loc <= 0 || K > 32 || cap % 128) return -1;
+  if (E_loc > MAX_E_LOC || E_loc <= 0 || K > 32 || (row_pad != 128 && row_pad != 256) || cap % row_pad) return -1;
   if (T <= 0) return 0;
   const int nblocks = (T + IDX_THREADS - 1) / IDX_THREADS;
   fill_int_kernel<<<148, 256, 0, stream>>>(src_of, cap, -1);
   moe_count_kernel<<<nblocks, IDX_THREADS, 0, stream>>>(indices, T, K, e_start, E_loc, ws);
-  moe_scan_kernel<<<1, 256, 0, stream>>>(ws, nblocks, E_loc, cap, meta, offsets, counts, status);
+  moe_scan_kernel<<<1, 256, 0, stream>>>(ws, nblocks, E_loc, cap, row_pad, meta, offsets, counts, status);
   moe_place_kernel<<<nblocks, IDX_THREADS, 0, stream>>>(indices, T, K, e_start, E_loc, ws, nblocks, offsets, row_of,
                                                         src_of, k_of);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;

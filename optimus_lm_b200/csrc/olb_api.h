@@ -70,6 +70,8 @@ typedef struct {
   // w(row) * silu(gate) * up to C2 [M, N] (row stride ldc2), computed from the bf16-rounded gate and up values.
   // w(row) = row_weights[row_src_of[row] * row_topk + row_k_of[row]], 0 where row_src_of[row] < 0; 1 when the three
   // pointers are null.
+  int pair_rows;             // RAGGED_M: the expert groups are padded to 256 rows (olb_moe_build_index with row_pad
+                             // 256), which lets two CTAs on neighbouring SMs share one 256-row tile
   int epilogue;
   void* C2;
   long long ldc2;
@@ -148,15 +150,16 @@ int olb_router_sigmoid_bwd(const float* logits, const int* indices, const float*
 
 // ---------------------------------------------------------------- MoE permutation (moe.cu)
 // Build the expert-grouped row layout for the pairs (t,k) whose expert lies in
-// [e_start, e_start+E_loc).  Each expert's rows start at a multiple of 128.
+// [e_start, e_start+E_loc).  Each expert's rows start at a multiple of `row_pad` (128, or 256 so that a pair of CTAs
+// can share a 256-row GEMM tile; `cap` must be a multiple of it).
 //   ws          : int workspace, at least olb_moe_ws_ints(T, E_loc) ints
 //   row_of      : [T, K]   destination row of pair (t,k) or -1
 //   src_of,k_of : [cap]    source token / k slot of each row, -1 for padding rows
 //   meta        : [1 + cap/128] GEMM tile table (see OLB_GEMM_RAGGED_M)
 //   offsets     : [E_loc+1] padded row offsets (see OLB_GEMM_RAGGED_K); counts: [E_loc] true counts
 // If the padded rows exceed `cap`, status receives ST_OVERFLOW and the excess pairs get row -1.
-int olb_moe_build_index(const int* indices, int T, int K, int e_start, int E_loc, int cap, int* ws, int* row_of,
-                        int* src_of, int* k_of, int* meta, int* offsets, int* counts, int* status,
+int olb_moe_build_index(const int* indices, int T, int K, int e_start, int E_loc, int cap, int row_pad, int* ws,
+                        int* row_of, int* src_of, int* k_of, int* meta, int* offsets, int* counts, int* status,
                         cudaStream_t stream);
 long long olb_moe_ws_ints(int T, int E_loc);
 // out[row,:] = src_of[row] >= 0 ? x[src_of[row],:] : 0   for row < meta[0]*128   (bf16, cols % 8 == 0)

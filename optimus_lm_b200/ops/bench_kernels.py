@@ -41,6 +41,22 @@ def bench_gemm():
         fl = 2.0 * M * N * K
         print(f"gemm NT {M}x{N}x{K}: tcgen05 kernel {t1:.3f} ms ({fl / t1 * 1e-9:.0f} TFLOP/s) | cuBLAS {t2:.3f} ms "
               f"({fl / t2 * 1e-9:.0f} TFLOP/s)", flush=True)
+    # the other two products of a projection at the model's shape: input gradient (NN) and weight gradient (TN)
+    M, N, K = 16384, 2048, 2048
+    dy = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+    w = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+    x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    dx = torch.empty(M, K, device="cuda", dtype=torch.bfloat16)
+    dw = torch.empty(N, K, device="cuda", dtype=torch.bfloat16)
+    fl = 2.0 * M * N * K
+    t1 = _time(lambda: OF.gemm(dy, w, M, K, N, b_mn_major=True, out=dx), flush=flush)
+    t2 = _time(lambda: torch.matmul(dy, w, out=dx), flush=flush)
+    print(f"gemm NN (dgrad) {M}x{K}x{N}: tcgen05 kernel {t1:.3f} ms ({fl / t1 * 1e-9:.0f} TFLOP/s) | cuBLAS {t2:.3f} ms "
+          f"({fl / t2 * 1e-9:.0f} TFLOP/s)", flush=True)
+    t1 = _time(lambda: OF.gemm(dy, x, N, K, M, a_mn_major=True, b_mn_major=True, out=dw), flush=flush)
+    t2 = _time(lambda: torch.matmul(dy.t(), x, out=dw), flush=flush)
+    print(f"gemm TN (wgrad) {N}x{K}x{M}: tcgen05 kernel {t1:.3f} ms ({fl / t1 * 1e-9:.0f} TFLOP/s) | cuBLAS {t2:.3f} ms "
+          f"({fl / t2 * 1e-9:.0f} TFLOP/s)", flush=True)
 
 
 def bench_grouped():

@@ -54,17 +54,20 @@ def _kernel_ok(*ts) -> bool:
 def gemm(a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, *, a_mn_major=False, b_mn_major=False,
          out: Optional[torch.Tensor] = None, accumulate=False, mode=GEMM_DENSE, meta=None, num_experts=1,
          b_expert_rows=0, c_expert_stride=0, out_dtype=torch.bfloat16, block_n=0, max_ctas=0,
-         b2: Optional[torch.Tensor] = None, k_split=0, blk_range: Optional[torch.Tensor] = None) -> torch.Tensor:
+         b2: Optional[torch.Tensor] = None, k_split=0, blk_range: Optional[torch.Tensor] = None,
+         pair_rows: bool = False) -> torch.Tensor:
     """Raw tcgen05 GEMM on 2D bf16 views (unit inner stride). See csrc/olb_api.h.  With ``b2`` (same
     layout as ``b``) the K range ``[k_split, K)`` is read from ``b2``: one launch for
     ``a[:, :k_split] @ b + a[:, k_split:] @ b2``.  ``blk_range`` (ragged-M, two int32 on the device) restricts the
-    launch to the 128-row blocks ``[blk_range[0], blk_range[1])``."""
+    launch to the 128-row blocks ``[blk_range[0], blk_range[1])``.  ``pair_rows`` (ragged-M): the expert groups are padded
+    to 256 rows, so two CTAs on neighbouring SMs may share a 256-row tile (``cta_group::2``)."""
     if out is None:
         assert not accumulate
         shape = (num_experts, M, N) if mode == GEMM_RAGGED_K else (M, N)
         out = torch.empty(shape, dtype=out_dtype, device=a.device)
     extension().gemm(a, b, out, M, N, K, a_mn_major, b_mn_major, accumulate, mode, meta, num_experts,
-                     b_expert_rows, c_expert_stride, status_word(a.device), block_n, max_ctas, b2, k_split, blk_range)
+                     b_expert_rows, c_expert_stride, status_word(a.device), block_n, max_ctas, b2, k_split, blk_range,
+                     pair_rows)
     return out
 
 
@@ -590,15 +593,18 @@ def moe_experts_reference(x, topk_w, topk_idx, wg, wu, wd, e_start=0):
     return out
 
 
+ROW_PAD = 256   # every expert's rows start at a multiple of this: a pair of CTAs shares one 256-row GEMM tile
+
+
 def moe_capacity_rows(T: int, K: int, E_loc: int, ep: int = 1, capacity_factor: float = 0.0) -> int:
-    """Row capacity of the expert-grouped buffers: every routed pair plus 127 padding rows per
-    local expert, rounded to 128.  With ``capacity_factor > 0`` (expert parallel receive
+    """Row capacity of the expert-grouped buffers: every routed pair plus ``ROW_PAD - 1`` padding rows per
+    local expert, rounded to ``ROW_PAD``.  With ``capacity_factor > 0`` (expert parallel receive
     side) the pair count is ``capacity_factor`` x the balanced share instead of the worst case."""
     pairs = T * K
     if capacity_factor and ep > 1:
         pairs = min(pairs, int(math.ceil(capacity_factor * T * K / ep)))
-    rows = pairs + E_loc * 127
-    return ((rows + 127) // 128) * 128
+    rows = pairs + E_loc * (ROW_PAD - 1)
+    return ((rows + ROW_PAD - 1) // ROW_PAD) * ROW_PAD
 
 
 _PART_CUTS = {}
@@ -625,7 +631,7 @@ class MoEIndex:
     choosing this rank's experts; sizing the saved activations for that would not fit, sizing them for a fixed
     multiple of the balanced share can overflow, so the count is read instead and no routed pair is ever dropped."""
 
-    __slots__ = ("row_of", "src_of", "k_of", "meta", "offsets", "counts", "cap", "rows", "E_loc", "K")
+    __slots__ = ("row_of", "src_of", "k_of", "meta", "offsets", "counts", "cap", "rows", "E_loc", "K", "pair")
 
     def __init__(self, topk_idx: torch.Tensor, e_start: int, E_loc: int, cap: int, exact: bool = False):
         C = extension()
@@ -639,8 +645,9 @@ class MoEIndex:
         self.offsets = torch.empty(E_loc + 1, dtype=torch.int32, device=dev)
         self.counts = torch.empty(E_loc, dtype=torch.int32, device=dev)
         self.cap, self.E_loc, self.K = cap, E_loc, K
+        self.pair = cap % ROW_PAD == 0      # expert groups padded to 256 rows: the CTA-pair kernels may take them
         C.moe_build_index(topk_idx.contiguous(), e_start, E_loc, cap, ws, self.row_of, self.src_of, self.k_of,
-                          self.meta, self.offsets, self.counts, status_word(dev))
+                          self.meta, self.offsets, self.counts, status_word(dev), ROW_PAD if self.pair else 128)
         self.rows = cap
         if exact:
             used = int(self.meta[0].item()) * 128
@@ -663,14 +670,14 @@ def grouped_linear_fwd(xp, w, index: MoEIndex, out=None, blk_range=None):
     """``y[rows of e] = xp[rows of e] @ w[e].T`` for merged weights ``w [E, N, K]``."""
     E, N, K = w.shape
     return gemm(xp, w.view(E * N, K), index.rows, N, K, mode=GEMM_RAGGED_M, meta=index.meta, b_expert_rows=N, out=out,
-                blk_range=blk_range)
+                blk_range=blk_range, pair_rows=index.pair)
 
 
 def grouped_linear_dgrad(dy, w, index: MoEIndex, out=None, accumulate=False, blk_range=None):
     """``dx[rows of e] (+)= dy[rows of e] @ w[e]``."""
     E, N, K = w.shape
     return gemm(dy, w.view(E * N, K), index.rows, K, N, b_mn_major=True, mode=GEMM_RAGGED_M, meta=index.meta,
-                b_expert_rows=N, out=out, accumulate=accumulate, blk_range=blk_range)
+                b_expert_rows=N, out=out, accumulate=accumulate, blk_range=blk_range, pair_rows=index.pair)
 
 
 def grouped_linear_dgrad_pair(dh, w1, w2, index: MoEIndex, out=None):
@@ -679,7 +686,7 @@ def grouped_linear_dgrad_pair(dh, w1, w2, index: MoEIndex, out=None):
     E, N, K = w1.shape
     assert w2.shape == w1.shape and dh.shape[1] == 2 * N
     return gemm(dh, w1.view(E * N, K), index.rows, K, 2 * N, b_mn_major=True, mode=GEMM_RAGGED_M, meta=index.meta,
-                b_expert_rows=N, out=out, b2=w2.view(E * N, K), k_split=N)
+                b_expert_rows=N, out=out, b2=w2.view(E * N, K), k_split=N, pair_rows=index.pair)
 
 
 def grouped_linear_wgrad(dy, xp, index: MoEIndex, N: int, K: int, holder: Optional["DirectGrad"] = None):
@@ -715,7 +722,8 @@ def grouped_gateup_swiglu(x_ptrs, x_ld: int, tokens: int, weights, wg, wu, index
         C.swiglu_rowscale_fwd(h[:, :I], h[:, I:], index.src_of, index.k_of, weights, index.meta, act)
         return xp, h, act
     C.gemm_gateup_swiglu(xp, wg.view(E * I, H), wu.view(E * I, H), h, act, rows, I, H, index.meta, index.src_of,
-                         index.k_of, weights, E, list(x_ptrs), x_ld, tokens, stage_flags(dev, rows), status_word(dev))
+                         index.k_of, weights, E, list(x_ptrs), x_ld, tokens, stage_flags(dev, rows), status_word(dev),
+                         index.pair)
     return xp, h, act
 
 
@@ -729,7 +737,7 @@ def grouped_gather_dgrad(y_ptrs, y_ld: int, tokens: int, w, index: MoEIndex):
     dyp = torch.empty((rows, H), dtype=w.dtype, device=dev)
     dact = torch.empty((rows, I), dtype=w.dtype, device=dev)
     C.gemm_ep_gather(dyp, w.view(E * H, I), dact, rows, I, H, True, index.meta, index.src_of, H, E, list(y_ptrs), y_ld,
-                     tokens, stage_flags(dev, rows), status_word(dev))
+                     tokens, stage_flags(dev, rows), status_word(dev), index.pair)
     return dyp, dact
 
 

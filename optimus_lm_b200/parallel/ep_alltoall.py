@@ -70,7 +70,7 @@ class _FusedEPMoEFn(torch.autograd.Function):
         ys = torch.empty((rows, H), dtype=x.dtype, device=x.device)
         recv = sg.named("ep_recv", (T, K, H), x.dtype)
         C.gemm_ep_push(act, wd.view(E_loc * H, I), ys, recv.ptrs, index.meta, index.src_of, index.k_of, rows, H, I, H,
-                       E_loc, T, K, rank, OF.stage_flags(x.device, rows), status)
+                       E_loc, T, K, rank, OF.stage_flags(x.device, rows), status, pair_rows=index.pair)
         del ys
         sg.barrier(1)
         out = torch.empty((T, H), dtype=x.dtype, device=x.device)
@@ -110,7 +110,8 @@ class _FusedEPMoEFn(torch.autograd.Function):
         dxp = torch.empty((rows, H), dtype=dout.dtype, device=dout.device)
         recv = sg.named("ep_recv", (T, K, H), dout.dtype)
         C.gemm_ep_push(dh, wg.view(E_loc * I, H), dxp, recv.ptrs, index.meta, index.src_of, index.k_of, rows, H, 2 * I, I,
-                       E_loc, T, K, rank, OF.stage_flags(dout.device, rows), status, True, wu.view(E_loc * I, H), I)
+                       E_loc, T, K, rank, OF.stage_flags(dout.device, rows), status, True, wu.view(E_loc * I, H), I,
+                       index.pair)
         del dxp
         dx = torch.empty((T, H), dtype=dout.dtype, device=dout.device)
         dtopk = torch.empty((T, K), dtype=torch.float32, device=dout.device)

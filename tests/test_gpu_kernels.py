@@ -108,8 +108,8 @@ def test_moe_index(T, E, K, e_start, E_loc):
     idx_c = idx.cpu()
     for le in range(E_loc):
         assert counts[le].item() == (idx_c == e_start + le).sum().item()
-        assert offs[le].item() % 128 == 0
-        assert offs[le + 1].item() - offs[le].item() == (counts[le].item() + 127) // 128 * 128
+        assert offs[le].item() % OF.ROW_PAD == 0
+        assert offs[le + 1].item() - offs[le].item() == -(-counts[le].item() // OF.ROW_PAD) * OF.ROW_PAD
     assert meta[0].item() * 128 == offs[E_loc].item()
     for i in range(meta[0].item()):
         e = meta[1 + i].item()
