@@ -107,14 +107,28 @@ void rmsnorm_fwd(const at::Tensor& x, const c10::optional<at::Tensor>& w, at::Te
 int64_t rmsnorm_bwd_blocks(int64_t rows) { return olb_rmsnorm_bwd_blocks(static_cast<int>(rows)); }
 
 void rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const c10::optional<at::Tensor>& w, const at::Tensor& rstd,
-                 at::Tensor& dx, const c10::optional<at::Tensor>& dw_partial) {
+                 at::Tensor& dx, const c10::optional<at::Tensor>& dw_partial, const c10::optional<at::Tensor>& dres) {
   CHECK_CUDA_BF16(x);
   c10::cuda::CUDAGuard guard(x.device());
   const int cols = x.size(-1);
   const int rows = x.numel() / cols;
-  check(olb_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), opt_ptr<const void>(w), rstd.data_ptr<float>(), dx.data_ptr(),
-                        opt_ptr<float>(dw_partial), rows, cols, cur_stream()),
+  if (dres.has_value()) TORCH_CHECK(dres->scalar_type() == at::kBFloat16 && dres->is_contiguous() && dres->numel() == x.numel());
+  check(olb_rmsnorm_bwd_res(dy.data_ptr(), x.data_ptr(), opt_ptr<const void>(w), rstd.data_ptr<float>(), dx.data_ptr(),
+                            opt_ptr<float>(dw_partial), opt_ptr<const void>(dres), rows, cols, cur_stream()),
         "olb_rmsnorm_bwd");
+}
+
+void add_rmsnorm_fwd(const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& w, at::Tensor& h,
+                     at::Tensor& y, at::Tensor& rstd, double eps) {
+  CHECK_CUDA_BF16(a);
+  CHECK_CUDA_BF16(b);
+  TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && h.is_contiguous() && y.is_contiguous() && a.numel() == b.numel());
+  c10::cuda::CUDAGuard guard(a.device());
+  const int cols = a.size(-1);
+  const int rows = a.numel() / cols;
+  check(olb_add_rmsnorm_fwd(a.data_ptr(), b.data_ptr(), opt_ptr<const void>(w), h.data_ptr(), y.data_ptr(),
+                            rstd.data_ptr<float>(), rows, cols, static_cast<float>(eps), cur_stream()),
+        "olb_add_rmsnorm_fwd");
 }
 
 void colsum_finalize(const at::Tensor& partial, int64_t nparts, at::Tensor& dw, bool accumulate) {
@@ -274,6 +288,18 @@ void moe_build_index(const at::Tensor& indices, int64_t e_start, int64_t E_loc, 
         "olb_moe_build_index");
 }
 
+void moe_scatter_dweights(const at::Tensor& partial, const at::Tensor& src_of, const at::Tensor& k_of, const at::Tensor& meta,
+                          at::Tensor& out) {
+  CHECK_CUDA_F32(partial);
+  CHECK_CUDA_F32(out);
+  TORCH_CHECK(partial.dim() == 2 && partial.is_contiguous() && out.dim() == 2 && out.is_contiguous());
+  c10::cuda::CUDAGuard guard(partial.device());
+  check(olb_moe_scatter_dweights(partial.data_ptr<float>(), static_cast<int>(partial.size(1)), src_of.data_ptr<int>(),
+                                 k_of.data_ptr<int>(), meta.data_ptr<int>(), static_cast<int>(out.size(1)),
+                                 out.data_ptr<float>(), static_cast<int>(partial.size(0)), cur_stream()),
+        "olb_moe_scatter_dweights");
+}
+
 void moe_gather_rows(const at::Tensor& x, const at::Tensor& src_of, const at::Tensor& meta, at::Tensor& out) {
   CHECK_CUDA_BF16(x);
   c10::cuda::CUDAGuard guard(x.device());
@@ -422,7 +448,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
-  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd, pybind11::arg("dy"), pybind11::arg("x"), pybind11::arg("w"), pybind11::arg("rstd"),
+        pybind11::arg("dx"), pybind11::arg("dw_partial"), pybind11::arg("dres") = pybind11::none());
+  m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
   m.def("rmsnorm_bwd_blocks", &rmsnorm_bwd_blocks);
   m.def("colsum_finalize", &colsum_finalize);
   m.def("layernorm_fwd", &layernorm_fwd);
@@ -442,6 +470,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("cap"), pybind11::arg("ws"), pybind11::arg("row_of"), pybind11::arg("src_of"), pybind11::arg("k_of"),
         pybind11::arg("meta"), pybind11::arg("offsets"), pybind11::arg("counts"), pybind11::arg("status"),
         pybind11::arg("row_pad") = 128);
+  m.def("moe_scatter_dweights", &moe_scatter_dweights);
   m.def("moe_gather_rows", &moe_gather_rows);
   m.def("moe_combine", &moe_combine);
   m.def("moe_combine_bwd", &moe_combine_bwd);

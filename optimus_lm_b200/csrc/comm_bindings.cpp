@@ -331,10 +331,15 @@ void gemm_gateup_swiglu(at::Tensor& xp, const at::Tensor& wg2d, const at::Tensor
 
 // Grouped GEMM whose operand rows are gathered inside the kernel (see gemm_gateup_swiglu): c[u, :] = xp[u, :] W[e(u)]^T
 // (or xp W with `b_mn_major`) with xp[u] = x_peers[src_of[u] / tokens][src_of[u] % tokens].  `xp` is left filled.
+// With `h` (saved gate | up [rows, 2 N]), `k_of`, `weights` and `dw_partial` the SwiGLU backward runs in the launch's
+// epilogue: `c` is then d(gate) | d(up) [rows, 2 N] and `dw_partial` [rows, N / 256] receives the per-tile partials of the
+// routing-weight gradient (CTA-pair kernel: rows padded to 256 per expert, N a multiple of 256).
 void gemm_ep_gather(at::Tensor& xp, const at::Tensor& w2d, at::Tensor& c, int64_t M, int64_t N, int64_t K, bool b_mn_major,
                     const at::Tensor& meta, const at::Tensor& src_of, int64_t b_expert_rows, int64_t num_experts,
                     const std::vector<int64_t>& x_peers, int64_t x_ld, int64_t tokens, at::Tensor& flags,
-                    const c10::optional<at::Tensor>& status, bool pair_rows) {
+                    const c10::optional<at::Tensor>& status, bool pair_rows, const c10::optional<at::Tensor>& h,
+                    const c10::optional<at::Tensor>& k_of, const c10::optional<at::Tensor>& weights,
+                    const c10::optional<at::Tensor>& dw_partial) {
   TORCH_CHECK(xp.is_cuda() && xp.scalar_type() == at::kBFloat16 && w2d.scalar_type() == at::kBFloat16 &&
                   c.scalar_type() == at::kBFloat16,
               "bf16 CUDA operands expected");
@@ -371,6 +376,21 @@ void gemm_ep_gather(at::Tensor& xp, const at::Tensor& w2d, at::Tensor& c, int64_
   d.ep_src_of = src_of.data_ptr<int>();
   d.ep_tokens = static_cast<int>(tokens);
   d.pair_rows = pair_rows;
+  if (h.has_value()) {
+    TORCH_CHECK(k_of.has_value() && weights.has_value() && dw_partial.has_value() && h->scalar_type() == at::kBFloat16 &&
+                h->dim() == 2 && h->stride(1) == 1 && h->size(0) >= M && h->size(1) == 2 * N && c.size(1) == 2 * N &&
+                weights->scalar_type() == at::kFloat && weights->is_contiguous() && weights->dim() == 2 &&
+                k_of->scalar_type() == at::kInt && dw_partial->scalar_type() == at::kFloat && dw_partial->is_contiguous() &&
+                dw_partial->numel() >= M * ((N + 255) / 256));
+    d.epilogue = OLB_EPI_SWIGLU_BWD;
+    d.aux_in = h->data_ptr();
+    d.aux_ld = h->stride(0);
+    d.aux_out = dw_partial->data_ptr<float>();
+    d.row_src_of = src_of.data_ptr<int>();
+    d.row_k_of = k_of->data_ptr<int>();
+    d.row_weights = weights->data_ptr<float>();
+    d.row_topk = static_cast<int>(weights->size(1));
+  }
   check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (expert-parallel dispatch variant)");
 }
 
@@ -428,7 +448,8 @@ void register_comm(pybind11::module& m) {
   m.def("gemm_ep_gather", &gemm_ep_gather, py::arg("xp"), py::arg("w2d"), py::arg("c"), py::arg("M"), py::arg("N"),
         py::arg("K"), py::arg("b_mn_major"), py::arg("meta"), py::arg("src_of"), py::arg("b_expert_rows"),
         py::arg("num_experts"), py::arg("x_peers"), py::arg("x_ld"), py::arg("tokens"), py::arg("flags"),
-        py::arg("status"), py::arg("pair_rows") = false);
+        py::arg("status"), py::arg("pair_rows") = false, py::arg("h") = py::none(), py::arg("k_of") = py::none(),
+        py::arg("weights") = py::none(), py::arg("dw_partial") = py::none());
   m.def("rs_adamw_blocks", &rs_adamw_blocks);
   m.def("rs_adamw", &rs_adamw);
 }

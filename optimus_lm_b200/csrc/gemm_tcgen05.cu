@@ -75,9 +75,15 @@ struct GemmParams {
   const int* row_k_of;
   const float* row_weights;
   int row_topk;
+  // EPI_SWIGLU_BWD: the accumulator is d(act) [rows, N]; aux_in = saved gate | up [rows, 2 N] (row stride aux_ld);
+  // tma_c covers d(gate) | d(up) [rows, 2 N]; aux_out [rows, ceil(N / 256)] receives, per row and column tile, the
+  // partial dot product <d(act), silu(gate) * up> (the routing-weight gradient, summed over its tiles afterwards).
+  const void* aux_in;
+  long long aux_ld;
+  float* aux_out;
 };
 
-enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_SWIGLU_BWD = 2 };
 
 // All-gather fused into the GEMM: the outer rows of A live in the memories of up to 8 GPUs.  Four extra warps per
 // CTA ("stagers") copy the other GPUs' rows into this GPU's gathered copy of A with plain loads over NVLink and
@@ -402,6 +408,66 @@ __device__ __forceinline__ void epilogue_swiglu(const GemmParams& p, const CUten
   }
 }
 
+// Epilogue of one 128-row tile of the down projection's input gradient with the SwiGLU backward folded in: the
+// accumulator holds d(act) for columns [ti.n0, ti.n0 + 256); gate and up of the same rows and columns are read from
+// the saved forward buffer; d(gate) = d(act) w up silu'(gate) and d(up) = d(act) w silu(gate) go out through staged
+// tensor-map stores, the row's partial <d(act), silu(gate) up> to aux_out.  d(act) is rounded to bf16 first, as if it
+// had been stored and read back by a separate kernel.
+__device__ __forceinline__ void epilogue_swiglu_bwd(const GemmParams& p, const CUtensorMap* tma_c, EpiStage& es,
+                                                    uint32_t taddr, const TileInfo& ti, int lane_group, int lane) {
+  const int row = ti.m0 + lane_group * 32 + lane;
+  const bool row_ok = row < p.M;
+  const int src = (row_ok && p.row_src_of) ? p.row_src_of[row] : (row_ok ? 0 : -1);
+  float w = 0.f;
+  if (src >= 0) w = p.row_weights ? p.row_weights[static_cast<long long>(src) * p.row_topk + p.row_k_of[row]] : 1.f;
+  const __nv_bfloat16* hrow = static_cast<const __nv_bfloat16*>(p.aux_in) + static_cast<long long>(row) * p.aux_ld;
+  const int y = ti.m0 + lane_group * 32;
+  float dot = 0.f;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {  // 64 columns per turn
+    uint32_t vg[32], vu[32];
+    const int x = ti.n0 + c * 64;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(taddr + c * 64 + half * 32, r);
+      uint4 g4[4], u4[4];
+      if (src >= 0 && x + half * 32 < p.N) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          g4[j] = *reinterpret_cast<const uint4*>(hrow + x + half * 32 + j * 8);
+          u4[j] = *reinterpret_cast<const uint4*>(hrow + p.N + x + half * 32 + j * 8);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) g4[j] = u4[j] = make_uint4(0, 0, 0, 0);
+      }
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t gw[4] = {g4[j].x, g4[j].y, g4[j].z, g4[j].w}, uw[4] = {u4[j].x, u4[j].y, u4[j].z, u4[j].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int i = j * 4 + q;  // pair index inside the 32-column half
+          const float2 fg = unpack_bf16(gw[q]), fu = unpack_bf16(uw[q]);
+          const float2 fd = unpack_bf16(pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
+          const float sig0 = 1.f / (1.f + __expf(-fg.x)), sig1 = 1.f / (1.f + __expf(-fg.y));
+          const float silu0 = fg.x * sig0, silu1 = fg.y * sig1;
+          dot += fd.x * silu0 * fu.x + fd.y * silu1 * fu.y;
+          vu[half * 16 + i] = pack_bf16(fd.x * w * silu0, fd.y * w * silu1);
+          vg[half * 16 + i] = pack_bf16(fd.x * w * fu.x * (sig0 + silu0 * (1.f - sig0)),
+                                        fd.y * w * fu.y * (sig1 + silu1 * (1.f - sig1)));
+        }
+      }
+    }
+    if (y < p.M && x < p.N) {
+      epi_store_chunk(es, tma_c, vg, lane, x, y);
+      epi_store_chunk(es, tma_c, vu, lane, p.N + x, y);
+    }
+  }
+  if (row_ok && p.aux_out) p.aux_out[static_cast<long long>(row) * ((p.N + 255) / 256) + ti.n0 / 256] = dot;
+}
+
 // The extra warps of the variants with a fused transfer (PeerArg<true>): `swarp` is the warp's index among the CTA's
 // STAGER_WARPS stagers, `num_m_blocks` the number of 128-row blocks of the launch.
 __device__ __forceinline__ void stager_loop(const PeerArg<true>& peers, const GemmParams& p, int num_m_blocks, int swarp,
@@ -413,40 +479,51 @@ __device__ __forceinline__ void stager_loop(const PeerArg<true>& peers, const Ge
   const long long total = (peers.push == 2 || peers.push == 3)
                               ? min(static_cast<long long>(num_m_blocks) * BLOCK_M, static_cast<long long>(p.M))
                               : static_cast<long long>(peers.n - 1) * peers.rows;
-  int ready_blk = -1;
-  bool ok = true;
-  for (long long u = blockIdx.x * STAGER_WARPS + swarp; ok && u < total;
-       u += static_cast<long long>(gridDim.x) * STAGER_WARPS) {
-    if (peers.push == 3) {
-      // -------- expert-parallel dispatch: the routed token row comes from its owner into the grouped operand
-      const int g = peers.src_of[u];
-      uint4* d = reinterpret_cast<uint4*>(static_cast<char*>(peers.dst) + u * peers.ld * 2);
-      if (g >= 0) {
-        const int owner = g / peers.T;
-        const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.src[owner]) +
-                                                        static_cast<long long>(g - owner * peers.T) * peers.src_ld * 2);
-        for (int c0 = 0; c0 < peers.row_vecs; c0 += 256) {
-          uint4 v[8];
+  if (peers.push == 3) {
+    // -------- expert-parallel dispatch: the routed token rows come from their owners into the grouped operand.
+    // A warp takes two consecutive rows per turn (same 128-row block): 16 loads of 16 bytes in flight per lane, and
+    // one fence + one count update for both.
+    for (long long c = blockIdx.x * STAGER_WARPS + swarp; 2 * c < total; c += static_cast<long long>(gridDim.x) * STAGER_WARPS) {
+      const long long u0 = 2 * c;
+      const uint4* s[2];
+      uint4* d[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int g = peers.src_of[u0 + r];
+        const int owner = g >= 0 ? g / peers.T : 0;
+        s[r] = g >= 0 ? reinterpret_cast<const uint4*>(static_cast<const char*>(peers.src[owner]) +
+                                                       static_cast<long long>(g - owner * peers.T) * peers.src_ld * 2)
+                      : nullptr;
+        d[r] = reinterpret_cast<uint4*>(static_cast<char*>(peers.dst) + (u0 + r) * peers.ld * 2);
+      }
+      for (int c0 = 0; c0 < peers.row_vecs; c0 += 256) {
+        uint4 v[2][8];
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const int c = c0 + i * 32 + lane;
-            if (c < peers.row_vecs) v[i] = s[c];
+            const int cc = c0 + i * 32 + lane;
+            v[r][i] = (s[r] != nullptr && cc < peers.row_vecs) ? s[r][cc] : make_uint4(0, 0, 0, 0);
           }
 #pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const int c = c0 + i * 32 + lane;
-            if (c < peers.row_vecs) d[c] = v[i];
+            const int cc = c0 + i * 32 + lane;
+            if (cc < peers.row_vecs) d[r][cc] = v[r][i];
           }
-        }
-      } else {
-        for (int c = lane; c < peers.row_vecs; c += 32) d[c] = make_uint4(0, 0, 0, 0);
       }
       fence_proxy_async_all();
       __threadfence();
       __syncwarp();
-      if (lane == 0) atomicAdd(peers.flags + u / BLOCK_M, 1);
-      continue;
+      if (lane == 0) atomicAdd(peers.flags + u0 / BLOCK_M, 2);
     }
+    return;
+  }
+  int ready_blk = -1;
+  bool ok = true;
+  for (long long u = blockIdx.x * STAGER_WARPS + swarp; ok && u < total;
+       u += static_cast<long long>(gridDim.x) * STAGER_WARPS) {
     if (peers.push == 2) {
       // -------- expert-parallel combine transport: a finished row goes to the owner of its token
       const int blk = static_cast<int>(u / BLOCK_M);
@@ -995,6 +1072,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       mine.m0 = ti.m0 + static_cast<int>(rank) * 128;
       if constexpr (EPI == EPI_SWIGLU) {
         epilogue_swiglu(p, &tma_c, &tma_c2, es, taddr, mine, lane_group, lane);
+      } else if constexpr (EPI == EPI_SWIGLU_BWD) {
+        epilogue_swiglu_bwd(p, &tma_c, es, taddr, mine, lane_group, lane);
       } else {
         epilogue_plain<BLOCK_N>(p, &tma_c, es, taddr, mine, has_k, lane_group, lane);
       }
@@ -1231,6 +1310,14 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
         ((d->row_src_of != nullptr) != (d->row_weights != nullptr)) || ((d->row_src_of != nullptr) != (d->row_k_of != nullptr)))
       return -15;
     block_n = 256;
+  } else if (epi == OLB_EPI_SWIGLU_BWD) {
+    // C = d(gate) | d(up) [rows, 2 N]; the accumulator d(act) [rows, N] is not stored.  CTA-pair kernel only.
+    if (d->N % 256 || d->aux_in == nullptr || d->accumulate || d->out_fp32 || d->mode != OLB_GEMM_RAGGED_M ||
+        !d->pair_rows || d->M % 256 || d->a_mn_major || (d->aux_ld % 8) || d->blk_range != nullptr ||
+        (reinterpret_cast<uintptr_t>(d->aux_in) & 15) || !pair_kernel_enabled() ||
+        ((d->row_src_of != nullptr) != (d->row_weights != nullptr)) || ((d->row_src_of != nullptr) != (d->row_k_of != nullptr)))
+      return -16;
+    block_n = 256;
   } else if (block_n == 0) {
     if (d->mode != OLB_GEMM_DENSE) {
       block_n = (d->N % 256 == 0) ? 256 : (d->N % 128 == 0 ? 128 : 64);
@@ -1245,7 +1332,7 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   // (ragged-M: only when the caller padded the expert groups to 256 rows; the dense all-gather / reduce-scatter
   // variants, whose peers own multiples of 128 rows, stay on the single-CTA kernel)
   const bool pair_shape = d->block_n == 0 && block_n == 256 && d->blk_range == nullptr && d->M >= 256 && num_sms >= 2 &&
-                          (epi == OLB_EPI_SWIGLU || d->N % 256 == 0 || d->N >= 2048);
+                          (epi != OLB_EPI_PLAIN || d->N % 256 == 0 || d->N >= 2048);
   const bool use_pair = pair_kernel_enabled() && pair_shape &&
                         (d->mode == OLB_GEMM_RAGGED_M ? (d->pair_rows != 0 && d->M % 256 == 0)
                                                       : (d->n_peers == 0 && epi == OLB_EPI_PLAIN));
@@ -1320,6 +1407,9 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   p.row_weights = d->row_weights;
   p.row_topk = d->row_topk;
   p.pair_rows = d->pair_rows;
+  p.aux_in = d->aux_in;
+  p.aux_ld = d->aux_ld;
+  p.aux_out = d->aux_out;
 
   // Output through tensor-map stores whenever a 2D map describes it: no read-modify-write, and for the per-expert
   // weight gradients experts that tile exactly (a box must not run into the next expert's rows).
@@ -1329,6 +1419,10 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
   if (epi == OLB_EPI_SWIGLU) {
     rc = make_tmap_2d(&tm.c, d->C, 2ull * d->N, d->M, d->ldc * 2, 64, 32, false);
     if (!rc) rc = make_tmap_2d(&tm.c2, d->C2, d->N, d->M, d->ldc2 * 2, 64, 32, false);
+    if (rc) return rc;
+    p.c_tma = 1;
+  } else if (epi == OLB_EPI_SWIGLU_BWD) {
+    rc = make_tmap_2d(&tm.c, d->C, 2ull * d->N, d->M, d->ldc * 2, 64, 32, false);
     if (rc) return rc;
     p.c_tma = 1;
   } else if (!d->accumulate) {
@@ -1388,9 +1482,12 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
         peers.src_ld = d->a_src_ld;
         peers.row_vecs = d->K / 8;
       }
-      if (use_pair)
-        return epi == OLB_EPI_SWIGLU ? launch_pair<true, EPI_SWIGLU>(tm, peers, p, sms, stream)
-                                     : launch_pair<true, EPI_PLAIN>(tm, peers, p, sms, stream);
+      if (use_pair) {
+        if (epi == OLB_EPI_SWIGLU) return launch_pair<true, EPI_SWIGLU>(tm, peers, p, sms, stream);
+        if (epi == OLB_EPI_SWIGLU_BWD) return launch_pair<true, EPI_SWIGLU_BWD>(tm, peers, p, sms, stream);
+        return launch_pair<true, EPI_PLAIN>(tm, peers, p, sms, stream);
+      }
+      if (epi == OLB_EPI_SWIGLU_BWD) return -16;
       return dispatch<true>(block_n, epi, tm, peers, p, sms, stream);
     }
     if (epi != OLB_EPI_PLAIN) return -14;
@@ -1429,8 +1526,11 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
     return dispatch<true>(block_n, epi, tm, peers, p, sms, stream);
   }
   PeerArg<false> nopeers{};
-  if (use_pair)
-    return epi == OLB_EPI_SWIGLU ? launch_pair<false, EPI_SWIGLU>(tm, nopeers, p, sms, stream)
-                                 : launch_pair<false, EPI_PLAIN>(tm, nopeers, p, sms, stream);
+  if (use_pair) {
+    if (epi == OLB_EPI_SWIGLU) return launch_pair<false, EPI_SWIGLU>(tm, nopeers, p, sms, stream);
+    if (epi == OLB_EPI_SWIGLU_BWD) return launch_pair<false, EPI_SWIGLU_BWD>(tm, nopeers, p, sms, stream);
+    return launch_pair<false, EPI_PLAIN>(tm, nopeers, p, sms, stream);
+  }
+  if (epi == OLB_EPI_SWIGLU_BWD) return -16;
   return dispatch<false>(block_n, epi, tm, nopeers, p, sms, stream);
 }

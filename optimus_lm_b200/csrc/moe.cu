@@ -285,9 +285,33 @@ moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat
   }
 }
 
+// dweights[src_of[row], k_of[row]] = sum_j partial[row, j] in a fixed order: the routing-weight gradients from the
+// per-column-tile partials that the down projection's input-gradient launch left behind.
+__global__ void moe_scatter_dweights_kernel(const float* __restrict__ partial, int nblk, const int* __restrict__ src_of,
+                                            const int* __restrict__ k_of, const int* __restrict__ meta, int K,
+                                            float* __restrict__ out, int cap) {
+  const int nrows = min(meta[0] * 128, cap);
+  for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < nrows; row += gridDim.x * blockDim.x) {
+    const int t = src_of[row];
+    if (t < 0) continue;
+    float s = 0.f;
+    for (int j = 0; j < nblk; ++j) s += partial[static_cast<long long>(row) * nblk + j];
+    out[static_cast<long long>(t) * K + k_of[row]] = s;
+  }
+}
+
 }  // namespace olb
 
 using namespace olb;
+
+extern "C" int olb_moe_scatter_dweights(const float* partial, int nblk, const int* src_of, const int* k_of, const int* meta,
+                                        int K, float* out, int cap, cudaStream_t stream) {
+  if (cap <= 0 || nblk <= 0) return 0;
+  int grid = (cap + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  moe_scatter_dweights_kernel<<<grid, 256, 0, stream>>>(partial, nblk, src_of, k_of, meta, K, out, cap);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 extern "C" long long olb_moe_ws_ints(int T, int E_loc) {
   const long long nblocks = (T + IDX_THREADS - 1) / IDX_THREADS;

@@ -66,11 +66,55 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
-// dx = r * (dn - n * mean(dn * n)), dn = dy * w, n = x * r.  dw partial = sum_rows dy * n.
+// h = a + b (rounded to bf16, the residual stream) and y = rmsnorm(h) * w in one pass over the rows.
+__global__ void __launch_bounds__(NORM_THREADS)
+add_rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h, __nv_bfloat16* __restrict__ y,
+                       float* __restrict__ rstd, int rows, int cols, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * NORM_WARPS + warp;
+  if (row >= rows) return;
+  const __nv_bfloat16* ar = a + row * cols;
+  const __nv_bfloat16* br = b + row * cols;
+  __nv_bfloat16* hr = h + row * cols;
+  __nv_bfloat16* yr = y + row * cols;
+  float ss = 0.f;
+  for (int c = lane * 8; c < cols; c += 256) {
+    float fa[8], fb[8];
+    load8(ar + c, fa);
+    load8(br + c, fb);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      fa[i] = round_bf16(fa[i] + fb[i]);
+      ss += fa[i] * fa[i];
+    }
+    store8(hr + c, fa);
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / cols + eps);
+  if (lane == 0 && rstd) rstd[row] = r;
+  __syncwarp();
+  for (int c = lane * 8; c < cols; c += 256) {
+    float f[8], g[8];
+    load8(hr + c, f);  // this lane's own stores
+    if (w) load8(w + c, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float n = round_bf16(f[i] * r);
+      f[i] = w ? n * g[i] : n;
+    }
+    store8(yr + c, f);
+  }
+}
+
+// dx = r * (dn - n * mean(dn * n)) (+ dres), dn = dy * w, n = x * r.  dw partial = sum_rows dy * n.
+// `dres` (optional) is the gradient that reaches x along the residual path; adding it here saves the separate
+// accumulation pass.
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
-                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int cols) {
+                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int cols,
+                   const __nv_bfloat16* __restrict__ dres = nullptr) {
   extern __shared__ float s_dw[];  // [NORM_WARPS][cols] when dw_partial != NULL
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* my_dw = s_dw + static_cast<size_t>(warp) * cols;
@@ -109,6 +153,12 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
         const float dn = w ? fd[i] * fw[i] : fd[i];
         o[i] = r * (dn - n * dot);
       }
+      if (dres) {
+        float fr[8];
+        load8(dres + row * cols + c, fr);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = round_bf16(o[i]) + fr[i];  // the sum of two bf16 gradients, as autograd adds them
+      }
       store8(dx + row * cols + c, o);
     }
   }
@@ -130,7 +180,8 @@ template <int NCH>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                        const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
-                       __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows) {
+                       __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows,
+                       const __nv_bfloat16* __restrict__ dres = nullptr) {
   constexpr int cols = NCH * 256;
   __shared__ __align__(16) __nv_bfloat16 s_w[cols];
   __shared__ float s_dw[NORM_WARPS][cols + 8];
@@ -185,6 +236,15 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16
         const float n0 = fx.x * r, n1 = fx.y * r;
         const float d0 = w ? fd.x * fw.x : fd.x, d1 = w ? fd.y * fw.y : fd.y;
         o[i] = pack_bf16(r * (d0 - n0 * dot), r * (d1 - n1 * dot));
+      }
+      if (dres) {
+        const uint4 vr = *reinterpret_cast<const uint4*>(dres + row * cols + k * 256 + lane * 8);
+        const uint32_t ur[4] = {vr.x, vr.y, vr.z, vr.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 a = unpack_bf16(o[i]), b = unpack_bf16(ur[i]);
+          o[i] = pack_bf16(a.x + b.x, a.y + b.y);
+        }
       }
       *reinterpret_cast<uint4*>(dx + row * cols + k * 256 + lane * 8) = make_uint4(o[0], o[1], o[2], o[3]);
     }
@@ -310,12 +370,13 @@ static bool raise_bwd_smem_limit() {
 
 // Launch the register-resident backward when `cols` is one of its widths.  Returns false when it is not.
 static bool launch_bwd_reg(const __nv_bfloat16* pdy, const __nv_bfloat16* px, const __nv_bfloat16* pw, const float* rstd,
-                           __nv_bfloat16* pdx, float* dw_partial, int rows, int cols, int nb, cudaStream_t stream) {
+                           __nv_bfloat16* pdx, float* dw_partial, int rows, int cols, int nb, cudaStream_t stream,
+                           const __nv_bfloat16* dres = nullptr) {
   switch (cols) {
-    case 256: rmsnorm_bwd_reg_kernel<1><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); return true;
-    case 512: rmsnorm_bwd_reg_kernel<2><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); return true;
-    case 1024: rmsnorm_bwd_reg_kernel<4><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); return true;
-    case 2048: rmsnorm_bwd_reg_kernel<8><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows); return true;
+    case 256: rmsnorm_bwd_reg_kernel<1><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows, dres); return true;
+    case 512: rmsnorm_bwd_reg_kernel<2><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows, dres); return true;
+    case 1024: rmsnorm_bwd_reg_kernel<4><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows, dres); return true;
+    case 2048: rmsnorm_bwd_reg_kernel<8><<<nb, NORM_THREADS, 0, stream>>>(pdy, px, pw, rstd, pdx, dw_partial, rows, dres); return true;
     default: return false;
   }
 }
@@ -339,21 +400,36 @@ extern "C" int olb_rmsnorm_bwd_blocks(int rows) {
   return nb < 296 ? (nb < 1 ? 1 : nb) : 296;
 }
 
+extern "C" int olb_add_rmsnorm_fwd(const void* a, const void* b, const void* w, void* h, void* y, float* rstd, int rows,
+                                   int cols, float eps, cudaStream_t stream) {
+  if (cols % 8) return -1;
+  if (rows <= 0) return 0;
+  add_rmsnorm_fwd_kernel<<<(rows + NORM_WARPS - 1) / NORM_WARPS, NORM_THREADS, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), static_cast<const __nv_bfloat16*>(w),
+      static_cast<__nv_bfloat16*>(h), static_cast<__nv_bfloat16*>(y), rstd, rows, cols, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 extern "C" int olb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
                                float* dw_partial, int rows, int cols, cudaStream_t stream) {
+  return olb_rmsnorm_bwd_res(dy, x, w, rstd, dx, dw_partial, nullptr, rows, cols, stream);
+}
+
+extern "C" int olb_rmsnorm_bwd_res(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                                   float* dw_partial, const void* dres, int rows, int cols, cudaStream_t stream) {
   if (cols % 8) return -1;
   if (rows <= 0) return 0;
   const int nb = olb_rmsnorm_bwd_blocks(rows);
   if (launch_bwd_reg(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
                      static_cast<const __nv_bfloat16*>(w), rstd, static_cast<__nv_bfloat16*>(dx), dw_partial, rows, cols,
-                     nb, stream))
+                     nb, stream, static_cast<const __nv_bfloat16*>(dres)))
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   const size_t smem = dw_partial ? sizeof(float) * NORM_WARPS * cols : 0;
   if (smem > 200 * 1024) return -3;
   if (smem > 48 * 1024 && !raise_bwd_smem_limit()) return -4;
   rmsnorm_bwd_kernel<<<nb, NORM_THREADS, smem, stream>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
-      rstd, static_cast<__nv_bfloat16*>(dx), dw_partial, rows, cols);
+      rstd, static_cast<__nv_bfloat16*>(dx), dw_partial, rows, cols, static_cast<const __nv_bfloat16*>(dres));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -11,7 +11,7 @@ extern "C" {
 
 // ---------------------------------------------------------------- GEMM (gemm_tcgen05.cu)
 enum { OLB_GEMM_DENSE = 0, OLB_GEMM_RAGGED_M = 1, OLB_GEMM_RAGGED_K = 2 };
-enum { OLB_EPI_PLAIN = 0, OLB_EPI_SWIGLU = 1 };
+enum { OLB_EPI_PLAIN = 0, OLB_EPI_SWIGLU = 1, OLB_EPI_SWIGLU_BWD = 2 };
 
 typedef struct {
   const void* A;  // bf16. K-major: [a_rows, K] with row stride lda; MN-major: [a_rows (=K extent), M]
@@ -79,6 +79,13 @@ typedef struct {
   const int* row_k_of;
   const float* row_weights;
   int row_topk;
+  // Down projection's input gradient with the SwiGLU backward in the epilogue (epilogue == OLB_EPI_SWIGLU_BWD;
+  // RAGGED_M with pair_rows, N a multiple of 256): the product d(act) [M, N] stays in the accumulator; aux_in is the
+  // saved gate | up [M, 2 N] (row stride aux_ld), C receives d(gate) | d(up) [M, 2 N], and aux_out [M, N / 256] the
+  // per-row, per-column-tile partial of <d(act), silu(gate) * up> (the routing-weight gradient before its small sum).
+  const void* aux_in;
+  long long aux_ld;
+  float* aux_out;
 } olb_gemm_desc;
 
 int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream);
@@ -91,6 +98,12 @@ int olb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows
 int olb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_partial,
                     int rows, int cols, cudaStream_t stream);
 int olb_rmsnorm_bwd_blocks(int rows);
+// Residual add fused with the norm: h = a + b (bf16), y = rmsnorm(h) * w, rstd of h.
+int olb_add_rmsnorm_fwd(const void* a, const void* b, const void* w, void* h, void* y, float* rstd, int rows, int cols,
+                        float eps, cudaStream_t stream);
+// olb_rmsnorm_bwd with the residual path's gradient `dres` [rows, cols] (may be NULL) added to dx.
+int olb_rmsnorm_bwd_res(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_partial,
+                        const void* dres, int rows, int cols, cudaStream_t stream);
 // dw[cols] (bf16 or fp32 by dw_fp32) (+)= sum over `nparts` rows of dw_partial.
 int olb_colsum_finalize(const float* partial, int nparts, int cols, void* dw, int dw_fp32, int accumulate,
                         cudaStream_t stream);
@@ -161,6 +174,9 @@ int olb_router_sigmoid_bwd(const float* logits, const int* indices, const float*
 int olb_moe_build_index(const int* indices, int T, int K, int e_start, int E_loc, int cap, int row_pad, int* ws,
                         int* row_of, int* src_of, int* k_of, int* meta, int* offsets, int* counts, int* status,
                         cudaStream_t stream);
+// out[src_of[row] * K + k_of[row]] = sum_j partial[row * nblk + j] for the routed rows below meta[0] * 128 (fixed order).
+int olb_moe_scatter_dweights(const float* partial, int nblk, const int* src_of, const int* k_of, const int* meta, int K,
+                             float* out, int cap, cudaStream_t stream);
 long long olb_moe_ws_ints(int T, int E_loc);
 // out[row,:] = src_of[row] >= 0 ? x[src_of[row],:] : 0   for row < meta[0]*128   (bf16, cols % 8 == 0)
 int olb_moe_gather_rows(const void* x, const int* src_of, const int* meta, void* out, int cap, int cols,

@@ -20,6 +20,10 @@ class RMSNorm(nn.Module):
     def forward(self, hidden_states):
         return OF.rms_norm(hidden_states, self.weight, self.variance_epsilon)
 
+    def forward_add(self, hidden_states, residual):
+        """``(hidden_states + residual, norm(hidden_states + residual))`` in one kernel."""
+        return OF.add_rms_norm(hidden_states, residual, self.weight, self.variance_epsilon)
+
     def extra_repr(self):
         return f"{tuple(self.weight.shape)}, eps={self.variance_epsilon}"
 

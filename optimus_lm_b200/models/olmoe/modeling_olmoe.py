@@ -103,20 +103,33 @@ class OlmoeParallelDecoderLayer(nn.Module):
             return torch_activation_checkpoint(fn, *args, use_reentrant=False)
         return fn(*args)
 
-    def forward(self, hidden_states, position_embeddings):
+    def forward(self, hidden_states, position_embeddings, residual=None, defer_add=False):
+        """One decoder layer.  With ``defer_add`` the layer returns ``(mlp_out, residual, router_logits)`` without the
+        last residual add, and accepts such a pair as input: every residual add then runs inside the RMSNorm kernel
+        that follows it (the next layer's input norm, or the model's final norm)."""
         self._log("Before Decoder")
-        residual = hidden_states
-        h = self._maybe_ckpt(self.ckpt_norm, self.input_layernorm, hidden_states)
+        fused = defer_add and not self.ckpt_norm
+        if residual is None:
+            residual = hidden_states
+            h = self._maybe_ckpt(self.ckpt_norm, self.input_layernorm, hidden_states)
+        elif fused:
+            residual, h = self.input_layernorm.forward_add(hidden_states, residual)
+        else:
+            residual = hidden_states + residual
+            h = self._maybe_ckpt(self.ckpt_norm, self.input_layernorm, residual)
         self._log("Before Attention")
         h = self._maybe_ckpt(self.ckpt_attn, self.self_attn, h, position_embeddings)
         self._log("After Attention")
-        hidden_states = h + residual
-
-        residual = hidden_states
-        h = self._maybe_ckpt(self.ckpt_norm, self.post_attention_layernorm, hidden_states)
+        if fused:
+            residual, h = self.post_attention_layernorm.forward_add(h, residual)
+        else:
+            residual = h + residual
+            h = self._maybe_ckpt(self.ckpt_norm, self.post_attention_layernorm, residual)
         self._log("Before MoE")
         h, router_logits = self.mlp(h)
         self._log("After MoE")
+        if defer_add:
+            return h, residual, router_logits
         hidden_states = h + residual
         self._log("After decoder")
         return hidden_states, router_logits
@@ -181,9 +194,15 @@ class OlmoeParallelModel(nn.Module):
             LV = self.num_layers_per_virtual_stage
             layers = self.layers[vp_ind * LV:(vp_ind + 1) * LV]
         router_logits = []
+        residual = None
         for layer in layers:
-            hidden_states, rl = layer(hidden_states, position_embeddings)
+            hidden_states, residual, rl = layer(hidden_states, position_embeddings, residual, defer_add=True)
             router_logits.append(rl)
+        if last_chunk and isinstance(self.norm, RMSNorm) and residual is not None and not self.ckpt_norm:
+            _, hidden_states = self.norm.forward_add(hidden_states, residual)   # last residual add inside the final norm
+            return hidden_states, tuple(router_logits)
+        if residual is not None:
+            hidden_states = hidden_states + residual
         if last_chunk:
             if self.ckpt_norm and torch.is_grad_enabled():
                 hidden_states = torch_activation_checkpoint(self.norm, hidden_states, use_reentrant=False)

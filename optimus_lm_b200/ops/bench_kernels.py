@@ -76,6 +76,28 @@ def bench_grouped():
     print(f"grouped dgrad: {t:.3f} ms ({fl / t * 1e-9:.0f} TFLOP/s)", flush=True)
     t = _time(lambda: OF.grouped_linear_wgrad(dy, xp, ix, I, H), flush=flush)
     print(f"grouped wgrad: {t:.3f} ms ({fl / t * 1e-9:.0f} TFLOP/s)", flush=True)
+    # the fused launches of the MoE layer, with and without the in-kernel row gather
+    from ._ext import extension
+    C = extension()
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    tw = torch.rand(T, K, device="cuda")
+    wu = (torch.randn(E, I, H, device="cuda") * 0.02).to(torch.bfloat16)
+    wd = (torch.randn(E, H, I, device="cuda") * 0.02).to(torch.bfloat16)
+    h = torch.empty(cap, 2 * I, device="cuda", dtype=torch.bfloat16)
+    act = torch.empty(cap, I, device="cuda", dtype=torch.bfloat16)
+    st = OF.status_word("cuda")
+    t = _time(lambda: C.gemm_gateup_swiglu(xp, w.view(E * I, H), wu.view(E * I, H), h, act, cap, I, H, ix.meta, ix.src_of,
+                                           ix.k_of, tw, E, [], 0, 0, None, st, ix.pair), flush=flush)
+    print(f"gate|up + SwiGLU epilogue, operand in place: {t:.3f} ms ({2 * fl / t * 1e-9:.0f} TFLOP/s)", flush=True)
+    t = _time(lambda: OF.grouped_gateup_swiglu([x.data_ptr()], H, T, tw, w, wu, ix), flush=flush)
+    print(f"gate|up + SwiGLU epilogue + row gather     : {t:.3f} ms ({2 * fl / t * 1e-9:.0f} TFLOP/s)", flush=True)
+    dout = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    t = _time(lambda: OF.grouped_gather_dgrad([dout.data_ptr()], H, T, wd, ix), flush=flush)
+    print(f"down dgrad + row gather                    : {t:.3f} ms ({fl / t * 1e-9:.0f} TFLOP/s)", flush=True)
+    dw = torch.zeros(T, K, device="cuda")
+    t = _time(lambda: OF.grouped_down_dgrad_swiglu_bwd([dout.data_ptr()], H, T, wd, h, tw, ix, dw), flush=flush)
+    print(f"down dgrad + row gather + SwiGLU backward  : {t:.3f} ms ({fl / t * 1e-9:.0f} TFLOP/s)", flush=True)
+    assert OF.check_status("cuda") == 0
 
 
 def bench_attention():
@@ -103,7 +125,7 @@ def bench_attention():
 def profile_case(name: str, launches: int = 4):
     """A few launches of ONE kernel on operands larger than L2 and well under a GB each: the case to
     put under a hardware profiler (``profile-gemm``, ``profile-grouped``, ``profile-attention``,
-    ``profile-attention-bwd``, ``profile-ep``, ``profile-gemm-allgather``, ``profile-gemm-push``, ``profile-rs-adamw``,
+    ``profile-attention-bwd``, ``profile-gateup``, ``profile-gateup-nogather``, ``profile-dgrad-gather``, ``profile-ep``, ``profile-gemm-allgather``, ``profile-gemm-push``, ``profile-rs-adamw``,
     ``profile-rmsnorm-bwd``)."""
     torch.manual_seed(0)
     if name == "gemm":
@@ -120,6 +142,28 @@ def profile_case(name: str, launches: int = 4):
         w = (torch.randn(E, I, H, device="cuda") * 0.02).to(torch.bfloat16)
         y = torch.empty(ix.cap, I, device="cuda", dtype=torch.bfloat16)
         fn = lambda: OF.grouped_linear_fwd(xp, w, ix, out=y)
+    elif name in ("gateup", "gateup-nogather", "dgrad-gather"):
+        # the fused launches of the MoE layer on half of the model's token count (operands ~1.5 GB in total)
+        from ._ext import extension
+        T, E, K, H, I = 8192, 64, 8, 2048, 1024
+        idx = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(T)]).to(torch.int32)
+        ix = OF.MoEIndex(idx, 0, E, OF.moe_capacity_rows(T, K, E))
+        x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+        tw = torch.rand(T, K, device="cuda")
+        wg = (torch.randn(E, I, H, device="cuda") * 0.02).to(torch.bfloat16)
+        wu = (torch.randn(E, I, H, device="cuda") * 0.02).to(torch.bfloat16)
+        wd = (torch.randn(E, H, I, device="cuda") * 0.02).to(torch.bfloat16)
+        if name == "gateup":
+            fn = lambda: OF.grouped_gateup_swiglu([x.data_ptr()], H, T, tw, wg, wu, ix)
+        elif name == "gateup-nogather":
+            xp = torch.randn(ix.rows, H, device="cuda").to(torch.bfloat16)
+            h = torch.empty(ix.rows, 2 * I, device="cuda", dtype=torch.bfloat16)
+            act = torch.empty(ix.rows, I, device="cuda", dtype=torch.bfloat16)
+            st = OF.status_word("cuda")
+            fn = lambda: extension().gemm_gateup_swiglu(xp, wg.view(E * I, H), wu.view(E * I, H), h, act, ix.rows, I, H,
+                                                        ix.meta, ix.src_of, ix.k_of, tw, E, [], 0, 0, None, st, ix.pair)
+        else:
+            fn = lambda: OF.grouped_gather_dgrad([x.data_ptr()], H, T, wd, ix)
     elif name == "attention":
         q, k, v = (torch.randn(4, 4096, 16, 128, device="cuda").to(torch.bfloat16) for _ in range(3))
         fn = lambda: OA.flash_attention(q, k, v)

@@ -14,6 +14,7 @@ so no transposed copies are ever materialised.
 from __future__ import annotations
 
 import math
+import os
 from typing import List, Optional, Sequence, Tuple
 
 import torch
@@ -268,6 +269,54 @@ def rms_norm(x, weight, eps=1e-5):
     if _kernel_ok(x, weight) and x.shape[-1] % 8 == 0:
         return _RMSNormFn.apply(x, weight, eps)
     return rms_norm_reference(x, weight, eps)
+
+
+class _AddRMSNormFn(torch.autograd.Function):
+    """``h = x + residual`` and ``y = rms_norm(h, w)`` in one kernel; the backward takes the gradients of both outputs and
+    returns their combination once: ``d(h) = rmsnorm_bwd(dy) + dh`` is the gradient of ``x`` and of ``residual``."""
+
+    @staticmethod
+    def forward(ctx, x, residual, w, eps):
+        C = extension()
+        xc, rc = x.contiguous(), residual.contiguous()
+        h = torch.empty_like(xc)
+        y = torch.empty_like(xc)
+        rstd = torch.empty(xc.numel() // xc.shape[-1], dtype=torch.float32, device=x.device)
+        C.add_rmsnorm_fwd(xc, rc, w, h, y, rstd, eps)
+        ctx.save_for_backward(h, w, rstd)
+        ctx.set_materialize_grads(False)
+        return h, y
+
+    @staticmethod
+    def backward(ctx, dh, dy):
+        C = extension()
+        h, w, rstd = ctx.saved_tensors
+        if dy is None:
+            return dh, dh, None, None
+        dy = dy.contiguous()
+        dres = dh.contiguous() if dh is not None else None
+        dx = torch.empty_like(h)
+        rows, cols = rstd.numel(), h.shape[-1]
+        dw = None
+        if w is not None and ctx.needs_input_grad[2]:
+            nb = C.rmsnorm_bwd_blocks(rows)
+            partial = torch.empty((nb, cols), dtype=torch.float32, device=h.device)
+            C.rmsnorm_bwd(dy, h, w, rstd, dx, partial, dres)
+            dw = torch.empty_like(w)
+            C.colsum_finalize(partial, nb, dw, False)
+        else:
+            C.rmsnorm_bwd(dy, h, w, rstd, dx, None, dres)
+        return dx, dx, dw, None
+
+
+def add_rms_norm(x, residual, weight, eps=1e-5):
+    """``(x + residual, rms_norm(x + residual, weight))``: the residual add of a decoder layer fused with the norm that
+    follows it (the reference does ``hidden = h + residual`` and the next RMSNorm as separate ops,
+    optimus/models/olmoe/modeling_olmoe.py:436-450)."""
+    if _kernel_ok(x, residual, weight) and x.shape[-1] % 8 == 0 and x.shape == residual.shape:
+        return _AddRMSNormFn.apply(x, residual, weight, eps)
+    h = x + residual
+    return h, rms_norm_reference(h, weight, eps)
 
 
 def layer_norm_noaffine_reference(x, eps=1e-5):
@@ -721,10 +770,22 @@ def grouped_gateup_swiglu(x_ptrs, x_ld: int, tokens: int, weights, wg, wu, index
         grouped_linear_fwd(xp, wu, index, out=h[:, I:])
         C.swiglu_rowscale_fwd(h[:, :I], h[:, I:], index.src_of, index.k_of, weights, index.meta, act)
         return xp, h, act
+    if len(x_ptrs) == 1 and not _GATHER_IN_KERNEL_LOCAL:
+        # every token is in this GPU's memory: nothing crosses NVLink that the GEMM could hide, and the gather's traffic
+        # through the L2 slows the tiles down by as much as it takes on its own (measured: 1.14 ms fused against
+        # 0.15 + 0.88 ms); the permutation runs as its own kernel and the GEMM reads the operand in place
+        C.ep_gather_rows(list(x_ptrs), tokens, index.src_of, index.meta, xp, None)
+        C.gemm_gateup_swiglu(xp, wg.view(E * I, H), wu.view(E * I, H), h, act, rows, I, H, index.meta, index.src_of,
+                             index.k_of, weights, E, [], 0, 0, None, status_word(dev), index.pair)
+        return xp, h, act
     C.gemm_gateup_swiglu(xp, wg.view(E * I, H), wu.view(E * I, H), h, act, rows, I, H, index.meta, index.src_of,
                          index.k_of, weights, E, list(x_ptrs), x_ld, tokens, stage_flags(dev, rows), status_word(dev),
                          index.pair)
     return xp, h, act
+
+
+_GATHER_IN_KERNEL_LOCAL = os.environ.get("OLB_GATHER_IN_KERNEL", "0") == "1"   # also gather local rows inside the GEMM
+_FUSE_SWIGLU_BWD = os.environ.get("OLB_FUSE_SWIGLU_BWD", "0") == "1"            # SwiGLU backward in the dgrad epilogue
 
 
 def grouped_gather_dgrad(y_ptrs, y_ld: int, tokens: int, w, index: MoEIndex):
@@ -736,9 +797,41 @@ def grouped_gather_dgrad(y_ptrs, y_ld: int, tokens: int, w, index: MoEIndex):
     rows = index.rows
     dyp = torch.empty((rows, H), dtype=w.dtype, device=dev)
     dact = torch.empty((rows, I), dtype=w.dtype, device=dev)
+    if len(y_ptrs) == 1 and not _GATHER_IN_KERNEL_LOCAL:
+        C.ep_gather_rows(list(y_ptrs), tokens, index.src_of, index.meta, dyp, None)
+        grouped_linear_dgrad(dyp, w, index, out=dact)
+        return dyp, dact
     C.gemm_ep_gather(dyp, w.view(E * H, I), dact, rows, I, H, True, index.meta, index.src_of, H, E, list(y_ptrs), y_ld,
                      tokens, stage_flags(dev, rows), status_word(dev), index.pair)
     return dyp, dact
+
+
+def grouped_down_dgrad_swiglu_bwd(y_ptrs, y_ld: int, tokens: int, w, h, weights, index: MoEIndex, dweights_out):
+    """Backward of ``act -> y`` and of the routing-weighted SwiGLU in one launch: the output gradients are gathered
+    (``dyp[u] = dout[src_of[u]]``) by extra warps, ``d(act) = dyp @ w[e]`` stays in the accumulator, and the epilogue
+    turns it into ``d(gate) | d(up)`` with the saved ``h = gate | up`` and the routing weights.  The routing-weight
+    gradients ``<d(act), silu(gate) * up>`` are written to ``dweights_out [tokens_total, K]`` (rows of pairs that are
+    not local stay untouched).  Returns ``(dyp, dh)``."""
+    C = extension()
+    E, H, I = w.shape
+    dev = w.device
+    rows = index.rows
+    dh = torch.empty_like(h)
+    if not (_FUSE_SWIGLU_BWD and index.pair and I % 256 == 0 and rows % 256 == 0
+            and os.environ.get("OLB_GEMM_PAIR", "1") != "0"):
+        # default: the product is stored and a separate kernel does the activation's backward.  The fused epilogue
+        # (OLB_FUSE_SWIGLU_BWD=1) reads the saved gate | up with one row per lane, which thrashes the small L1 that is
+        # left beside 224 KB of shared memory: 1.07 ms against 0.55 + 0.28 ms for the two kernels.
+        dyp, dact = grouped_gather_dgrad(y_ptrs, y_ld, tokens, w, index)
+        C.swiglu_rowscale_bwd(dact, h[:, :I], h[:, I:], index.src_of, index.k_of, weights, index.meta, dh[:, :I],
+                              dh[:, I:], dweights_out)
+        return dyp, dh
+    dyp = torch.empty((rows, H), dtype=w.dtype, device=dev)
+    partial = torch.empty((rows, I // 256), dtype=torch.float32, device=dev)
+    C.gemm_ep_gather(dyp, w.view(E * H, I), dh, rows, I, H, True, index.meta, index.src_of, H, E, list(y_ptrs), y_ld,
+                     tokens, stage_flags(dev, rows), status_word(dev), index.pair, h, index.k_of, weights, partial)
+    C.moe_scatter_dweights(partial, index.src_of, index.k_of, index.meta, dweights_out)
+    return dyp, dh
 
 
 class _MoEExpertsFn(torch.autograd.Function):
@@ -772,16 +865,13 @@ class _MoEExpertsFn(torch.autograd.Function):
         index = ctx.index
         T, H, I, E_loc = ctx.dims
         dout = dout.contiguous()
-        # d(y) = gather of dout (the combine was an unweighted sum), inside the down projection's input-gradient launch
-        dyp, dact = grouped_gather_dgrad([dout.data_ptr()], H, T, wd, index)
+        # d(y) = gather of dout (the combine was an unweighted sum), d(act) = d(y) wd and the activation's backward:
+        # one launch
+        dtopk = torch.zeros_like(topk_w)
+        dyp, dh = grouped_down_dgrad_swiglu_bwd([dout.data_ptr()], H, T, wd, h, topk_w, index, dtopk)
         hg, hu, hd = ctx.holders
         dwd = grouped_linear_wgrad(dyp, act, index, H, I, hd) if ctx.needs_input_grad[5] else None
         del dyp
-        dh = torch.empty_like(h)
-        dtopk = torch.zeros_like(topk_w)
-        C.swiglu_rowscale_bwd(dact, h[:, :I], h[:, I:], index.src_of, index.k_of, topk_w, index.meta, dh[:, :I],
-                              dh[:, I:], dtopk)
-        del dact
         dwg = grouped_linear_wgrad(dh[:, :I], xp, index, I, H, hg) if ctx.needs_input_grad[3] else None
         dwu = grouped_linear_wgrad(dh[:, I:], xp, index, I, H, hu) if ctx.needs_input_grad[4] else None
         dxp = grouped_linear_dgrad_pair(dh, wg, wu, index)

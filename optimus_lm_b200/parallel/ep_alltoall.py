@@ -98,13 +98,10 @@ class _FusedEPMoEFn(torch.autograd.Function):
         hg, hu, hd = ctx.holders
         # Critical path first: the input-gradient chain up to the rows that go back to the tokens' owners.
         # dispatch of the output gradients inside the down projection's input-gradient launch
-        dyp, dact = OF.grouped_gather_dgrad(ds.ptrs, H, T, wd, index)
-        dh = torch.empty_like(h)
+        # ... with the activation's backward in its epilogue (d(act) never goes to memory)
         dwt = sg.named("ep_dw", (n * T, K), torch.float32)
         dwt.local.zero_()
-        C.swiglu_rowscale_bwd(dact, h[:, :I], h[:, I:], index.src_of, index.k_of, w_all, index.meta, dh[:, :I],
-                              dh[:, I:], dwt.local)
-        del dact
+        dyp, dh = OF.grouped_down_dgrad_swiglu_bwd(ds.ptrs, H, T, wd, h, w_all, index, dwt.local)
         # input gradient of gate and up in one K-concatenated launch that also sends every finished row to slot
         # [token, k] of the token owner's receive buffer
         dxp = torch.empty((rows, H), dtype=dout.dtype, device=dout.device)

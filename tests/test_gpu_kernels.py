@@ -273,10 +273,11 @@ def test_grouped_gemm_with_fused_combine_push(n, T, E_loc, K, H, I):
 
 
 @pytest.mark.parametrize("n,T,E_loc,K,H,I", [(1, 700, 8, 2, 256, 512), (2, 256, 4, 2, 256, 128), (4, 512, 8, 4, 512, 256)])
-def test_gateup_swiglu_launch_with_fused_dispatch(n, T, E_loc, K, H, I):
+def test_gateup_swiglu_launch_with_fused_dispatch(n, T, E_loc, K, H, I, monkeypatch):
     """One launch = gather of the routed rows (from n token buffers standing in this GPU's memory) + gate and up
     projections + routing-weighted SwiGLU.  Checked bit for bit against the separate kernels, and element-wise against
     fp32 torch."""
+    monkeypatch.setattr(OF, "_GATHER_IN_KERNEL_LOCAL", True)   # the in-kernel gather also with a single token buffer
     E = n * E_loc
     e_start = E_loc if n > 1 else 0
     g = torch.Generator(device="cuda").manual_seed(5)
@@ -346,6 +347,36 @@ def test_down_dgrad_launch_with_fused_gather(n, T, E_loc, K, H, I):
                            torch.zeros((), dtype=torch.bfloat16, device="cuda"))
     assert torch.equal(dyp[:used], want_dyp)
     assert torch.equal(dact[:used], OF.grouped_linear_dgrad(dyp, wd, ix)[:used])
+
+
+@pytest.mark.parametrize("n,T,E_loc,K,H,I", [(1, 700, 8, 2, 256, 512), (4, 512, 8, 4, 512, 256)])
+def test_down_dgrad_launch_with_swiglu_backward_epilogue(n, T, E_loc, K, H, I, monkeypatch):
+    """Gather + d(act) = d(y) wd + SwiGLU backward in one launch against the three separate kernels."""
+    from optimus_lm_b200.ops import extension
+    C = extension()
+    monkeypatch.setattr(OF, "_FUSE_SWIGLU_BWD", True)          # the fused epilogue is opt-in
+    monkeypatch.setattr(OF, "_GATHER_IN_KERNEL_LOCAL", True)   # also with a single token buffer
+    E = n * E_loc
+    e_start = E_loc if n > 1 else 0
+    g = torch.Generator(device="cuda").manual_seed(7)
+    idx_all = torch.stack([torch.randperm(E, device="cuda", generator=g)[:K] for _ in range(n * T)]).to(torch.int32)
+    w_all = torch.rand(n * T, K, device="cuda", generator=g)
+    ds = [bf(T, H, seed=50 + r) for r in range(n)]
+    wd = bf(E_loc, H, I, seed=4, scale=0.05)
+    ix = OF.MoEIndex(idx_all, e_start, E_loc, OF.moe_capacity_rows(n * T, K, E_loc))
+    h = bf(ix.rows, 2 * I, seed=77)
+    dw = torch.zeros(n * T, K, device="cuda")
+    dyp, dh = OF.grouped_down_dgrad_swiglu_bwd([t.data_ptr() for t in ds], H, T, wd, h, w_all, ix, dw)
+    used = int(ix.meta[0].item()) * 128
+    dyp2, dact = OF.grouped_gather_dgrad([t.data_ptr() for t in ds], H, T, wd, ix)
+    dh2 = torch.empty_like(h)
+    dw2 = torch.zeros_like(dw)
+    C.swiglu_rowscale_bwd(dact, h[:, :I], h[:, I:], ix.src_of, ix.k_of, w_all, ix.meta, dh2[:, :I], dh2[:, I:], dw2)
+    assert torch.equal(dyp[:used], dyp2[:used])
+    assert rel_err(dh[:used], dh2[:used]) < 2e-3
+    assert (dh[:used].float() - dh2[:used].float()).abs().max().item() <= 1e-2 * dh2[:used].float().abs().max().item() + 1e-6
+    assert rel_err(dw, dw2) < 1e-3
+    assert (dw - dw2).abs().max().item() <= 1e-3 * dw2.abs().max().item() + 1e-6
 
 
 def test_gate_up_dgrad_launch_with_fused_combine_push():
