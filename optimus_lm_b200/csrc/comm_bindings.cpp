@@ -399,7 +399,7 @@ int64_t rs_adamw_blocks(int64_t n) { return olb_rs_adamw_blocks(n); }
 void rs_adamw(const std::vector<int64_t>& peer_grad, const std::vector<int64_t>& peer_param, int64_t shard_off,
               at::Tensor& master, at::Tensor& m, at::Tensor& v, double lr, double beta1, double beta2, double eps,
               double weight_decay, int64_t step, double grad_scale, const c10::optional<at::Tensor>& clip_coef,
-              at::Tensor& norm_partial, int64_t mode, bool skip_weight_update) {
+              at::Tensor& norm_partial, int64_t mode, bool skip_weight_update, int64_t mc_grad, int64_t mc_param) {
   c10::cuda::CUDAGuard guard(master.device());
   olb_adamw_hparams hp;
   hp.lr = static_cast<float>(lr);
@@ -414,10 +414,11 @@ void rs_adamw(const std::vector<int64_t>& peer_grad, const std::vector<int64_t>&
   auto pg = cptrs(peer_grad);
   auto pp = mptrs(peer_param);
   TORCH_CHECK(norm_partial.numel() >= olb_rs_adamw_blocks(master.numel()), "norm_partial too small");
-  check(olb_rs_adamw(pg.data(), pp.data(), static_cast<int>(pg.size()), shard_off, master.numel(),
-                     master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), &hp,
-                     clip_coef.has_value() ? clip_coef->data_ptr<float>() : nullptr, norm_partial.data_ptr<float>(),
-                     static_cast<int>(mode), cur_stream()),
+  check(olb_rs_adamw_mc(pg.data(), pp.data(), static_cast<int>(pg.size()), shard_off, master.numel(),
+                        master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), &hp,
+                        clip_coef.has_value() ? clip_coef->data_ptr<float>() : nullptr, norm_partial.data_ptr<float>(),
+                        static_cast<int>(mode), reinterpret_cast<const void*>(static_cast<uintptr_t>(mc_grad)),
+                        reinterpret_cast<void*>(static_cast<uintptr_t>(mc_param)), cur_stream()),
         "olb_rs_adamw");
 }
 
@@ -451,5 +452,8 @@ void register_comm(pybind11::module& m) {
         py::arg("status"), py::arg("pair_rows") = false, py::arg("h") = py::none(), py::arg("k_of") = py::none(),
         py::arg("weights") = py::none(), py::arg("dw_partial") = py::none());
   m.def("rs_adamw_blocks", &rs_adamw_blocks);
-  m.def("rs_adamw", &rs_adamw);
+  m.def("rs_adamw", &rs_adamw, py::arg("peer_grad"), py::arg("peer_param"), py::arg("shard_off"), py::arg("master"),
+        py::arg("m"), py::arg("v"), py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"),
+        py::arg("weight_decay"), py::arg("step"), py::arg("grad_scale"), py::arg("clip_coef"), py::arg("norm_partial"),
+        py::arg("mode"), py::arg("skip_weight_update"), py::arg("mc_grad") = 0, py::arg("mc_param") = 0);
 }

@@ -13,7 +13,9 @@
 //                         fp32 (the reference reduce-scatters a [EP*T, H] buffer,
 //                         optimus/models/olmoe/modeling_olmoe.py:338-341).
 //   ep_pull_dweights    : routing-weight gradients back to the tokens' rank.
-//   rs_adamw            : gradient reduce-scatter fused with the bf16->fp32 cast, the 1/N scaling,
+//   rs_adamw            : (plain peer loads / stores, or multimem.ld_reduce / multimem.st through the NVSwitch when the
+//                         buffers have a multicast address)
+//                         gradient reduce-scatter fused with the bf16->fp32 cast, the 1/N scaling,
 //                         the gradient-norm partial, the sharded AdamW update and the parameter
 //                         all-gather (updated bf16 parameters are stored into every peer's flat
 //                         parameter buffer).  Replaces reduce_scatter_tensor + ~12 elementwise
@@ -257,10 +259,30 @@ pull_reduce_rows_kernel(PeerPtrs peer_partial, int n, long long row0, int rows, 
 // gradient; mode 1: update (+ norm partial).
 constexpr long long RS_ELEMS_PER_BLOCK = 1 << 15;
 
+// NVLS forms (MC): `mc_grad` / `mc_param` are the buffers' multicast addresses (the same offsets reach every rank's
+// copy through the NVSwitch).  One multimem.ld_reduce returns the sum over all ranks of eight bf16 gradients
+// (fp32 accumulation in the switch, rounded to bf16 as a bf16 reduce-scatter would), one multimem.st delivers the
+// eight updated parameters to every rank: 16 bytes cross this GPU's links once per direction instead of n - 1 times.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(mc_addr)
+               : "memory");
+  return r;
+}
+__device__ __forceinline__ void multimem_st_bf16x8(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+template <bool MC>
 __global__ void __launch_bounds__(256)
 rs_adamw_kernel(PeerPtrs peer_grad, PeerPtrsMut peer_param, int n, long long shard_off, long long n_elems,
                 float* __restrict__ master, float* __restrict__ m, float* __restrict__ v, olb_adamw_hparams hp,
-                const float* __restrict__ clip_coef_dev, float* __restrict__ norm_partial, int mode) {
+                const float* __restrict__ clip_coef_dev, float* __restrict__ norm_partial, int mode,
+                const __nv_bfloat16* mc_grad, __nv_bfloat16* mc_param) {
   __shared__ float s_red[8];
   const long long begin = static_cast<long long>(blockIdx.x) * RS_ELEMS_PER_BLOCK;
   const long long end = min(begin + RS_ELEMS_PER_BLOCK, n_elems);
@@ -270,15 +292,24 @@ rs_adamw_kernel(PeerPtrs peer_grad, PeerPtrsMut peer_param, int n, long long sha
   float sq = 0.f;
   for (long long i = begin + threadIdx.x * 8; i < end; i += 256 * 8) {
     float g[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) g[k] = 0.f;
-    for (int p = 0; p < n; ++p) {
-      const uint4 t = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(peer_grad.p[p]) + shard_off + i);
+    if constexpr (MC) {
+      const uint4 t = multimem_ld_reduce_bf16x8(mc_grad + shard_off + i);
       float2 a;
-      a = unpack_bf16(t.x); g[0] += a.x; g[1] += a.y;
-      a = unpack_bf16(t.y); g[2] += a.x; g[3] += a.y;
-      a = unpack_bf16(t.z); g[4] += a.x; g[5] += a.y;
-      a = unpack_bf16(t.w); g[6] += a.x; g[7] += a.y;
+      a = unpack_bf16(t.x); g[0] = a.x; g[1] = a.y;
+      a = unpack_bf16(t.y); g[2] = a.x; g[3] = a.y;
+      a = unpack_bf16(t.z); g[4] = a.x; g[5] = a.y;
+      a = unpack_bf16(t.w); g[6] = a.x; g[7] = a.y;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) g[k] = 0.f;
+      for (int p = 0; p < n; ++p) {
+        const uint4 t = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(peer_grad.p[p]) + shard_off + i);
+        float2 a;
+        a = unpack_bf16(t.x); g[0] += a.x; g[1] += a.y;
+        a = unpack_bf16(t.y); g[2] += a.x; g[3] += a.y;
+        a = unpack_bf16(t.z); g[4] += a.x; g[5] += a.y;
+        a = unpack_bf16(t.w); g[6] += a.x; g[7] += a.y;
+      }
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
@@ -314,8 +345,12 @@ rs_adamw_kernel(PeerPtrs peer_grad, PeerPtrsMut peer_param, int n, long long sha
     o.y = pack_bf16(pp[2], pp[3]);
     o.z = pack_bf16(pp[4], pp[5]);
     o.w = pack_bf16(pp[6], pp[7]);
-    for (int p = 0; p < n; ++p)
-      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(peer_param.p[p]) + shard_off + i) = o;
+    if constexpr (MC) {
+      multimem_st_bf16x8(mc_param + shard_off + i, o);
+    } else {
+      for (int p = 0; p < n; ++p)
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(peer_param.p[p]) + shard_off + i) = o;
+    }
   }
   // deterministic block reduction of the norm partial
   sq = warp_sum(sq);
@@ -446,10 +481,25 @@ extern "C" int olb_rs_adamw_blocks(long long n_elems) {
 extern "C" int olb_rs_adamw(const void* const* peer_grad, void* const* peer_param, int n, long long shard_off,
                             long long n_elems, float* master, float* m, float* v, const olb_adamw_hparams* hp,
                             const float* clip_coef_dev, float* norm_partial, int mode, cudaStream_t stream) {
+  return olb_rs_adamw_mc(peer_grad, peer_param, n, shard_off, n_elems, master, m, v, hp, clip_coef_dev, norm_partial, mode,
+                         nullptr, nullptr, stream);
+}
+
+extern "C" int olb_rs_adamw_mc(const void* const* peer_grad, void* const* peer_param, int n, long long shard_off,
+                               long long n_elems, float* master, float* m, float* v, const olb_adamw_hparams* hp,
+                               const float* clip_coef_dev, float* norm_partial, int mode, const void* mc_grad,
+                               void* mc_param, cudaStream_t stream) {
   if (n > MAX_PEERS || (n_elems % 8) || (shard_off % 8)) return -1;
+  if ((mc_grad == nullptr) != (mc_param == nullptr)) return -1;
+  if ((reinterpret_cast<uintptr_t>(mc_grad) | reinterpret_cast<uintptr_t>(mc_param)) & 15) return -1;
   if (n_elems <= 0) return 0;
-  rs_adamw_kernel<<<olb_rs_adamw_blocks(n_elems), 256, 0, stream>>>(to_peers(peer_grad, n), to_peers_mut(peer_param, n),
-                                                                    n, shard_off, n_elems, master, m, v, *hp,
-                                                                    clip_coef_dev, norm_partial, mode);
+  if (mc_grad)
+    rs_adamw_kernel<true><<<olb_rs_adamw_blocks(n_elems), 256, 0, stream>>>(
+        to_peers(peer_grad, n), to_peers_mut(peer_param, n), n, shard_off, n_elems, master, m, v, *hp, clip_coef_dev,
+        norm_partial, mode, static_cast<const __nv_bfloat16*>(mc_grad), static_cast<__nv_bfloat16*>(mc_param));
+  else
+    rs_adamw_kernel<false><<<olb_rs_adamw_blocks(n_elems), 256, 0, stream>>>(
+        to_peers(peer_grad, n), to_peers_mut(peer_param, n), n, shard_off, n_elems, master, m, v, *hp, clip_coef_dev,
+        norm_partial, mode, nullptr, nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

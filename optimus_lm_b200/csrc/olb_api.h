@@ -258,6 +258,12 @@ int olb_rs_adamw(const void* const* peer_grad, void* const* peer_param, int n, l
                  float* master, float* m, float* v, const olb_adamw_hparams* hp, const float* clip_coef_dev,
                  float* norm_partial, int mode, cudaStream_t stream);
 int olb_rs_adamw_blocks(long long n_elems);
+// The same with NVLS: mc_grad / mc_param are the multicast addresses of the flat gradient / parameter buffers (both or
+// neither; NULL = plain peer loads and stores).  The reduced gradient is rounded to bf16 once, as after a bf16
+// reduce-scatter.
+int olb_rs_adamw_mc(const void* const* peer_grad, void* const* peer_param, int n, long long shard_off, long long n_elems,
+                    float* master, float* m, float* v, const olb_adamw_hparams* hp, const float* clip_coef_dev,
+                    float* norm_partial, int mode, const void* mc_grad, void* mc_param, cudaStream_t stream);
 
 // ---------------------------------------------------------------- attention (attention.cu)
 // Causal flash attention forward, bf16, q/k/v as [B, S, H, D] with arbitrary token/head strides

@@ -15,7 +15,8 @@ from torch import nn
 from torch.utils.checkpoint import checkpoint as torch_activation_checkpoint
 
 from ...ops import functional as OF
-from .comms_ptfunctions import forward_allreduce_backward_identity, forward_identity_backward_allreduce
+from .comms_ptfunctions import (forward_allgather_backward_split, forward_allreduce_backward_identity,
+                                forward_identity_backward_allreduce, forward_split_backward_allgather)
 from .modeling_rope_utils import RotaryEmbedding
 from .norm_modules import NonParametricLayerNorm, RMSNorm
 from .parallel_converter_utils import populate_ColumnLinear_from_Linear, populate_RowLinear_from_Linear
@@ -46,8 +47,13 @@ class ParallelMLP(nn.Module):
         self.up_proj = nn.Linear(self.hidden_size, self.intermediate_size_per_rank, bias=False)
         self.down_proj = nn.Linear(self.intermediate_size_per_rank, self.hidden_size, bias=False)
 
-    def forward(self, x):
+    def forward(self, x, seq_parallel=False):
         tp = self.pmap.tensor_parallelism
+        if seq_parallel:
+            from ...parallel import tp_fused
+            pm = self.pmap
+            g, u = tp_fused.ag_linear(x, (self.gate_proj.weight, self.up_proj.weight), pm.tp_ind, tp, pm.tp_group)
+            return tp_fused.linear_rs(OF.swiglu(g, u), self.down_proj.weight, pm.tp_ind, tp, pm.tp_group)
         if tp > 1:
             x = forward_identity_backward_allreduce.apply(x, self.pmap.tp_group)
         h = OF.swiglu(OF.linear(x, self.gate_proj.weight), OF.linear(x, self.up_proj.weight))
@@ -94,14 +100,23 @@ class ParallelAttention(nn.Module):
         y = OF.linear(x, lin.weight)
         return y if lin.bias is None else y + lin.bias
 
-    def forward(self, hidden_states, position_embeddings):
+    def forward(self, hidden_states, position_embeddings, seq_parallel=None):
+        """``seq_parallel = (B, S)``: ``hidden_states`` holds this rank's ``B * S / TP`` token rows ``[T_loc, H]`` and so
+        does the result; the projections carry the all-gather and the reduce-scatter (no biases in this form)."""
         tp = self.pmap.tensor_parallelism
-        if tp > 1:
-            hidden_states = forward_identity_backward_allreduce.apply(hidden_states, self.pmap.tp_group)
-        B, S, _ = hidden_states.shape
-        q = self._proj(hidden_states, self.q_proj)
-        k = self._proj(hidden_states, self.k_proj)
-        v = self._proj(hidden_states, self.v_proj)
+        if seq_parallel is not None:
+            from ...parallel import tp_fused
+            pm = self.pmap
+            B, S = seq_parallel
+            q, k, v = tp_fused.ag_linear(hidden_states, (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight),
+                                         pm.tp_ind, tp, pm.tp_group, lead=(B, S))
+        else:
+            if tp > 1:
+                hidden_states = forward_identity_backward_allreduce.apply(hidden_states, self.pmap.tp_group)
+            B, S, _ = hidden_states.shape
+            q = self._proj(hidden_states, self.q_proj)
+            k = self._proj(hidden_states, self.k_proj)
+            v = self._proj(hidden_states, self.v_proj)
         if self.use_qk_norm:
             q, k = self.q_norm(q), self.k_norm(k)
         clip = getattr(self.config, "clip_qkv", None)
@@ -114,6 +129,9 @@ class ParallelAttention(nn.Module):
         k = k.view(B, S, self.num_key_value_heads_per_rank, self.head_dim)
         v = v.view(B, S, self.num_key_value_heads_per_rank, self.head_dim)
         o = OF.attention(q, k, v, scale=self.scaling, causal=True)
+        if seq_parallel is not None:
+            return tp_fused.linear_rs(o.reshape(B * S, self.num_attention_heads_per_rank * self.head_dim),
+                                      self.o_proj.weight, pm.tp_ind, tp, pm.tp_group)
         o = self._proj(o.reshape(B, S, self.num_attention_heads_per_rank * self.head_dim), self.o_proj)
         if tp > 1:
             o = forward_allreduce_backward_identity.apply(o, self.pmap.tp_group)
@@ -128,6 +146,15 @@ class ParallelAttention(nn.Module):
         if self.use_qk_norm:
             self.q_norm.load_state_dict(module.q_norm.state_dict())
             self.k_norm.load_state_dict(module.k_norm.state_dict())
+
+
+def _sp_norm(mod, x, group):
+    """A norm applied to sequence-sharded rows: its scale is replicated over the tensor-parallel group, so its
+    gradient (a sum over token rows) has to be summed over the group."""
+    if isinstance(mod, RMSNorm):
+        from ...parallel import tp_fused
+        return OF.rms_norm(x, tp_fused.replicated_weight(mod.weight, group), mod.variance_epsilon)
+    return mod(x)
 
 
 class ParallelDecoderLayer(nn.Module):
@@ -145,6 +172,13 @@ class ParallelDecoderLayer(nn.Module):
         if self.ckpt_norm and torch.is_grad_enabled():
             return torch_activation_checkpoint(mod, x, use_reentrant=False)
         return mod(x)
+
+    def forward_seq_parallel(self, hidden_states, position_embeddings, batch_seq, group):
+        """The layer on this rank's token rows ``[T_loc, H]`` (see the module docstring)."""
+        h = _sp_norm(self.input_layernorm, hidden_states, group)
+        hidden_states = hidden_states + self.self_attn(h, position_embeddings, seq_parallel=batch_seq)
+        h = _sp_norm(self.post_attention_layernorm, hidden_states, group)
+        return hidden_states + self.mlp(h, seq_parallel=True)
 
     def forward(self, hidden_states, position_embeddings):
         residual = hidden_states
@@ -189,10 +223,42 @@ class ParallelDenseModel(nn.Module):
         self.norm = _make_norm(config, family) if pmap.is_last_stage_rank else nn.Identity()
         self.rotary_emb = RotaryEmbedding(config)
 
+    def _seq_parallel_ok(self, hidden_states) -> bool:
+        """Sequence-parallel execution with the collectives inside the GEMMs: tensor parallel, bf16 on GPUs with peer
+        access, no projection biases, token rows divisible into 128-row blocks per rank."""
+        pm = self.pmap
+        tp = pm.tensor_parallelism
+        if tp <= 1 or not hidden_states.is_cuda or hidden_states.dtype != torch.bfloat16:
+            return False
+        if getattr(self.config, "attention_bias", False) or hidden_states.dim() != 3:
+            return False
+        B, S, H = hidden_states.shape
+        if (B * S) % (tp * 128) or any(l.ckpt_norm for l in self.layers):
+            return False
+        from ...parallel import tp_fused
+        l0 = self.layers[0]
+        ws = (l0.self_attn.q_proj.weight, l0.self_attn.k_proj.weight, l0.self_attn.o_proj.weight,
+              l0.mlp.gate_proj.weight, l0.mlp.down_proj.weight)
+        return tp_fused.usable(hidden_states.view(B * S, H)[:(B * S) // tp], pm.tp_group, ws)
+
     def forward(self, input_ids, vp_ind=0):
         hidden_states = OF.embed(self.embed_tokens, input_ids) if vp_ind == 0 else input_ids
         pos = self.rotary_emb.table(hidden_states.size(1), hidden_states.device)
         LV = self.num_hidden_layers_per_vpp_rank
+        if self._seq_parallel_ok(hidden_states):
+            pm = self.pmap
+            B, S, H = hidden_states.shape
+            # this rank's rows of the flattened [B * S] token axis; the backward all-gathers the rows' gradients for
+            # the (vocabulary-parallel) embedding or the previous pipeline stage
+            h = forward_split_backward_allgather.apply(hidden_states.reshape(B * S, H), pm.tp_ind, pm.tensor_parallelism,
+                                                       pm.tp_group)
+            for i in range(vp_ind * LV, (vp_ind + 1) * LV):
+                h = self.layers[i].forward_seq_parallel(h, pos, (B, S), pm.tp_group)
+            if vp_ind == self.VPP - 1:
+                h = _sp_norm(self.norm, h, pm.tp_group)
+            # every rank continues with all rows (the hidden-split LM head, or the next pipeline stage)
+            h = forward_allgather_backward_split.apply(h, pm.tp_ind, pm.tensor_parallelism, pm.tp_group)
+            return h.view(B, S, H)
         for i in range(vp_ind * LV, (vp_ind + 1) * LV):
             hidden_states = self.layers[i](hidden_states, pos)
         return self.norm(hidden_states) if vp_ind == self.VPP - 1 else hidden_states

@@ -133,10 +133,17 @@ def bench_adamw():
     partial = torch.empty(C.rs_adamw_blocks(shard), dtype=torch.float32, device="cuda")
     hp = dict(lr=4e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1)
 
+    from .fused_optimizer import use_multimem
+    nvls = use_multimem(world) and bool(grad.multicast_ptr and param.multicast_ptr)
+    mcg, mcp = (grad.multicast_ptr, param.multicast_ptr) if nvls else (0, 0)
+    if rank == 0:
+        print(f"rs_adamw: {'multimem.ld_reduce / multimem.st through the NVSwitch' if nvls else 'plain peer loads and stores'}",
+              flush=True)
+
     def fused():
         sg.barrier(8)
         C.rs_adamw(grad.ptrs, param.ptrs, rank * shard, master, m, v, hp["lr"], hp["beta1"], hp["beta2"], hp["eps"],
-                   hp["wd"], 1, 1.0 / world, None, partial, 1, False)
+                   hp["wd"], 1, 1.0 / world, None, partial, 1, False, mcg, mcp)
         partial.sum()
         sg.barrier(9)
 

@@ -142,3 +142,149 @@ def ag_swiglu_mlp_rs(x, wg, wu, wd, rank, n, group):
     sg = SymmGroup.get(group)
     holders = (OF._holder(wg), OF._holder(wu), OF._holder(wd))
     return _AGSwiGLURSFn.apply(x.contiguous(), wg, wu, wd, rank, n, sg, holders)
+
+
+# ----------------------------------------------------------------------------- sequence-parallel building blocks
+class _AGLinearFn(torch.autograd.Function):
+    """``[all_gather(x) @ w.T for w in weights]`` for row-sharded ``x [T_loc, H]`` and column-parallel weights
+    (q / k / v, or gate / up).  The first product's launch gathers the peers' rows (all-gather -> GEMM); the others
+    read the gathered copy.  Backward: ``dx = reduce_scatter(sum_i dy_i @ w_i)`` as one K-concatenated
+    GEMM -> reduce-scatter launch, ``dw_i = dy_i.T @ all_gather(x)``."""
+
+    @staticmethod
+    def forward(ctx, x, rank, n, sg, holders, lead, *weights):
+        C = extension()
+        T_loc, H = x.shape
+        T = n * T_loc
+        lead = tuple(lead) if lead else (T,)
+        st = OF.status_word(x.device)
+        xs = sg.named("tp_x", (T_loc, H), x.dtype)
+        xs.local.copy_(x)
+        xg = torch.empty((T, H), dtype=x.dtype, device=x.device)
+        xg[rank * T_loc:(rank + 1) * T_loc].copy_(x)
+        sg.barrier(_CH_X)
+        outs = []
+        for i, w in enumerate(weights):
+            # allocated in its final shape: a later in-place op (RoPE) then works on the output itself, not on a view
+            y = torch.empty(lead + (w.shape[0],), dtype=x.dtype, device=x.device)
+            y2 = y.view(T, w.shape[0])
+            if i == 0:
+                C.gemm_peer(xg, xs.ptrs, w, y2, T, w.shape[0], H, False, rank, _flags(sg, T), st)
+            else:
+                OF.gemm(xg, w, T, w.shape[0], H, out=y2)
+            outs.append(y)
+        ctx.save_for_backward(xg, *weights)
+        ctx.misc = (rank, n, sg, holders)
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *douts):
+        xg, *weights = ctx.saved_tensors
+        rank, n, sg, holders = ctx.misc
+        T, H = xg.shape
+        dws = []
+        for i, (dy, w) in enumerate(zip(douts, weights)):
+            dw = None
+            if ctx.needs_input_grad[6 + i]:
+                dy2 = dy.contiguous().view(T, w.shape[0])
+                h = holders[i]
+                if h is not None:
+                    OF.gemm(dy2, xg, w.shape[0], H, T, a_mn_major=True, b_mn_major=True, out=h.buf, accumulate=h.ready)
+                    h.ready = True
+                else:
+                    dw = OF.gemm(dy2, xg, w.shape[0], H, T, a_mn_major=True, b_mn_major=True)
+            dws.append(dw)
+        # dx_full = [dy_0 | dy_1 | ...] @ [w_0; w_1; ...]: one GEMM whose rows go to their owners as they finish
+        d2 = [d.contiguous().view(T, w.shape[0]) for d, w in zip(douts, weights)]
+        dcat = d2[0] if len(d2) == 1 else torch.cat(d2, dim=1)
+        wcat = weights[0] if len(weights) == 1 else _stacked(weights)
+        dx = _gemm_reduce_scatter(sg, dcat, wcat, T, H, dcat.shape[1], rank, n, b_mn_major=True)
+        return (dx, None, None, None, None, None) + tuple(dws)
+
+
+def _stacked(weights):
+    """``[w_0; w_1; ...]`` as one matrix: a view when the weights sit back to back in memory (parameters of a flat
+    optimizer buffer in registration order), else a copy."""
+    w0 = weights[0]
+    end = w0.data_ptr() + w0.numel() * w0.element_size()
+    ok = w0.is_contiguous()
+    for w in weights[1:]:
+        ok = ok and w.is_contiguous() and w.data_ptr() == end and w.shape[1] == w0.shape[1]
+        end = w.data_ptr() + w.numel() * w.element_size()
+    rows = sum(w.shape[0] for w in weights)
+    if ok:
+        return torch.as_strided(w0, (rows, w0.shape[1]), (w0.shape[1], 1))
+    return torch.cat(list(weights), dim=0)
+
+
+class _LinearRSFn(torch.autograd.Function):
+    """``reduce_scatter(a @ w.T)`` for a row-parallel weight (o / down): the GEMM pushes finished rows to their owners
+    (GEMM -> reduce-scatter).  Backward: ``da = all_gather(dout) @ w`` with the gather inside the launch,
+    ``dw = all_gather(dout).T @ a``."""
+
+    @staticmethod
+    def forward(ctx, a, w, rank, n, sg, holder):
+        T, K = a.shape
+        out = _gemm_reduce_scatter(sg, a, w, T, w.shape[0], K, rank, n)
+        ctx.save_for_backward(a, w)
+        ctx.misc = (rank, n, sg, holder)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        C = extension()
+        a, w = ctx.saved_tensors
+        rank, n, sg, holder = ctx.misc
+        T, K = a.shape
+        H = w.shape[0]
+        T_loc = T // n
+        st = OF.status_word(a.device)
+        dys = sg.named("tp_dy", (T_loc, H), a.dtype)
+        dys.local.copy_(dout)
+        dyg = torch.empty((T, H), dtype=a.dtype, device=a.device)
+        dyg[rank * T_loc:(rank + 1) * T_loc].copy_(dout)
+        sg.barrier(_CH_DY)
+        da = torch.empty((T, K), dtype=a.dtype, device=a.device)
+        C.gemm_peer(dyg, dys.ptrs, w, da, T, K, H, True, rank, _flags(sg, T), st)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            if holder is not None:
+                OF.gemm(dyg, a, H, K, T, a_mn_major=True, b_mn_major=True, out=holder.buf, accumulate=holder.ready)
+                holder.ready = True
+            else:
+                dw = OF.gemm(dyg, a, H, K, T, a_mn_major=True, b_mn_major=True)
+        return da, dw, None, None, None, None
+
+
+def ag_linear(x, weights, rank, n, group, lead=None):
+    """Column-parallel projections of a row-sharded activation: returns ``all_gather(x) @ w.T`` for every ``w``, shaped
+    ``lead + (w.shape[0],)`` (default ``[T, N]``)."""
+    sg = SymmGroup.get(group)
+    return _AGLinearFn.apply(x.contiguous(), rank, n, sg, tuple(OF._holder(w) for w in weights), lead, *weights)
+
+
+def linear_rs(a, w, rank, n, group):
+    """Row-parallel projection whose partial sums are reduce-scattered over the rows: ``[T / n, N]`` of the sum."""
+    sg = SymmGroup.get(group)
+    return _LinearRSFn.apply(a.contiguous(), w, rank, n, sg, OF._holder(w))
+
+
+class _GradAllReduceFn(torch.autograd.Function):
+    """Identity on a parameter that every rank of ``group`` holds; its gradient is summed over the group.  With
+    sequence-sharded activations a replicated weight (a norm's scale) sees only this rank's rows."""
+
+    @staticmethod
+    def forward(ctx, w, group):
+        ctx.group = group
+        return w.view_as(w)
+
+    @staticmethod
+    def backward(ctx, g):
+        import torch.distributed as dist
+        g = g.contiguous()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+def replicated_weight(w, group):
+    return _GradAllReduceFn.apply(w, group)

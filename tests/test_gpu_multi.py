@@ -223,6 +223,33 @@ def w_tp_fused_mlp_vs_nccl(rank, world):
     assert OF.check_status("cuda") == 0
 
 
+def w_dense_tp_sequence_parallel_vs_allreduce(rank, world):
+    """Llama under tensor parallelism: the sequence-parallel execution with all-gather -> GEMM / GEMM -> reduce-scatter
+    launches against the reference form (replicated activations, all-reduces of the collective library)."""
+    from optimus_lm_b200.engine import EngineArgs, TrainEngine
+    runs = {}
+    for fused in (False, True):
+        if fused:
+            os.environ.pop("OLB_DISABLE_TP_FUSED", None)
+        else:
+            os.environ["OLB_DISABLE_TP_FUSED"] = "1"
+        eng = TrainEngine(EngineArgs(model_choice="meta-llama/Llama-3.2-1B--L2", dtype="bf16", context_size=512,
+                                     batch_size=2, warmup_steps=0, lr=1e-3, seed=0, optimizer="shard",
+                                     tensor_parallelism=world))
+        g = torch.Generator().manual_seed(11)
+        out = []
+        for _ in range(4):
+            ids = torch.randint(0, 32000, (2, 512), generator=g)
+            o = eng.train_step(ids.cuda())
+            out.append((float(o.loss), float(o.grad_norm)))
+        assert eng.check_device_status() == 0
+        runs[fused] = out
+    os.environ.pop("OLB_DISABLE_TP_FUSED", None)
+    for (la, na), (lb, nb) in zip(runs[False], runs[True]):
+        assert abs(la - lb) < 3e-2 * abs(la), runs
+        assert abs(na - nb) < 6e-2 * abs(na) + 1e-3, runs
+
+
 LAYOUTS = {
     "olmo_dp2_shard": ("allenai/OLMo-1B-hf--L2", dict(optimizer="shard", batch_size=4)),
     "olmoe_pp2_1f1b": ("allenai/OLMoE-1B-7B-0924--L4-SH0.5-SI0.5",
@@ -276,6 +303,11 @@ def test_fused_engine_matches_nccl_engine(world):
 @pytest.mark.parametrize("world", WORLDS)
 def test_tp_fused_mlp_matches_nccl_path(world):
     _run("w_tp_fused_mlp_vs_nccl", world)
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_dense_tensor_parallel_sequence_parallel_form_matches_allreduce_form(world):
+    _run("w_dense_tp_sequence_parallel_vs_allreduce", world)
 
 
 @pytest.mark.parametrize("name", list(LAYOUTS))
