@@ -1,9 +1,11 @@
 """Reference arm of the benchmark.
 
 Runs the IntelLabs/Optimus-LM code installed (unmodified) under ``baseline/_ref`` for the same
-metric and config as ``bench.py``: OLMoE-1B-7B, sequence 4096, micro-batch 4 per GPU, bf16,
+metric and config as ``bench.py``: by default OLMoE-1B-7B, sequence 4096, micro-batch 4 per GPU, bf16,
 EP = number of GPUs, its process-group-sharded AdamW, synthetic uniform-random tokens and
-N(0, 0.02) random-init weights.
+N(0, 0.02) random-init weights; ``--config`` selects the further configurations (OLMoE data parallel, OLMo-1B
+with ``ShardedMixedPrecisionAdamW``, OLMoE pipeline x expert parallel through the reference's
+``ParallelTrainer``, reduced DeepSeek-V3 expert parallel).
 
 What is the reference's and what is the harness's:
 
@@ -26,8 +28,6 @@ import time
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF = os.path.join(ROOT, "baseline", "_ref")
-METRIC = "OLMoE-1B-7B EP train tokens/s (device-timed, max over ranks)"
-VOCAB = 50304
 
 
 def _unavailable(why):
@@ -47,6 +47,87 @@ def run_reference(opts):
             _unavailable(f"reference run failed: {type(exc).__name__}: {str(exc)[:300]}")
 
 
+def _build(opts, kw, n, rank, dev):
+    """Model, optimizer and (for pipeline runs) trainer of the reference for one named configuration, built the way
+    ``dist_train.py`` builds them (dist_train.py:278-285, 365-450, 534-574, 716-730)."""
+    import torch
+
+    from optimus.config_utils import get_modified_config
+    from optimus.mapper import ParallelDpPpEpTpMapper
+    from optimus.utils import no_init_weights
+    import optimus.optimizers as ropt
+
+    pp = kw.get("pipeline_parallelism", 1)
+    ep = kw.get("expert_parallelism", 1)
+    dp = kw.get("data_parallelism") or max(1, n // (pp * ep))
+    model_choice = kw["model_choice"]
+    pmap = ParallelDpPpEpTpMapper(data_parallelism=dp, pipeline_parallelism=pp, expert_parallelism=ep,
+                                  tensor_parallelism=1, rank=rank, create_groups=(n > 1))
+    family = model_choice.split("--")[0]
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        if family == "allenai/OLMoE-1B-7B-0924":
+            from optimus.models.olmoe.configuration_olmoe import OlmoeParallelConfig
+            from optimus.models.olmoe.modeling_olmoe import OlmoeParallelForCausalLM
+            config = OlmoeParallelConfig(pipeline_parallelism=pp, expert_parallelism=ep, tensor_parallelism=1,
+                                         virtual_pipeline_parallelism=1)
+            config = get_modified_config(model_choice, config)
+            if opts.layers:
+                config.num_hidden_layers = opts.layers
+            config.check_compatibility()
+            with no_init_weights(), torch.device(dev):
+                model = OlmoeParallelForCausalLM(config, pmap=pmap, memory_tracker=None)
+        elif family == "allenai/OLMo-1B-hf":
+            from optimus.models.olmo.configuration_olmo import OlmoParallelConfig
+            from optimus.models.olmo.modeling_olmo import OlmoParallelForCausalLM
+            # the class defaults are OLMo-1B's sizes (the reference copies them from the hub's config, which needs a network)
+            config = OlmoParallelConfig(tensor_parallelism=1, pipeline_parallelism=pp, virtual_pipeline_parallelism=1)
+            config = get_modified_config(model_choice, config)
+            if opts.layers:
+                config.num_hidden_layers = opts.layers
+            with no_init_weights(), torch.device(dev):
+                model = OlmoParallelForCausalLM(config, pmap=pmap)
+        elif family == "deepseek-ai/DeepSeek-V3":
+            from optimus.models.deepseek_v3.configuration_deepseek_v3 import DeepseekV3ParallelConfig
+            from optimus.models.deepseek_v3.modeling_deepseek_v3 import DeepseekV3ParallelForCausalLM
+            config = DeepseekV3ParallelConfig(expert_parallelism=ep, pipeline_parallelism=pp, tensor_parallelism=1,
+                                              virtual_pipeline_parallelism=1)
+            config = get_modified_config(model_choice, config)
+            with no_init_weights(), torch.device(dev):
+                model = DeepseekV3ParallelForCausalLM(config, pmap=pmap, memory_tracker=None)
+        else:
+            raise ValueError(f"no reference builder for {model_choice}")
+    finally:
+        torch.set_default_dtype(prev)
+    std = kw.get("init_std") or 0.02
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() == 1:
+                p.fill_(1.0)
+            else:
+                p.normal_(0.0, std)
+    model = model.to(torch.bfloat16).to(dev)
+
+    cls = {"pgshard": ropt.ParamGroupShardedMixedPrecisionAdamW, "shard": ropt.ShardedMixedPrecisionAdamW}[kw["optimizer"]]
+    optimizer = cls(
+        model.parameters(), model, lr=4e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, warmup_steps=2500,
+        dtype=torch.bfloat16, device=dev, num_shards=pmap.data_parallelism, shard_id=pmap.dp_ind, group=pmap.dp_group,
+        opt_disable_delayed_grad_clipping=False, profiler=None, tensor_parallelism=1, tp_ind=0, tp_group=pmap.tp_group,
+        expert_parallelism=ep, ep_ind=pmap.ep_ind, ep_group=pmap.ep_group, dpep_ind=pmap.dpep_ind,
+        dpep_group=pmap.dpep_group, opt_use_chunked_allreduce=False, opt_use_allreduce_for_grad_acc=False,
+        opt_use_allreduce_for_param_gather=False, skip_optimizer_step=False)
+    optimizer.pmap, optimizer.config, optimizer.dump_weight_gradients = pmap, config, False
+
+    trainer = None
+    if pp > 1:
+        from optimus.training import ParallelTrainer
+        trainer = ParallelTrainer(config, model, pmap, opts.micro_batch, kw.get("micro_batch_size") or opts.micro_batch,
+                                  opts.seq_len, 1, torch.bfloat16, dev, kw.get("pp_scheme", "1f1b"), True,
+                                  memory_tracker=None)
+    return pmap, config, model, optimizer, trainer
+
+
 def _run(opts):
     import torch
     import torch.distributed as dist
@@ -58,7 +139,7 @@ def _run(opts):
         if hasattr(torch.cuda, name):
             setattr(torch.xpu, name, getattr(torch.cuda, name))
 
-    from bench import ClockSampler  # same sampler as the other arm
+    from bench import ClockSampler, metric_name, named_config, result_config  # shared with the other arm
 
     n = opts.gpus
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -72,45 +153,15 @@ def _run(opts):
         torch.cuda.set_device(0)
     dev = torch.device("cuda", torch.cuda.current_device())
 
-    from optimus.config_utils import get_modified_config
-    from optimus.mapper import ParallelDpPpEpTpMapper
-    from optimus.models.olmoe.configuration_olmoe import OlmoeParallelConfig
-    from optimus.models.olmoe.modeling_olmoe import OlmoeParallelForCausalLM
-    from optimus.optimizers import ParamGroupShardedMixedPrecisionAdamW
-    from optimus.utils import get_total_norm, no_init_weights
+    from optimus.utils import get_total_norm
 
+    kw, cfg_mb, cfg_seq, vocab, metric, par_tag = named_config(opts.config, n)
+    if opts.config != "olmoe_ep":
+        opts.micro_batch, opts.seq_len = cfg_mb, cfg_seq
+    metric = metric_name(metric, opts)
     torch.manual_seed(0)
-    pmap = ParallelDpPpEpTpMapper(data_parallelism=1, pipeline_parallelism=1, expert_parallelism=n,
-                                  tensor_parallelism=1, rank=rank, create_groups=(n > 1))
-    config = OlmoeParallelConfig(pipeline_parallelism=1, expert_parallelism=n, tensor_parallelism=1,
-                                 virtual_pipeline_parallelism=1)
-    config = get_modified_config("allenai/OLMoE-1B-7B-0924", config)
-    if opts.layers:
-        config.num_hidden_layers = opts.layers
-    config.check_compatibility()
-    prev = torch.get_default_dtype()
-    torch.set_default_dtype(torch.bfloat16)
-    try:
-        with no_init_weights(), torch.device(dev):
-            model = OlmoeParallelForCausalLM(config, pmap=pmap, memory_tracker=None)
-    finally:
-        torch.set_default_dtype(prev)
-    with torch.no_grad():
-        for name, p in model.named_parameters():
-            if p.dim() == 1:
-                p.fill_(1.0)
-            else:
-                p.normal_(0.0, 0.02)
-    model = model.to(torch.bfloat16).to(dev)
-
-    optimizer = ParamGroupShardedMixedPrecisionAdamW(
-        model.parameters(), model, lr=4e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, warmup_steps=2500,
-        dtype=torch.bfloat16, device=dev, num_shards=pmap.data_parallelism, shard_id=pmap.dp_ind, group=pmap.dp_group,
-        opt_disable_delayed_grad_clipping=False, profiler=None, tensor_parallelism=1, tp_ind=0, tp_group=pmap.tp_group,
-        expert_parallelism=n, ep_ind=pmap.ep_ind, ep_group=pmap.ep_group, dpep_ind=pmap.dpep_ind,
-        dpep_group=pmap.dpep_group, opt_use_chunked_allreduce=False, opt_use_allreduce_for_grad_acc=False,
-        opt_use_allreduce_for_param_gather=False, skip_optimizer_step=False)
-    optimizer.pmap, optimizer.config, optimizer.dump_weight_gradients = pmap, config, False
+    pmap, config, model, optimizer, trainer = _build(opts, kw, n, rank, dev)
+    dpep = pmap.data_parallelism * pmap.expert_parallelism
 
     def sync_all():
         torch.cuda.synchronize()
@@ -120,27 +171,34 @@ def _run(opts):
     def step(tokens):
         """One iteration of the reference's training loop (dist_train.py:748-923)."""
         input_ids = tokens.to(dev).long()
-        outputs = model(input_ids, labels=input_ids)
-        loss = outputs.loss
-        loss.backward()
+        if trainer is None:
+            outputs = model(input_ids, labels=input_ids)
+            loss = outputs.loss
+            loss.backward()
+        else:
+            loss = trainer.step(input_ids, input_ids).loss
         local_grad_norm = get_total_norm([p.grad for p in model.parameters() if p.grad is not None])
-        global_loss = loss.detach().clone()
+        global_loss = torch.zeros(1, dtype=torch.float32, device=dev)
+        if pmap.is_last_stage_rank and loss is not None:
+            global_loss += loss.detach().float()
         if dist.is_initialized():
             dist.all_reduce(global_loss)
-            global_loss /= (pmap.data_parallelism * n)
+            global_loss /= dpep
         torch.cuda.synchronize()
         grad_norm = optimizer.step()
         optimizer.zero_grad()
         torch.cuda.synchronize()
         return global_loss, grad_norm, local_grad_norm
 
-    g = torch.Generator().manual_seed(1234 + rank)
-    total = opts.warmup + 2 * opts.steps
-    host = [torch.randint(0, VOCAB, (opts.micro_batch, opts.seq_len), generator=g, dtype=torch.int64).pin_memory()
+    # ranks of one pipeline read the same batch: the seed is the data-parallel index (as in the other arm)
+    g = torch.Generator().manual_seed(1234 + (rank if opts.config == "olmoe_ep" else pmap.dpep_ind))
+    settle = 5   # untimed steps before the warm-up proper: the reference's allocation pattern needs them to settle
+    total = settle + opts.warmup + 2 * opts.steps
+    host = [torch.randint(0, vocab, (opts.micro_batch, opts.seq_len), generator=g, dtype=torch.int64).pin_memory()
             for _ in range(total)]
-    devb = [b.to(dev) for b in host[:opts.warmup + opts.steps]]
+    devb = [b.to(dev) for b in host[:settle + opts.warmup + opts.steps]]
 
-    for i in range(opts.warmup):
+    for i in range(settle + opts.warmup):
         step(devb[i])
     sync_all()
     sampler = ClockSampler(local_rank)
@@ -150,7 +208,7 @@ def _run(opts):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for i in range(opts.steps):
-        out = step(devb[opts.warmup + i])
+        out = step(devb[settle + opts.warmup + i])
     ev1.record()
     sync_all()
     dev_ms = ev0.elapsed_time(ev1)
@@ -159,7 +217,7 @@ def _run(opts):
     sync_all()
     t0 = time.perf_counter()
     for i in range(opts.steps):
-        out = step(host[opts.warmup + opts.steps + i])
+        out = step(host[settle + opts.warmup + opts.steps + i])
         e2e_loss = out[0].item()
     sync_all()
     e2e_s = time.perf_counter() - t0
@@ -169,18 +227,17 @@ def _run(opts):
     if dist.is_initialized():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dev_ms, e2e_s = t[0].item(), t[1].item()
-    tokens_per_step = opts.micro_batch * opts.seq_len * n
+    tokens_per_step = opts.micro_batch * opts.seq_len * dpep
     if rank == 0:
         res = {
-            "impl": "reference", "metric": METRIC, "value": tokens_per_step * opts.steps / (dev_ms / 1e3),
-            "unit": "tokens/s", "n_gpus": n, "steps": opts.steps, "warmup": opts.warmup,
+            "impl": "reference", "metric": metric, "value": tokens_per_step * opts.steps / (dev_ms / 1e3),
+            "unit": "tokens/s", "n_gpus": n, "steps": opts.steps, "warmup": opts.warmup, "warmup_extra": settle,
             "ms_per_step": dev_ms / opts.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"model": "OLMoE-1B-7B" + (f" (reduced to {opts.layers} layers)" if opts.layers else ""),
-                       "global_batch": opts.micro_batch * n, "seq_len": opts.seq_len,
-                       "parallelism": f"ep{n}" if n > 1 else "ep1", "optimizer": "pgshard (reference)",
-                       "moe_path": "reference stock expert loop (use_fast_moe=False)",
-                       "l2": "activations and weights of every step are far larger than the 126 MB L2; no flush"},
+            "config": result_config(opts, kw, tokens_per_step, par_tag),
+            "impl_notes": {"optimizer": f"{kw['optimizer']} (reference class)",
+                           "moe_path": "reference stock expert loop (use_fast_moe=False: its FastMoE path needs XPU-only code)",
+                           "trainer": "optimus.training.ParallelTrainer" if trainer is not None else "model(input_ids, labels)"},
             "clocks": clocks,
             "e2e": {"value": tokens_per_step * opts.steps / e2e_s, "unit": "tokens/s",
                     "h2d_bytes_per_step": opts.micro_batch * opts.seq_len * 8, "d2h_bytes_per_step": 4,

@@ -73,6 +73,26 @@ def named_config(name: str, n: int):
     raise SystemExit(f"unknown --config {name}")
 
 
+def metric_name(metric, opts):
+    """The configuration's metric name - unless debugging flags changed the shape: a run with another sequence length,
+    micro-batch or layer count is not that benchmark and must not carry its name."""
+    if opts.config == "olmoe_ep" and (opts.seq_len != SEQ_LEN or opts.micro_batch != MICRO_BATCH) or opts.layers:
+        return "DEBUG (not the benchmark configuration): " + metric
+    return metric
+
+
+def result_config(opts, kw, tokens_per_step, par_tag):
+    """The ``config`` record of the JSON line: what was measured, in the same keys and words for both arms (what differs
+    between the implementations goes under ``impl_notes``)."""
+    model = "OLMoE-1B-7B" if kw["model_choice"] == MODEL_CHOICE else kw["model_choice"]
+    if opts.layers:
+        model += f" (reduced to {opts.layers} layers)"
+    return {"model": model, "global_batch": tokens_per_step // opts.seq_len, "seq_len": opts.seq_len,
+            "parallelism": par_tag, "optimizer": kw["optimizer"] + " AdamW, bf16 parameters with fp32 master and moments",
+            "micro_batch_per_gpu": opts.micro_batch,
+            "l2": "activations and weights of every step are far larger than the 126 MB L2; no flush"}
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed
     region runs."""
@@ -150,6 +170,7 @@ def run_ours(opts):
     kw, cfg_mb, cfg_seq, vocab, metric, par_tag = named_config(opts.config, n)
     if opts.config != "olmoe_ep":
         opts.micro_batch, opts.seq_len = cfg_mb, cfg_seq
+    metric = metric_name(metric, opts)
     overrides = {"output_router_logits": True} if "OLMoE" in kw["model_choice"] else {}
     if opts.layers:
         overrides["num_hidden_layers"] = opts.layers  # debugging only; reported in the config
@@ -234,12 +255,10 @@ def run_ours(opts):
             "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": n, "steps": opts.steps,
             "warmup": opts.warmup, "ms_per_step": dev_ms / opts.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"model": ("OLMoE-1B-7B" if opts.config == "olmoe_ep" else kw["model_choice"])
-                       + (f" (reduced to {opts.layers} layers)" if opts.layers else ""),
-                       "global_batch": tokens_per_step // opts.seq_len, "seq_len": opts.seq_len,
-                       "parallelism": par_tag, "optimizer": kw["optimizer"] + " (fp32 master + moments)",
-                       "micro_batch_per_gpu": opts.micro_batch, "ep_transport": "nccl all-gather/reduce-scatter" if opts.nccl_only else "fused all-to-all",
-                       "l2": "activations and weights of every step are far larger than the 126 MB L2; no flush"},
+            "config": result_config(opts, kw, tokens_per_step, par_tag),
+            "impl_notes": {"ep_transport": "nccl all-gather/reduce-scatter" if opts.nccl_only
+                           else "dispatch / combine inside the grouped GEMM launches over NVLink peer memory",
+                           "optimizer_collectives": "nccl" if opts.nccl_only else "fused reduce-scatter + AdamW + all-gather kernel"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "ms_per_step": e2e_s * 1e3 / opts.steps},

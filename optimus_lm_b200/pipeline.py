@@ -7,10 +7,15 @@ which use blocking ``send``/``recv`` followed by a device synchronise after ever
 * sends are ``isend`` and are only waited for at the end of the step, so a stage starts its next
   micro-batch while the previous output is still in flight; receives are posted when the data is
   needed and only the compute stream waits for them - the host never synchronises;
-* forward traffic, backward traffic and the two wrap-around directions of virtual pipelining each
-  use their own process group.  Every channel is then one-directional and in schedule order on
-  both ends, which makes the exchange dead-lock free without the reference's recv-before-send
-  choreography;
+* every (sender, receiver) pair of neighbouring stages has two process groups of its own, of two ranks each: one
+  for the activations going forward, one for the gradients coming back (the wrap-around pair of virtual
+  pipelining is one more such pair).  Every channel is then one-directional and in schedule order on both
+  ends, which makes the exchange dead-lock free without the reference's recv-before-send choreography; and
+  because each group has its own communicator and stream, a transfer waits neither for the other
+  direction nor for the collectives of the data / expert / tensor parallel groups.  The operations are
+  issued through ``batch_isend_irecv``;
+* ``OLB_PP_BLOCKING=1`` restores the reference's behaviour (blocking transfer + device synchronise after each)
+  for A/B measurements of the overlap;
 * the global router auxiliary loss travels as ``2E+2`` running sums forward and the global
   selection fractions (``E`` floats) backward instead of the concatenated router logits and their
   gradients (see ``ops/aux_loss.py``);
@@ -19,6 +24,7 @@ which use blocking ``send``/``recv`` followed by a device synchronise after ever
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -46,15 +52,42 @@ class _MicroState:
 
 
 _CHANNEL_GROUPS: Dict[str, object] = {}
+_PAIR_GROUPS: Dict[Tuple[int, int, str], object] = {}
 
 
 def _channel_groups(need_wrap: bool):
-    """One process group per traffic direction (created once per process, by all ranks)."""
+    """One world-size process group per traffic direction (the fall-back when the stage neighbours of the other ranks
+    cannot be derived from the mapper)."""
     names = ["fwd", "bwd"] + (["wrap_fwd", "wrap_bwd"] if need_wrap else [])
     for n in names:
         if n not in _CHANNEL_GROUPS:
             _CHANNEL_GROUPS[n] = dist.new_group(list(range(dist.get_world_size())))
     return _CHANNEL_GROUPS
+
+
+def _pair_groups(pmap):
+    """Two-rank process groups for every (stage rank -> next stage rank) pair of the job, one for each direction of
+    traffic: ``(src, dst, "fwd")`` carries activations from ``src`` to ``dst``, ``(src, dst, "bwd")`` the gradients from
+    ``dst`` back to ``src``.  Group creation is collective, so every rank walks all pairs in the same order.  Returns
+    ``None`` when the mapper cannot be instantiated for other ranks (legacy mappers)."""
+    world = dist.get_world_size()
+    if _PAIR_GROUPS:
+        return _PAIR_GROUPS
+    try:
+        nexts = []
+        for r in range(world):
+            other = type(pmap)(pmap.data_parallelism, pmap.pipeline_parallelism, pmap.expert_parallelism,
+                               pmap.tensor_parallelism, rank=r, create_groups=False,
+                               use_pp_first=getattr(pmap, "use_pp_first", False))
+            nexts.append(other.next_stage_rank)
+    except Exception:  # noqa: BLE001 - a mapper with another constructor: keep the world-size channels
+        return None
+    for r in range(world):
+        if nexts[r] == r:
+            continue
+        for kind in ("fwd", "bwd"):
+            _PAIR_GROUPS[(r, nexts[r], kind)] = dist.new_group(sorted((r, nexts[r])))
+    return _PAIR_GROUPS
 
 
 class PipelineExecutor:
@@ -85,7 +118,12 @@ class PipelineExecutor:
         self.use_global_router_aux_loss = self.use_aux_loss and not self.use_local_router_aux_loss
 
         self.schedule: List[PipeOp] = make_schedule(pp_scheme, pmap.pp_ind, self.PP, self.NMB, self.VPP)
-        self.groups = _channel_groups(self.VPP > 1) if dist.is_initialized() else {}
+        self.groups, self.pairs = {}, None
+        if dist.is_initialized() and self.PP > 1:
+            self.pairs = _pair_groups(pmap)
+            if self.pairs is None:
+                self.groups = _channel_groups(self.VPP > 1)
+        self.blocking = os.environ.get("OLB_PP_BLOCKING", "0") == "1"
         self.last_virtual = self.PP * self.VPP - 1
         self._pending: List[Tuple[object, torch.Tensor]] = []
 
@@ -95,33 +133,55 @@ class PipelineExecutor:
 
     def _fwd_src(self, vp):
         """(rank, group) the input of chunk ``vp`` comes from."""
+        me, prev = self.pmap.rank, self.pmap.prev_stage_rank
+        if self.pairs is not None:
+            return prev, self.pairs[(prev, me, "fwd")]
         if self.pmap.pp_ind > 0:
-            return self.pmap.prev_stage_rank, self.groups["fwd"]
-        return self.pmap.prev_stage_rank, self.groups["wrap_fwd"]  # first stage, vp > 0: from the last stage
+            return prev, self.groups["fwd"]
+        return prev, self.groups["wrap_fwd"]  # first stage, vp > 0: from the last stage
 
     def _fwd_dst(self, vp):
+        me, nxt = self.pmap.rank, self.pmap.next_stage_rank
+        if self.pairs is not None:
+            return nxt, self.pairs[(me, nxt, "fwd")]
         if self.pmap.pp_ind < self.PP - 1:
-            return self.pmap.next_stage_rank, self.groups["fwd"]
-        return self.pmap.next_stage_rank, self.groups["wrap_fwd"]
+            return nxt, self.groups["fwd"]
+        return nxt, self.groups["wrap_fwd"]
 
     def _bwd_src(self, vp):
+        me, nxt = self.pmap.rank, self.pmap.next_stage_rank
+        if self.pairs is not None:
+            return nxt, self.pairs[(me, nxt, "bwd")]
         if self.pmap.pp_ind < self.PP - 1:
-            return self.pmap.next_stage_rank, self.groups["bwd"]
-        return self.pmap.next_stage_rank, self.groups["wrap_bwd"]
+            return nxt, self.groups["bwd"]
+        return nxt, self.groups["wrap_bwd"]
 
     def _bwd_dst(self, vp):
+        me, prev = self.pmap.rank, self.pmap.prev_stage_rank
+        if self.pairs is not None:
+            return prev, self.pairs[(prev, me, "bwd")]
         if self.pmap.pp_ind > 0:
-            return self.pmap.prev_stage_rank, self.groups["bwd"]
-        return self.pmap.prev_stage_rank, self.groups["wrap_bwd"]
+            return prev, self.groups["bwd"]
+        return prev, self.groups["wrap_bwd"]
 
     def _isend(self, t, dst_group):
         dst, group = dst_group
         t = t.contiguous()
-        self._pending.append((dist.isend(t, dst, group=group), t))
+        works = dist.batch_isend_irecv([dist.P2POp(dist.isend, t, dst, group)])
+        if self.blocking:
+            for w in works:
+                w.wait()
+            if t.is_cuda:
+                torch.cuda.synchronize()
+            return
+        self._pending.extend((w, t) for w in works)
 
     def _recv(self, t, src_group):
         src, group = src_group
-        dist.irecv(t, src, group=group).wait()
+        for w in dist.batch_isend_irecv([dist.P2POp(dist.irecv, t, src, group)]):
+            w.wait()
+        if self.blocking and t.is_cuda:
+            torch.cuda.synchronize()
         return t
 
     # ------------------------------------------------------------------ model call / router info

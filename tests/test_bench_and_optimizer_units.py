@@ -78,3 +78,17 @@ def test_fused_step_alignment_predicate(dp):
     params = [torch.nn.Parameter(torch.zeros(4096)), torch.nn.Parameter(torch.zeros(1000))]
     plain = _Family(_FamilySpec("", params, None, dp, dp - 1, 1.0), torch.bfloat16, "cpu", 512, keep_state=False)
     assert slices_aligned([plain])
+
+
+def test_debug_shapes_do_not_carry_the_benchmark_metric_name():
+    import types
+    b = _bench()
+    opts = types.SimpleNamespace(config="olmoe_ep", seq_len=b.SEQ_LEN, micro_batch=b.MICRO_BATCH, layers=0)
+    assert b.metric_name(b.METRIC, opts) == b.METRIC
+    for change in (dict(seq_len=1024), dict(micro_batch=1), dict(layers=4)):
+        o = types.SimpleNamespace(**{**vars(opts), **change})
+        assert b.metric_name(b.METRIC, o).startswith("DEBUG")
+    # both arms describe the measured configuration with the same record
+    kw, mb, seq, vocab, metric, tag = b.named_config("olmoe_ep", 8)
+    rec = b.result_config(opts, kw, 8 * mb * seq, tag)
+    assert rec["model"] == "OLMoE-1B-7B" and rec["global_batch"] == 32 and rec["parallelism"] == "ep8"
