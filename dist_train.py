@@ -156,6 +156,9 @@ def optimizer_key(args) -> str:
              "subshard": args.opt_use_subsharded_optimizer, "pgsubshard": args.opt_use_pgsubsharded_optimizer}
     chosen = [k for k, v in flags.items() if v]
     assert len(chosen) <= 1, "choose at most one optimizer"
+    if args.opt_use_pt_optimizer:
+        assert not chosen, "--opt_use_pt_optimizer excludes the flat-buffer optimizers"
+        return "pt"
     return chosen[0] if chosen else "unsharded"
 
 
@@ -290,8 +293,6 @@ def main(argv=None):
         args.micro_batch_size = args.batch_size
     if args.pipeline_parallelism > 1 or args.expert_parallelism > 1 or args.tensor_parallelism > 1:
         assert not args.use_hf_model, "Huggingface model does not support parallelism"
-    assert not args.use_hf_model, "--use_hf_model needs the HuggingFace hub, which this build does not assume"
-    assert not args.opt_use_pt_optimizer, "--opt_use_pt_optimizer is not supported; use the flat-buffer optimizers"
 
     launched = int(os.environ.get("WORLD_SIZE", os.environ.get("PMI_SIZE", "1"))) > 1
     rank, world_size, local_rank = 0, 1, 0
@@ -322,7 +323,11 @@ def main(argv=None):
     overrides = {"router_z_loss_coef": args.router_z_loss_coef} if args.router_z_loss_coef else {}
     if args.moe_capacity_factor is not None:
         overrides["moe_capacity_factor"] = args.moe_capacity_factor
-    config, model = build_model(
+    if args.use_hf_model:
+        from optimus_lm_b200.engine import build_hf_model
+        config, model = build_hf_model(args.model_choice, dtype=dtype, device=device, config_overrides=overrides)
+    else:
+        config, model = build_model(
         args.model_choice, pmap, dtype=dtype, device=device, memory_tracker=memory_tracker, config_overrides=overrides,
         pipeline_parallelism=args.pipeline_parallelism, expert_parallelism=args.expert_parallelism,
         tensor_parallelism=args.tensor_parallelism, virtual_pipeline_parallelism=args.virtual_pipeline_parallelism,
@@ -333,7 +338,8 @@ def main(argv=None):
         use_fused_ep_alltoall=not args.disable_fused_ep_alltoall)
     if rank == 0:
         print(config, flush=True)
-    load_initial_weights(args, model, pmap, rank)
+    if not args.use_hf_model:
+        load_initial_weights(args, model, pmap, rank)
     if profiler is not None and args.profile_modules:
         profiler.setup_profiler_for_pytorch_model(model)
 
@@ -357,7 +363,7 @@ def main(argv=None):
     engine = TrainEngine(eargs, pmap=pmap, model=model, config=config, device=device)
     optimizer = engine.optimizer
     optimizer.dump_weight_gradients = args.dump_weight_gradients
-    sharded_opt = optimizer_key(args) != "unsharded"
+    sharded_opt = optimizer_key(args) not in ("unsharded", "pt")
 
     # ------------------------------------------------------------------ resume
     train_step_id = 0

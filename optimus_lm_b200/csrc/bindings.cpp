@@ -438,6 +438,7 @@ void stamp_globaltimer(at::Tensor& slot) {
 
 void register_attention(pybind11::module& m);
 void register_comm(pybind11::module& m);
+void register_customops(pybind11::module& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, pybind11::arg("a"), pybind11::arg("b"), pybind11::arg("c"), pybind11::arg("M"), pybind11::arg("N"),
@@ -484,4 +485,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("stamp_globaltimer", &stamp_globaltimer);
   register_attention(m);
   register_comm(m);
+  register_customops(m);
 }

@@ -489,7 +489,8 @@ __device__ __forceinline__ void stager_loop(const PeerArg<true>& peers, const Ge
       uint4* d[2];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
-        const int g = peers.src_of[u0 + r];
+        int g = peers.src_of[u0 + r];
+        if (g >= 0 && !OLB_INDEX_OK(g, static_cast<long long>(peers.n) * peers.T, p.status)) g = -1;
         const int owner = g >= 0 ? g / peers.T : 0;
         s[r] = g >= 0 ? reinterpret_cast<const uint4*>(static_cast<const char*>(peers.src[owner]) +
                                                        static_cast<long long>(g - owner * peers.T) * peers.src_ld * 2)
@@ -536,6 +537,9 @@ __device__ __forceinline__ void stager_loop(const PeerArg<true>& peers, const Ge
       }
       const int g = peers.src_of[u];
       if (g < 0) continue;
+      if (!OLB_INDEX_OK(g, static_cast<long long>(peers.n) * peers.T, p.status) ||
+          !OLB_INDEX_OK(peers.k_of[u], peers.topk, p.status))
+        continue;
       const int owner = g / peers.T;
       const long long slot = static_cast<long long>(g - owner * peers.T) * peers.topk + peers.k_of[u];
       const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.c_base) + u * peers.ldc * 2);

@@ -225,6 +225,21 @@ int olb_adamw_step(const void* grad, int grad_fp32, float* master, float* m, flo
                    long long n, const olb_adamw_hparams* hp, const float* clip_coef_dev, float* norm_partial,
                    cudaStream_t stream);
 
+// ---------------------------------------------------------------- reference custom-op interface (customops.cu)
+// The seven entry points of the reference's pcl_xpu_customops extension on its data layout (see customops.cu).
+// int32 indices; data bf16, or fp32 when `fp32` is set.
+int olb_co_partial_token_counts(const int* sel, int T, int K, int e_start, int E_loc, int* partial, int* counts_ep,
+                                cudaStream_t stream);
+int olb_co_input_output_indices(const int* sel, int T, int K, int e_start, int E_loc, const int* partial_cum, int* incr,
+                                const int* cum_ep, int* sel_idx, int* in_idx, int* out_idx, cudaStream_t stream);
+int olb_co_index_gather(const void* inp, const int* idx, void* out, int rows_out, int cols, int fp32, cudaStream_t stream);
+// out[t] (+)= sum over the slots of t of w * y[out_idx[slot]]; weights NULL = unweighted (shuffle_sub_matrix_reduce).
+int olb_co_reduce(const void* y, const void* weights, int K, const int* cum_ep, const int* sel_idx, const int* out_idx,
+                  void* out, int T, int cols, int accumulate, int fp32, cudaStream_t stream);
+int olb_co_reduce_bwd(const void* dout, const void* y, const void* weights, int K, const int* cum_ep, const int* sel_idx,
+                      const int* out_idx, void* dy, void* dw, int T, int cols, int fp32, cudaStream_t stream);
+int olb_co_index_add(const void* src, void* dst, const int* idx, int rows, int cols, int fp32, cudaStream_t stream);
+
 // ---------------------------------------------------------------- peer-memory kernels (comm_p2p.cu)
 // Host arrays of n (<= 16) device pointers, one per rank of the group, into symmetric buffers.
 // Rendezvous of all ranks through signal words pads[rank][channel*16 + src]; `epoch` must grow by one

@@ -26,6 +26,21 @@ enum : int {
   ST_BAD_ARG = 7,
 };
 
+// Debug builds (-DOLB_DEBUG_CHECKS, `OLB_DEBUG_CHECKS=1 python setup.py build_ext --inplace`): index-driven accesses of
+// the kernels that move rows by index check their indices first; a bad one records ST_BAD_ARG in the status word and
+// the access is skipped, so the run ends with a readable status instead of a memory fault.  In regular builds the
+// check is the constant `true`.
+#ifdef OLB_DEBUG_CHECKS
+__device__ __forceinline__ bool olb_index_ok(long long idx, long long limit, int* status) {
+  if (idx >= 0 && idx < limit) return true;
+  if (status) atomicCAS(status, 0, ST_BAD_ARG);
+  return false;
+}
+#define OLB_INDEX_OK(idx, limit, status) olb_index_ok((idx), (limit), (status))
+#else
+#define OLB_INDEX_OK(idx, limit, status) true
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

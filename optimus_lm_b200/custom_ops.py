@@ -16,14 +16,29 @@ Data layout of that interface (R = routed rows on this rank, TH = ceil(T / 8) "t
 
 This framework's own MoE path does not go through these functions: it builds a padded,
 tile-aligned index on the device in one pass (``ops.functional.MoEIndex``) and folds the routing
-weight into the expert activation.  The functions here are vectorised tensor programs with the
-reference's semantics, usable on any device; ``index_gather`` runs the row-gather kernel on CUDA bf16.
+weight into the expert activation.  On CUDA tensors (int32 indices, contiguous bf16 or fp32 data) every
+function runs its kernel of ``csrc/customops.cu``; elsewhere the vectorised tensor programs below, which are also
+the kernels' test oracle.
 """
 from __future__ import annotations
 
 import torch
 
 TOKENS_PER_THREAD = 8
+
+
+def _native(*tensors):
+    """The compiled extension when every tensor is a contiguous CUDA tensor the kernels take, else ``None``."""
+    for t in tensors:
+        if not (torch.is_tensor(t) and t.is_cuda and t.is_contiguous()):
+            return None
+        if t.dtype not in (torch.int32, torch.float32, torch.bfloat16):
+            return None
+    from .ops._ext import extension, kernels_disabled
+    if kernels_disabled():
+        return None
+    C = extension()
+    return C if hasattr(C, "co_index_gather") else None
 
 
 def _local_mask(selected_experts, e_start, e_end):
@@ -33,6 +48,10 @@ def _local_mask(selected_experts, e_start, e_end):
 def compute_partial_token_counts(selected_experts, partial_token_counts, expert_counts_ep, expert_start_idx,
                                  expert_end_idx):
     """K1: fills ``partial_token_counts [E_loc, TH]`` and ``expert_counts_ep [T]``; returns the former."""
+    C = _native(selected_experts, partial_token_counts, expert_counts_ep)
+    if C is not None and selected_experts.dtype == torch.int32:
+        return C.co_compute_partial_token_counts(selected_experts, partial_token_counts, expert_counts_ep,
+                                                 expert_start_idx, expert_end_idx)
     T, K = selected_experts.shape
     E_loc = expert_end_idx - expert_start_idx
     TH = partial_token_counts.shape[1]
@@ -50,7 +69,16 @@ def compute_input_and_output_indices(selected_experts, partial_cum_token_counts,
                                      expert_start_idx, expert_end_idx):
     """K3: deterministic bucket placement.  ``partial_cum_token_counts [E_loc * TH + 1]`` is the exclusive
     prefix of the flattened K1 counts; ``input_increment_buffer`` is scratch of the reference's kernel and
-    is left untouched."""
+    is left untouched (the CUDA kernel uses it for its per-bucket counters)."""
+    C = _native(selected_experts, partial_cum_token_counts, input_increment_buffer, cum_expert_counts_ep,
+                selected_experts_indices, input_indices, output_indices)
+    if C is not None and all(t.dtype == torch.int32 for t in (selected_experts, partial_cum_token_counts,
+                                                               input_increment_buffer, cum_expert_counts_ep,
+                                                               selected_experts_indices, input_indices, output_indices)):
+        C.co_compute_input_and_output_indices(selected_experts, partial_cum_token_counts, input_increment_buffer,
+                                              cum_expert_counts_ep, selected_experts_indices, input_indices,
+                                              output_indices, expert_start_idx, expert_end_idx)
+        return
     T, K = selected_experts.shape
     E_loc = expert_end_idx - expert_start_idx
     TH = (partial_cum_token_counts.numel() - 1) // E_loc
@@ -77,6 +105,9 @@ def compute_input_and_output_indices(selected_experts, partial_cum_token_counts,
 
 def index_gather(inp, indices, out):
     """K4f: ``out[o, :] = inp[indices[o], :]``."""
+    C = _native(inp, indices, out)
+    if C is not None and indices.dtype == torch.int32 and inp.dtype == out.dtype != torch.int32:
+        return C.co_index_gather(inp, indices, out)
     torch.index_select(inp, 0, indices.long(), out=out)
     return out
 
@@ -88,6 +119,10 @@ def _slot_tokens(cum_expert_counts_ep):
 
 def shuffle_sub_matrix_reduce(ggemm_input_grad, cum_expert_counts_ep, output_indices, hidden_states_grad):
     """K4b: ``dX[t] = sum over the slots of t of dY[output_indices[slot]]`` (fp32 accumulation)."""
+    C = _native(ggemm_input_grad, cum_expert_counts_ep, output_indices, hidden_states_grad)
+    if C is not None and cum_expert_counts_ep.dtype == output_indices.dtype == torch.int32 \
+            and ggemm_input_grad.dtype == hidden_states_grad.dtype != torch.int32:
+        return C.co_shuffle_sub_matrix_reduce(ggemm_input_grad, cum_expert_counts_ep, output_indices, hidden_states_grad)
     tok = _slot_tokens(cum_expert_counts_ep)
     acc = torch.zeros(hidden_states_grad.shape, dtype=torch.float32, device=hidden_states_grad.device)
     acc.index_add_(0, tok, ggemm_input_grad[output_indices.long()].float())
@@ -98,6 +133,12 @@ def shuffle_sub_matrix_reduce(ggemm_input_grad, cum_expert_counts_ep, output_ind
 def reduce_ggemm_output(ggemm_output, routing_weights, cum_expert_counts_ep, selected_experts_indices, output_indices,
                         final_hidden_states, accumulate=False):
     """K6f: ``out[t] (+)= sum over slots of w[t, k_slot] * Y[output_indices[slot]]`` (fp32 accumulation)."""
+    C = _native(ggemm_output, routing_weights, cum_expert_counts_ep, selected_experts_indices, output_indices,
+                final_hidden_states)
+    if C is not None and cum_expert_counts_ep.dtype == selected_experts_indices.dtype == output_indices.dtype == torch.int32 \
+            and ggemm_output.dtype == routing_weights.dtype == final_hidden_states.dtype != torch.int32:
+        return C.co_reduce_ggemm_output(ggemm_output, routing_weights, cum_expert_counts_ep, selected_experts_indices,
+                                        output_indices, final_hidden_states, bool(accumulate))
     tok = _slot_tokens(cum_expert_counts_ep)
     w = routing_weights[tok, selected_experts_indices.long()].float().unsqueeze(1)
     acc = final_hidden_states.float() if accumulate else torch.zeros(final_hidden_states.shape, dtype=torch.float32,
@@ -112,6 +153,16 @@ def reduce_ggemm_output_backward(final_hidden_states_grad, ggemm_output, routing
                                  routing_weights_grad):
     """K6b: ``dY[row] = w[t, k] * dOut[t]`` and ``dw[t, k] = <Y[row], dOut[t]>`` for every slot (t, k) -> row;
     entries of ``dw`` whose expert is not local stay as they were."""
+    C = _native(final_hidden_states_grad, ggemm_output, routing_weights, cum_expert_counts_ep, selected_experts_indices,
+                output_indices, ggemm_output_grad, routing_weights_grad)
+    dts = {t.dtype for t in (final_hidden_states_grad, ggemm_output, routing_weights, ggemm_output_grad,
+                             routing_weights_grad)}
+    if C is not None and len(dts) == 1 and torch.int32 not in dts \
+            and cum_expert_counts_ep.dtype == selected_experts_indices.dtype == output_indices.dtype == torch.int32:
+        C.co_reduce_ggemm_output_backward(final_hidden_states_grad, ggemm_output, routing_weights, cum_expert_counts_ep,
+                                          selected_experts_indices, input_indices, output_indices, ggemm_output_grad,
+                                          routing_weights_grad)
+        return
     tok = _slot_tokens(cum_expert_counts_ep)
     rows = output_indices.long()
     k = selected_experts_indices.long()
@@ -122,6 +173,10 @@ def reduce_ggemm_output_backward(final_hidden_states_grad, ggemm_output, routing
 
 def index_add_op(expert_output, final_output, indices):
     """K7: ``final_output[indices[c], :] += expert_output[c, :]``."""
+    C = _native(expert_output, final_output, indices)
+    if C is not None and indices.dtype == torch.int32 and expert_output.dtype == final_output.dtype != torch.int32 \
+            and expert_output.shape[1] % 2 == 0:
+        return C.co_index_add_op(expert_output, final_output, indices)
     final_output.index_add_(0, indices.long(), expert_output.to(final_output.dtype))
     return final_output
 

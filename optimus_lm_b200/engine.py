@@ -47,7 +47,8 @@ class EngineArgs:
     batch_size: int = 1
     micro_batch_size: Optional[int] = None
     context_size: int = 4096
-    optimizer: str = "unsharded"          # unsharded | shard | pgshard | subshard | pgsubshard
+    optimizer: str = "unsharded"          # unsharded | shard | pgshard | subshard | pgsubshard | pt (torch.optim.AdamW)
+    use_hf_model: bool = False            # the transformers implementation of the architecture (no model parallelism)
     lr: float = 4e-4
     min_lr: float = 4e-5
     weight_decay: float = 0.1
@@ -114,6 +115,27 @@ def build_model(model_choice: str, pmap, *, dtype=torch.bfloat16, device="cpu", 
     finally:
         torch.set_default_dtype(prev)
     return cfg, model
+
+
+def build_hf_model(model_choice: str, *, dtype=torch.bfloat16, device="cpu", config_overrides=None):
+    """``--use_hf_model``: the ``transformers`` implementation of ``model_choice`` with the sizes of the model tag
+    (reference dist_train.py:304-318).  The reference fetches the base configuration from the hub; here it is built from
+    this package's own configuration of the architecture, so no network is needed.  Random initialisation as
+    ``from_config`` does it; no pipeline, expert or tensor parallelism."""
+    import transformers
+
+    from .convert import hf_config_dict
+    cfg = config_utils.build_config(model_choice)
+    for k, v in (config_overrides or {}).items():
+        setattr(cfg, k, v)
+    d = hf_config_dict(model_choice, cfg, torch_dtype="bfloat16" if dtype == torch.bfloat16 else "float32")
+    d = {k: v for k, v in d.items() if k not in ("architectures", "torch_dtype", "dtype", "transformers_version")}
+    hf_cfg = transformers.AutoConfig.for_model(**d)
+    hf_cfg.use_cache = False
+    if getattr(cfg, "output_router_logits", False):
+        hf_cfg.output_router_logits = True
+    model = transformers.AutoModelForCausalLM.from_config(hf_cfg)
+    return cfg, model.to(dtype).to(device)
 
 
 @torch.no_grad()
@@ -184,6 +206,11 @@ class TrainEngine:
         self.device = torch.device(device)
         self.dtype = torch.bfloat16 if args.dtype in ("bf16", "bfloat16") else torch.float32
 
+        if model is None and args.use_hf_model:
+            assert args.pipeline_parallelism == args.expert_parallelism == args.tensor_parallelism == 1, \
+                "Huggingface model does not support parallelism"
+            config, model = build_hf_model(args.model_choice, dtype=self.dtype, device=self.device,
+                                           config_overrides=args.config_overrides)
         if model is None:
             config, model = build_model(
                 args.model_choice, pmap, dtype=self.dtype, device=self.device,
@@ -218,7 +245,7 @@ class TrainEngine:
                       expert_parallelism=p.expert_parallelism, ep_ind=p.ep_ind, ep_group=p.ep_group,
                       dpep_ind=p.dpep_ind, dpep_group=p.dpep_group, skip_optimizer_step=a.skip_optimizer_step,
                       opt_use_chunked_allreduce=a.opt_use_chunked_allreduce)
-        if a.optimizer != "unsharded":
+        if a.optimizer not in ("unsharded", "pt"):
             kwargs.update(opt_use_allreduce_for_grad_acc=a.opt_use_allreduce_for_grad_acc,
                           opt_use_allreduce_for_param_gather=a.opt_use_allreduce_for_param_gather,
                           disable_optimizer_state_checkpointing=a.disable_optimizer_state_checkpointing,

@@ -743,7 +743,62 @@ class ParamGroupSubShardedMixedPrecisionAdamW(ParamGroupShardedMixedPrecisionAda
         super().__init__(*args, _chunk_limit=chunk_size_limit, **kwargs)
 
 
+class TorchAdamW:
+    """``--opt_use_pt_optimizer``: ``torch.optim.AdamW`` on the model's own parameters (reference
+    dist_train.py:575-589, 889-906).  The reference wraps the model in DistributedDataParallel when there are
+    data-parallel replicas; here the gradients are averaged over the data-parallel group right before the
+    update, which gives the same numbers without a wrapper module around the model.  Gradient clipping to norm 1
+    starts after ``warmup_steps`` optimizer steps unless delayed clipping is disabled, with the local norm as in the
+    reference.  Takes the constructor keywords of the flat-buffer classes and ignores those it has no use for."""
+
+    def __init__(self, params, model, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, warmup_steps=0,
+                 num_shards=1, group=None, opt_disable_delayed_grad_clipping=False, skip_optimizer_step=False,
+                 opt_use_one_step_grad_clipping=False, **_unused):
+        self.model = model
+        self.inner = torch.optim.AdamW(list(params), lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        self.param_groups = self.inner.param_groups
+        self.defaults = self.inner.defaults
+        self.warmup_steps = warmup_steps
+        self.num_shards, self.group = num_shards, group
+        self.opt_disable_delayed_grad_clipping = opt_disable_delayed_grad_clipping
+        self.skip_optimizer_step = skip_optimizer_step
+        self.one_step_clipping = opt_use_one_step_grad_clipping
+        self.max_grad_norm = 1.0
+        self.step_id = 0
+
+    def _params(self):
+        return [p for g in self.param_groups for p in g["params"] if p.grad is not None]
+
+    @torch.no_grad()
+    def step(self):
+        ps = self._params()
+        if self.num_shards > 1 and _group_ok(self.group):
+            for p in ps:
+                dist.all_reduce(p.grad, group=self.group)
+                p.grad.div_(self.num_shards)
+        grads = [p.grad for p in ps]
+        grad_norm = torch.nn.utils.get_total_norm(grads) if grads else torch.zeros(())
+        if grads and (self.opt_disable_delayed_grad_clipping or self.step_id >= self.warmup_steps):
+            torch.nn.utils.clip_grads_with_norm_(ps, self.max_grad_norm, grad_norm)
+        if not self.skip_optimizer_step:
+            self.inner.step()
+        self.step_id += 1
+        return grad_norm
+
+    def zero_grad(self, set_to_none=True):
+        self.inner.zero_grad(set_to_none=set_to_none)
+
+    def state_dict(self):
+        return {"inner": self.inner.state_dict(), "step_id": self.step_id}
+
+    def load_state_dict(self, sd):
+        self.inner.load_state_dict(sd["inner"])
+        self.step_id = int(sd.get("step_id", 0))
+        self.param_groups = self.inner.param_groups
+
+
 OPTIMIZER_CLASSES = {
+    "pt": TorchAdamW,
     "unsharded": MixedPrecisionAdamW,
     "shard": ShardedMixedPrecisionAdamW,
     "pgshard": ParamGroupShardedMixedPrecisionAdamW,

@@ -26,18 +26,33 @@ from ..ops import functional as OF
 from ..ops._ext import extension
 
 _SIGNAL_WORDS = 16 * 64  # 64 channels x 16 peers
+_CANARY_BYTES = 4096     # guard band on each side of a symmetric buffer when OLB_SYMM_CANARY=1
+_CANARY_VALUE = 0xA5
+
+
+def canaries_enabled() -> bool:
+    """``OLB_SYMM_CANARY=1``: every symmetric buffer gets a guard band of ``_CANARY_BYTES`` on both sides, filled with a
+    pattern; ``SymmGroup.check_canaries`` then tells whether a kernel (of this or of another rank: peers store into these
+    buffers) wrote outside a buffer.  The stand-in for a memory checker on the multi-GPU paths; the tests switch it on."""
+    return os.environ.get("OLB_SYMM_CANARY", "0") == "1"
 
 
 class SymmTensor:
     """Local tensor + the addresses of every rank's copy."""
 
-    __slots__ = ("local", "ptrs", "multicast_ptr", "_keep")
+    __slots__ = ("local", "ptrs", "multicast_ptr", "_keep", "_guards")
 
-    def __init__(self, local: torch.Tensor, ptrs: List[int], multicast_ptr: int = 0, keep=None):
+    def __init__(self, local: torch.Tensor, ptrs: List[int], multicast_ptr: int = 0, keep=None, guards=None):
         self.local = local
         self.ptrs = ptrs
         self.multicast_ptr = multicast_ptr
         self._keep = keep
+        self._guards = guards      # (front, back) uint8 views of the guard bands, or None
+
+    def guards_intact(self) -> bool:
+        if self._guards is None:
+            return True
+        return all(bool((g == _CANARY_VALUE).all().item()) for g in self._guards)
 
     def offset_ptrs(self, elem_offset: int) -> List[int]:
         b = elem_offset * self.local.element_size()
@@ -55,10 +70,15 @@ class SymmGroup:
         self.provider = os.environ.get("OLB_SYMM_PROVIDER", "auto")
         self._epochs: Dict[int, int] = {}
         self._named: Dict[str, SymmTensor] = {}
+        self._all: List[SymmTensor] = []
         self.pads = self.empty((_SIGNAL_WORDS,), torch.int32, zero=True)
         # every rank must have zeroed its signal words before anyone signals
         dist.barrier(group=group)
         torch.cuda.synchronize()
+
+    @classmethod
+    def all_canaries_intact(cls) -> bool:
+        return all(g.check_canaries() for g in cls._instances.values())
 
     @classmethod
     def get(cls, group) -> "SymmGroup":
@@ -100,7 +120,7 @@ class SymmGroup:
             ptrs.append(st.data_ptr() + byte_off)
         return SymmTensor(t, ptrs, 0, keep=keep)
 
-    def empty(self, shape, dtype, zero=False) -> SymmTensor:
+    def _alloc(self, shape, dtype) -> SymmTensor:
         st = None
         if self.provider in ("auto", "symm_mem"):
             try:
@@ -112,9 +132,36 @@ class SymmGroup:
                 self.provider = "ipc"
         if st is None:
             st = self._alloc_ipc(tuple(shape), dtype)
+        return st
+
+    def empty(self, shape, dtype, zero=False) -> SymmTensor:
+        if not canaries_enabled():
+            st = self._alloc(shape, dtype)
+        else:
+            # one flat allocation [guard | payload | guard]; the tensor handed out is the payload
+            esz = torch.empty((), dtype=dtype).element_size()
+            numel = 1
+            for d in shape:
+                numel *= int(d)
+            pad = _CANARY_BYTES // esz
+            raw = self._alloc((numel + 2 * pad,), dtype)
+            flat = raw.local
+            bytes_view = flat.view(torch.uint8)
+            front, back = bytes_view[:_CANARY_BYTES], bytes_view[_CANARY_BYTES + numel * esz:]
+            front.fill_(_CANARY_VALUE)
+            back.fill_(_CANARY_VALUE)
+            st = SymmTensor(flat[pad:pad + numel].view(tuple(shape)), [p + _CANARY_BYTES for p in raw.ptrs],
+                            raw.multicast_ptr + _CANARY_BYTES if raw.multicast_ptr else 0, keep=(raw, raw._keep),
+                            guards=(front, back))
         if zero:
             st.local.zero_()
+        self._all.append(st)
         return st
+
+    def check_canaries(self) -> bool:
+        """True when no guard band of this group's buffers has been written (always true without canaries).  Call it
+        after a barrier, when the peers' stores of the step under test are complete."""
+        return all(st.guards_intact() for st in self._all)
 
     def named(self, name: str, shape, dtype, zero=False) -> SymmTensor:
         """Cached symmetric tensor (all ranks must request the same names in the same order)."""

@@ -17,6 +17,10 @@ CSRC = os.path.join("optimus_lm_b200", "csrc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 
+if os.environ.get("OLB_DEBUG_CHECKS", "0") == "1":
+    # index checks that record ST_BAD_ARG instead of faulting (csrc/ptx.cuh: OLB_INDEX_OK)
+    NVCC_FLAGS.append("-DOLB_DEBUG_CHECKS")
+
 cu_sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 cpp_sources = sorted(glob.glob(os.path.join(CSRC, "*.cpp")))
 
@@ -30,6 +34,8 @@ def build_c_library():
         return
     cmd = ["nvcc", "-shared", "-Xcompiler", "-fPIC", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
            "-O3", "-std=c++17", "--expt-relaxed-constexpr", "-o", out] + srcs + ["-lcudart"]
+    if os.environ.get("OLB_DEBUG_CHECKS", "0") == "1":
+        cmd.insert(1, "-DOLB_DEBUG_CHECKS")
     print(" ".join(cmd))
     subprocess.check_call(cmd)
 

@@ -220,3 +220,21 @@ def test_a_rank_that_raises_is_reported_by_the_spawn_helper():
     from dist_utils import run_distributed
     with pytest.raises(AssertionError, match="injected failure on rank 1"):
         run_distributed(_raising_worker, 2)
+
+
+def test_torch_adamw_path_and_hf_model_path():
+    """``--opt_use_pt_optimizer`` (torch.optim.AdamW through the engine) and ``--use_hf_model`` (the transformers
+    implementation built without the hub) both train: the loss of a repeated batch falls."""
+    from optimus_lm_b200.engine import EngineArgs, TrainEngine
+    torch.manual_seed(0)
+    tag = "allenai/OLMoE-1B-7B-0924--L2-SH0.0625-SA0.25-SE0.125-SC0.0625-SI0.125"
+    over = {"vocab_size": 256, "max_position_embeddings": 64}
+    ids = torch.randint(0, 256, (2, 32))
+    for hf in (False, True):
+        eng = TrainEngine(EngineArgs(model_choice=tag, dtype="fp32", batch_size=2, context_size=32, optimizer="pt",
+                                     warmup_steps=0, lr=3e-3, use_hf_model=hf, config_overrides=over))
+        losses = [float(eng.train_step(ids).loss) for _ in range(6)]
+        assert losses[-1] < losses[0] - 0.2, (hf, losses)
+        if hf:
+            import transformers
+            assert isinstance(eng.model, transformers.PreTrainedModel)

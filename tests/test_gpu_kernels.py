@@ -681,3 +681,71 @@ def test_embedding_fwd_bwd(v_start, rows):
     for _ in range(2):
         OF.embedding(ids, w, padding_idx=pad, v_start=v_start).backward(dy)
     assert rel_err(h.buf, 2 * want) < 1e-2
+
+
+# ------------------------------------------------------------------ reference custom-op interface, profiler shim
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_custom_op_kernels_match_their_tensor_programs(dtype):
+    """The CUDA kernels behind the reference's custom-op entry points against the same functions on CPU tensors."""
+    from optimus_lm_b200 import custom_ops as ops
+    torch.manual_seed(0)
+    T, K, E, e0, e1, H = 203, 4, 16, 4, 12, 64
+    sel = torch.stack([torch.randperm(E)[:K] for _ in range(T)]).int()
+    E_loc, TH = e1 - e0, (T + 7) // 8
+
+    def pipeline(dev):
+        s = sel.to(dev)
+        ptc = torch.zeros((E_loc, TH), dtype=torch.int32, device=dev)
+        cnt = torch.zeros(T, dtype=torch.int32, device=dev)
+        ops.compute_partial_token_counts(s, ptc, cnt, e0, e1)
+        pc = torch.zeros(E_loc * TH + 1, dtype=torch.int32, device=dev)
+        pc[1:] = torch.cumsum(ptc.flatten(), 0).int()
+        cum = torch.zeros(T + 1, dtype=torch.int32, device=dev)
+        cum[1:] = torch.cumsum(cnt, 0).int()
+        R = int(pc[-1])
+        sei, ii, oi = (torch.empty(R, dtype=torch.int32, device=dev) for _ in range(3))
+        incr = torch.zeros(E_loc * TH, dtype=torch.int32, device=dev)
+        ops.compute_input_and_output_indices(s, pc, incr, cum, sei, ii, oi, e0, e1)
+        g = torch.Generator().manual_seed(3)
+        x = torch.randn(T, H, generator=g).to(dtype).to(dev)
+        w = torch.rand(T, K, generator=g).to(dtype).to(dev)
+        y = torch.randn(R, H, generator=g).to(dtype).to(dev)
+        dout = torch.randn(T, H, generator=g).to(dtype).to(dev)
+        xg = torch.empty(R, H, dtype=dtype, device=dev)
+        ops.index_gather(x, ii, xg)
+        out = torch.empty(T, H, dtype=dtype, device=dev)
+        ops.reduce_ggemm_output(y, w, cum, sei, oi, out, False)
+        dy = torch.zeros(R, H, dtype=dtype, device=dev)
+        dw = torch.zeros(T, K, dtype=dtype, device=dev)
+        ops.reduce_ggemm_output_backward(dout, y, w, cum, sei, ii, oi, dy, dw)
+        dx = torch.empty(T, H, dtype=dtype, device=dev)
+        ops.shuffle_sub_matrix_reduce(dy, cum, oi, dx)
+        base = torch.zeros(T, H, dtype=dtype, device=dev)
+        ops.index_add_op(y, base, ii)
+        return [t.cpu() for t in (ptc, cnt, sei, ii, oi, xg, out, dy, dw, dx, base)]
+
+    got, want = pipeline("cuda"), pipeline("cpu")
+    for a, b in zip(got[:5], want[:5]):
+        assert torch.equal(a, b)
+    assert torch.equal(got[5], want[5])
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    for a, b in zip(got[6:], want[6:]):
+        assert (a.float() - b.float()).abs().max().item() <= tol * (b.float().abs().max().item() + 1.0)
+    assert OF.check_status("cuda") == 0
+
+
+def test_native_profiler_shim_marks_events_and_times_copies():
+    from optimus_lm_b200.ops import extension
+    C = extension()
+    a = C.mark_event()
+    src = torch.randn(64 * 1024 * 1024 // 4, device="cuda")
+    dst = torch.empty_like(src)
+    cp = C.async_memcpy(src, dst)
+    b = C.mark_event()
+    b.wait()
+    assert torch.equal(src, dst)
+    assert a.get_elapsed_time() >= 0 and a.get_start_time() > 0
+    assert a.get_start_time() <= cp.get_start_time() <= cp.get_end_time() <= b.get_end_time()
+    gbs = 2 * src.numel() * 4 / cp.get_elapsed_time()           # bytes per nanosecond = GB/s
+    assert 100.0 < gbs < 20000.0, gbs
+    assert cp.get_submit_time() > 0

@@ -19,13 +19,15 @@ def _free_port():
 def _worker(rank, world, port, fn_name, args, errq):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
-                      LOCAL_RANK=str(rank))
+                      LOCAL_RANK=str(rank), OLB_SYMM_CANARY="1")     # guard bands around every symmetric buffer
     try:
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
         globals()[fn_name](rank, world, *args)
         dist.barrier()
         torch.cuda.synchronize()
+        from optimus_lm_b200.parallel.symm import SymmGroup
+        assert SymmGroup.all_canaries_intact(), "a kernel wrote outside a symmetric buffer (guard band overwritten)"
     except Exception:
         errq.put((rank, traceback.format_exc()))
     finally:
