@@ -14,8 +14,6 @@ which use blocking ``send``/``recv`` followed by a device synchronise after ever
   because each group has its own communicator and stream, a transfer waits neither for the other
   direction nor for the collectives of the data / expert / tensor parallel groups.  The operations are
   issued through ``batch_isend_irecv``;
-* ``OLB_PP_BLOCKING=1`` restores the reference's behaviour (blocking transfer + device synchronise after each)
-  for A/B measurements of the overlap;
 * the global router auxiliary loss travels as ``2E+2`` running sums forward and the global
   selection fractions (``E`` floats) backward instead of the concatenated router logits and their
   gradients (see ``ops/aux_loss.py``);
@@ -24,7 +22,6 @@ which use blocking ``send``/``recv`` followed by a device synchronise after ever
 """
 from __future__ import annotations
 
-import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -123,7 +120,6 @@ class PipelineExecutor:
             self.pairs = _pair_groups(pmap)
             if self.pairs is None:
                 self.groups = _channel_groups(self.VPP > 1)
-        self.blocking = os.environ.get("OLB_PP_BLOCKING", "0") == "1"
         self.last_virtual = self.PP * self.VPP - 1
         self._pending: List[Tuple[object, torch.Tensor]] = []
 
@@ -168,20 +164,12 @@ class PipelineExecutor:
         dst, group = dst_group
         t = t.contiguous()
         works = dist.batch_isend_irecv([dist.P2POp(dist.isend, t, dst, group)])
-        if self.blocking:
-            for w in works:
-                w.wait()
-            if t.is_cuda:
-                torch.cuda.synchronize()
-            return
         self._pending.extend((w, t) for w in works)
 
     def _recv(self, t, src_group):
         src, group = src_group
         for w in dist.batch_isend_irecv([dist.P2POp(dist.irecv, t, src, group)]):
             w.wait()
-        if self.blocking and t.is_cuda:
-            torch.cuda.synchronize()
         return t
 
     # ------------------------------------------------------------------ model call / router info
