@@ -101,6 +101,9 @@ def cold_checkpoint_name(train_step_id, pmap, batch_size, context_size) -> str:
 def save_checkpoint(exp_dir, model, optimizer, pmap, train_step_id, *, name=None, model_only=False,
                     optimizer_sharded=True, dp_staggered=False, rank=None, verbose=True) -> str:
     """Collective over all ranks.  ``train_step_id`` is the step that just finished."""
+    fused = getattr(optimizer, "_fused", None)
+    if fused is not None and hasattr(fused, "materialize"):
+        fused.materialize()      # weights whose all-gather is pending until their next forward GEMM
     rank = (dist.get_rank() if dist.is_initialized() else 0) if rank is None else rank
     name = choose_checkpoint_for_writing(exp_dir, verbose and rank == 0) if name is None else name
     d = _ckpt_dir(exp_dir, name)

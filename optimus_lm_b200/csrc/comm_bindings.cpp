@@ -394,13 +394,69 @@ void gemm_ep_gather(at::Tensor& xp, const at::Tensor& w2d, at::Tensor& c, int64_
   check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (expert-parallel dispatch variant)");
 }
 
+// dst (a CUDA tensor, contiguous) <- `bytes` bytes at address `src` (possibly another GPU's memory).
+void peer_copy(int64_t src, at::Tensor& dst, int64_t bytes) {
+  c10::cuda::CUDAGuard guard(dst.device());
+  TORCH_CHECK(dst.is_contiguous() && bytes <= static_cast<int64_t>(dst.numel() * dst.element_size()));
+  check(olb_peer_copy(reinterpret_cast<const void*>(static_cast<uintptr_t>(src)), dst.data_ptr(), bytes, cur_stream()),
+        "olb_peer_copy");
+}
+
+// y = x w^T where parts of w are fetched from the peers that own their current values while the GEMM runs (the parameter
+// all-gather of a sharded optimizer step, fused into the first GEMM that consumes the weight).  `w_peers[r]` is the
+// address of w in peer r's memory, `seg` = [lo_0, hi_0, lo_1, hi_1, ...]: elements of w current only on peer r.
+void gemm_b_gather(const at::Tensor& x, at::Tensor& w, at::Tensor& y, int64_t M, int64_t N, int64_t K,
+                   const std::vector<int64_t>& w_peers, const std::vector<int64_t>& seg, int64_t my_peer, at::Tensor& flags,
+                   const c10::optional<at::Tensor>& status) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 &&
+                  y.scalar_type() == at::kBFloat16,
+              "bf16 CUDA operands expected");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2 && x.stride(1) == 1 && w.is_contiguous() && y.stride(1) == 1);
+  TORCH_CHECK(w_peers.size() <= 8 && seg.size() == 2 * w_peers.size() && !w_peers.empty());
+  TORCH_CHECK(flags.scalar_type() == at::kInt && flags.is_contiguous() && flags.numel() >= (N + 127) / 128);
+  c10::cuda::CUDAGuard guard(x.device());
+  flags.zero_();
+  auto wp = cptrs(w_peers);
+  std::vector<long long> sg(seg.begin(), seg.end());
+  olb_gemm_desc d{};
+  d.A = x.data_ptr();
+  d.B = w.data_ptr();
+  d.C = y.data_ptr();
+  d.lda = x.stride(0);
+  d.ldb = w.stride(0);
+  d.ldc = y.stride(0);
+  d.a_rows = x.size(0);
+  d.b_rows = w.size(0);
+  d.M = static_cast<int>(M);
+  d.N = static_cast<int>(N);
+  d.K = static_cast<int>(K);
+  d.mode = OLB_GEMM_DENSE;
+  d.num_experts = 1;
+  d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
+  d.n_peers = static_cast<int>(wp.size());
+  d.my_peer = static_cast<int>(my_peer);
+  d.B_peers = wp.data();
+  d.b_seg = sg.data();
+  d.stage_flags = flags.data_ptr<int>();
+  check(olb_gemm_bf16(&d, cur_stream()), "olb_gemm_bf16 (parameter all-gather variant)");
+}
+
 int64_t rs_adamw_blocks(int64_t n) { return olb_rs_adamw_blocks(n); }
 
 void rs_adamw(const std::vector<int64_t>& peer_grad, const std::vector<int64_t>& peer_param, int64_t shard_off,
               at::Tensor& master, at::Tensor& m, at::Tensor& v, double lr, double beta1, double beta2, double eps,
               double weight_decay, int64_t step, double grad_scale, const c10::optional<at::Tensor>& clip_coef,
-              at::Tensor& norm_partial, int64_t mode, bool skip_weight_update, int64_t mc_grad, int64_t mc_param) {
+              at::Tensor& norm_partial, int64_t mode, bool skip_weight_update, int64_t mc_grad, int64_t mc_param,
+              const c10::optional<at::Tensor>& local_only, int64_t my_rank) {
   c10::cuda::CUDAGuard guard(master.device());
+  const long long* lo_ptr = nullptr;
+  int n_lo = 0;
+  if (local_only.has_value() && local_only->numel() > 0) {
+    TORCH_CHECK(local_only->is_cuda() && local_only->scalar_type() == at::kLong && local_only->is_contiguous() &&
+                local_only->dim() == 2 && local_only->size(1) == 2, "local_only: int64 CUDA tensor [n, 2]");
+    lo_ptr = reinterpret_cast<const long long*>(local_only->data_ptr<int64_t>());
+    n_lo = static_cast<int>(local_only->size(0));
+  }
   olb_adamw_hparams hp;
   hp.lr = static_cast<float>(lr);
   hp.beta1 = static_cast<float>(beta1);
@@ -414,11 +470,12 @@ void rs_adamw(const std::vector<int64_t>& peer_grad, const std::vector<int64_t>&
   auto pg = cptrs(peer_grad);
   auto pp = mptrs(peer_param);
   TORCH_CHECK(norm_partial.numel() >= olb_rs_adamw_blocks(master.numel()), "norm_partial too small");
-  check(olb_rs_adamw_mc(pg.data(), pp.data(), static_cast<int>(pg.size()), shard_off, master.numel(),
+  check(olb_rs_adamw_ex(pg.data(), pp.data(), static_cast<int>(pg.size()), shard_off, master.numel(),
                         master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), &hp,
                         clip_coef.has_value() ? clip_coef->data_ptr<float>() : nullptr, norm_partial.data_ptr<float>(),
                         static_cast<int>(mode), reinterpret_cast<const void*>(static_cast<uintptr_t>(mc_grad)),
-                        reinterpret_cast<void*>(static_cast<uintptr_t>(mc_param)), cur_stream()),
+                        reinterpret_cast<void*>(static_cast<uintptr_t>(mc_param)), lo_ptr, n_lo, static_cast<int>(my_rank),
+                        cur_stream()),
         "olb_rs_adamw");
 }
 
@@ -455,5 +512,8 @@ void register_comm(pybind11::module& m) {
   m.def("rs_adamw", &rs_adamw, py::arg("peer_grad"), py::arg("peer_param"), py::arg("shard_off"), py::arg("master"),
         py::arg("m"), py::arg("v"), py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"),
         py::arg("weight_decay"), py::arg("step"), py::arg("grad_scale"), py::arg("clip_coef"), py::arg("norm_partial"),
-        py::arg("mode"), py::arg("skip_weight_update"), py::arg("mc_grad") = 0, py::arg("mc_param") = 0);
+        py::arg("mode"), py::arg("skip_weight_update"), py::arg("mc_grad") = 0, py::arg("mc_param") = 0,
+        py::arg("local_only") = py::none(), py::arg("my_rank") = 0);
+  m.def("peer_copy", &peer_copy);
+  m.def("gemm_b_gather", &gemm_b_gather);
 }

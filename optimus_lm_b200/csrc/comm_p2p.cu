@@ -282,7 +282,8 @@ __global__ void __launch_bounds__(256)
 rs_adamw_kernel(PeerPtrs peer_grad, PeerPtrsMut peer_param, int n, long long shard_off, long long n_elems,
                 float* __restrict__ master, float* __restrict__ m, float* __restrict__ v, olb_adamw_hparams hp,
                 const float* __restrict__ clip_coef_dev, float* __restrict__ norm_partial, int mode,
-                const __nv_bfloat16* mc_grad, __nv_bfloat16* mc_param) {
+                const __nv_bfloat16* mc_grad, __nv_bfloat16* mc_param, const long long* __restrict__ local_only,
+                int n_local_only, int my_rank) {
   __shared__ float s_red[8];
   const long long begin = static_cast<long long>(blockIdx.x) * RS_ELEMS_PER_BLOCK;
   const long long end = min(begin + RS_ELEMS_PER_BLOCK, n_elems);
@@ -345,7 +346,20 @@ rs_adamw_kernel(PeerPtrs peer_grad, PeerPtrsMut peer_param, int n, long long sha
     o.y = pack_bf16(pp[2], pp[3]);
     o.z = pack_bf16(pp[4], pp[5]);
     o.w = pack_bf16(pp[6], pp[7]);
-    if constexpr (MC) {
+    // ranges whose all-gather is left to the first GEMM that consumes the weight: the update stays on this GPU
+    bool keep_local = false;
+    if (n_local_only > 0) {
+      const long long pos = shard_off + i;
+      int lo = 0, hi = n_local_only;   // last range with start <= pos
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (local_only[2 * mid] <= pos) lo = mid + 1; else hi = mid;
+      }
+      keep_local = lo > 0 && pos < local_only[2 * (lo - 1) + 1];
+    }
+    if (keep_local) {
+      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(peer_param.p[my_rank]) + shard_off + i) = o;
+    } else if constexpr (MC) {
       multimem_st_bf16x8(mc_param + shard_off + i, o);
     } else {
       for (int p = 0; p < n; ++p)
@@ -481,25 +495,53 @@ extern "C" int olb_rs_adamw_blocks(long long n_elems) {
 extern "C" int olb_rs_adamw(const void* const* peer_grad, void* const* peer_param, int n, long long shard_off,
                             long long n_elems, float* master, float* m, float* v, const olb_adamw_hparams* hp,
                             const float* clip_coef_dev, float* norm_partial, int mode, cudaStream_t stream) {
-  return olb_rs_adamw_mc(peer_grad, peer_param, n, shard_off, n_elems, master, m, v, hp, clip_coef_dev, norm_partial, mode,
-                         nullptr, nullptr, stream);
+  return olb_rs_adamw_ex(peer_grad, peer_param, n, shard_off, n_elems, master, m, v, hp, clip_coef_dev, norm_partial, mode,
+                         nullptr, nullptr, nullptr, 0, 0, stream);
 }
 
 extern "C" int olb_rs_adamw_mc(const void* const* peer_grad, void* const* peer_param, int n, long long shard_off,
                                long long n_elems, float* master, float* m, float* v, const olb_adamw_hparams* hp,
                                const float* clip_coef_dev, float* norm_partial, int mode, const void* mc_grad,
                                void* mc_param, cudaStream_t stream) {
+  return olb_rs_adamw_ex(peer_grad, peer_param, n, shard_off, n_elems, master, m, v, hp, clip_coef_dev, norm_partial, mode,
+                         mc_grad, mc_param, nullptr, 0, 0, stream);
+}
+
+// dst[i] = src[i] for `bytes` bytes (multiple of 16, both 16-byte aligned); src may be another GPU's memory.
+__global__ void __launch_bounds__(256) peer_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long vecs) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < vecs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[i] = src[i];
+}
+
+extern "C" int olb_peer_copy(const void* src, void* dst, long long bytes, cudaStream_t stream) {
+  if ((bytes % 16) || ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15)) return -1;
+  if (bytes <= 0) return 0;
+  long long blocks = (bytes / 16 + 255) / 256;
+  if (blocks > sm_count() * 8) blocks = sm_count() * 8;
+  peer_copy_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst),
+                                                                 bytes / 16);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int olb_rs_adamw_ex(const void* const* peer_grad, void* const* peer_param, int n, long long shard_off,
+                               long long n_elems, float* master, float* m, float* v, const olb_adamw_hparams* hp,
+                               const float* clip_coef_dev, float* norm_partial, int mode, const void* mc_grad,
+                               void* mc_param, const long long* local_only, int n_local_only, int my_rank,
+                               cudaStream_t stream) {
   if (n > MAX_PEERS || (n_elems % 8) || (shard_off % 8)) return -1;
+  if (n_local_only > 0 && (local_only == nullptr || my_rank < 0 || my_rank >= n)) return -1;
   if ((mc_grad == nullptr) != (mc_param == nullptr)) return -1;
   if ((reinterpret_cast<uintptr_t>(mc_grad) | reinterpret_cast<uintptr_t>(mc_param)) & 15) return -1;
   if (n_elems <= 0) return 0;
   if (mc_grad)
     rs_adamw_kernel<true><<<olb_rs_adamw_blocks(n_elems), 256, 0, stream>>>(
         to_peers(peer_grad, n), to_peers_mut(peer_param, n), n, shard_off, n_elems, master, m, v, *hp, clip_coef_dev,
-        norm_partial, mode, static_cast<const __nv_bfloat16*>(mc_grad), static_cast<__nv_bfloat16*>(mc_param));
+        norm_partial, mode, static_cast<const __nv_bfloat16*>(mc_grad), static_cast<__nv_bfloat16*>(mc_param), local_only,
+        n_local_only, my_rank);
   else
     rs_adamw_kernel<false><<<olb_rs_adamw_blocks(n_elems), 256, 0, stream>>>(
         to_peers(peer_grad, n), to_peers_mut(peer_param, n), n, shard_off, n_elems, master, m, v, *hp, clip_coef_dev,
-        norm_partial, mode, nullptr, nullptr);
+        norm_partial, mode, nullptr, nullptr, local_only, n_local_only, my_rank);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -119,7 +119,24 @@ struct PeerArg<true> {
   const int* k_of;
   int T, topk;
   long long src_ld;
+  // Parameter all-gather inside the consuming GEMM (push == 4, dense mode, B K-major and contiguous [N, K]): elements
+  // [seg_lo[r], seg_hi[r]) of B (counted from B's first element, multiples of 8) are current only in peer r's copy
+  // src[r]; the stagers copy them into this GPU's B (`dst`) row piece by row piece and count the 16-byte vectors that
+  // have landed per 128-row block of B in `flags`; the producer of a CTA waits until its 128 rows of B are complete.
+  long long seg_lo[8], seg_hi[8];
 };
+
+// 16-byte vectors of rows [blk * 128, blk * 128 + 128) of B [N, K] that the stagers have to bring in (push == 4).
+__device__ __forceinline__ int stale_vectors_in_block(const PeerArg<true>& peers, int blk, int N, int K) {
+  const long long b_lo = static_cast<long long>(blk) * 128 * K;
+  const long long b_hi = static_cast<long long>(min((blk + 1) * 128, N)) * K;
+  long long total = 0;
+  for (int r = 0; r < peers.n; ++r) {
+    const long long lo = max(b_lo, peers.seg_lo[r]), hi = min(b_hi, peers.seg_hi[r]);
+    if (hi > lo) total += (hi - lo) / 8;
+  }
+  return static_cast<int>(total);
+}
 constexpr int STAGER_WARPS = 4;
 constexpr int NUM_THREADS_STAGED = NUM_THREADS + 32 * STAGER_WARPS;
 
@@ -479,6 +496,40 @@ __device__ __forceinline__ void stager_loop(const PeerArg<true>& peers, const Ge
   const long long total = (peers.push == 2 || peers.push == 3)
                               ? min(static_cast<long long>(num_m_blocks) * BLOCK_M, static_cast<long long>(p.M))
                               : static_cast<long long>(peers.n - 1) * peers.rows;
+  if (peers.push == 4) {
+    // -------- parameter all-gather: the parts of B that other GPUs updated, row piece by row piece in row order
+    const long long K = p.K;
+    const long long gw = static_cast<long long>(blockIdx.x) * STAGER_WARPS + swarp;
+    const long long nw = static_cast<long long>(gridDim.x) * STAGER_WARPS;
+    for (int s = 0; s < peers.n; ++s) {
+      if (peers.seg_hi[s] <= peers.seg_lo[s]) continue;
+      const long long r0 = peers.seg_lo[s] / K, r1 = (peers.seg_hi[s] - 1) / K;
+      for (long long r = r0 + gw; r <= r1; r += nw) {
+        const long long lo = max(peers.seg_lo[s], r * K), hi = min(peers.seg_hi[s], (r + 1) * K);
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.src[s]) + lo * 2);
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(peers.dst) + lo * 2);
+        const int vecs = static_cast<int>((hi - lo) / 8);
+        for (int c0 = 0; c0 < vecs; c0 += 256) {
+          uint4 v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int c = c0 + i * 32 + lane;
+            if (c < vecs) v[i] = src[c];
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int c = c0 + i * 32 + lane;
+            if (c < vecs) dst[c] = v[i];
+          }
+        }
+        fence_proxy_async_all();
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(peers.flags + r / BLOCK_M, vecs);
+      }
+    }
+    return;
+  }
   if (peers.push == 3) {
     // -------- expert-parallel dispatch: the routed token rows come from their owners into the grouped operand.
     // A warp takes two consecutive rows per turn (same 128-row block): 16 loads of 16 bytes in flight per lane, and
@@ -955,6 +1006,20 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       for (int t = pair_id; ok && get_tile_pair<EPI>(p, t, num_m, ti); t += num_pairs) {
         const int m0 = ti.m0 + static_cast<int>(rank) * 128;
         if constexpr (PEER) {
+          if (peers.push == 4) {
+            // this CTA's 128 rows of B: wait for the parts that other GPUs own (nothing to wait for once they are in)
+            const int nb = (ti.n0 + static_cast<int>(rank) * 128) / BLOCK_M;
+            if (nb * BLOCK_M < p.N) {
+              const int need = stale_vectors_in_block(peers, nb, p.N, p.K);
+              if (need > 0) {
+                if (!wait_count(peers.flags + nb, need, p.status, abort_flag)) {
+                  ok = false;
+                  break;
+                }
+                fence_proxy_async_all();
+              }
+            }
+          }
           if (peers.push == 3) {
             // the stagers bring this CTA's 128 rows into the local operand (the other CTA waits for its own)
             if (!wait_count(peers.flags + m0 / BLOCK_M, BLOCK_M, p.status, abort_flag)) {
@@ -1339,7 +1404,7 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
                           (epi != OLB_EPI_PLAIN || d->N % 256 == 0 || d->N >= 2048);
   const bool use_pair = pair_kernel_enabled() && pair_shape &&
                         (d->mode == OLB_GEMM_RAGGED_M ? (d->pair_rows != 0 && d->M % 256 == 0)
-                                                      : (d->n_peers == 0 && epi == OLB_EPI_PLAIN));
+                                                      : ((d->n_peers == 0 || d->B_peers != nullptr) && epi == OLB_EPI_PLAIN));
 
   // cuTensorMapEncodeTiled is a driver call and needs a current context in the calling thread.
   // A thread that has only been handed tensors (an autograd worker whose first CUDA work is this
@@ -1495,6 +1560,27 @@ extern "C" int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream) {
       return dispatch<true>(block_n, epi, tm, peers, p, sms, stream);
     }
     if (epi != OLB_EPI_PLAIN) return -14;
+    if (d->B_peers != nullptr) {
+      // Parameter all-gather inside the GEMM: parts of B are fetched from the peers that updated them.
+      if (!use_pair || d->n_peers > 8 || d->mode != OLB_GEMM_DENSE || d->stage_flags == nullptr || d->b_seg == nullptr ||
+          d->b_mn_major || d->ldb != d->K || d->K % 8 || d->A_peers != nullptr || d->C_peers != nullptr)
+        return -17;
+      PeerArg<true> peers{};
+      peers.flags = d->stage_flags;
+      peers.n = d->n_peers;
+      peers.me = d->my_peer;
+      peers.push = 4;
+      peers.dst = const_cast<void*>(d->B);
+      for (int r = 0; r < 8; ++r) {
+        peers.src[r] = d->B_peers[r < d->n_peers ? r : 0];
+        peers.seg_lo[r] = r < d->n_peers ? d->b_seg[2 * r] : 0;
+        peers.seg_hi[r] = r < d->n_peers ? d->b_seg[2 * r + 1] : 0;
+        if ((reinterpret_cast<uintptr_t>(peers.src[r]) & 15) || (peers.seg_lo[r] % 8) || (peers.seg_hi[r] % 8) ||
+            peers.seg_hi[r] > static_cast<long long>(d->N) * d->K || peers.seg_lo[r] < 0)
+          return -17;
+      }
+      return launch_pair<true, EPI_PLAIN>(tm, peers, p, sms, stream);
+    }
     if (d->n_peers > 8 || d->mode != OLB_GEMM_DENSE || d->stage_flags == nullptr || d->a_peer_rows <= 0 ||
         d->a_peer_rows % BLOCK_M || d->my_peer < 0 || d->my_peer >= d->n_peers || d->M != d->n_peers * d->a_peer_rows)
       return -14;

@@ -86,6 +86,13 @@ typedef struct {
   const void* aux_in;
   long long aux_ld;
   float* aux_out;
+  // Parameter all-gather fused into the first GEMM that consumes a weight (DENSE mode, B K-major and contiguous [N, K];
+  // n_peers > 0 with B_peers set): after a sharded optimizer step the elements [b_seg[2r], b_seg[2r+1]) of B (counted
+  // from B's first element, multiples of 8; empty for this GPU itself) are current only in peer r's copy B_peers[r].
+  // Extra warps copy them into B over NVLink while the tiles whose rows of B are already complete run; stage_flags
+  // (one int per 128 rows of B, zero at launch) counts the 16-byte vectors landed.  B is complete when the launch ends.
+  const void* const* B_peers;
+  const long long* b_seg;    // host array [2 * n_peers]
 } olb_gemm_desc;
 
 int olb_gemm_bf16(const olb_gemm_desc* d, cudaStream_t stream);
@@ -279,6 +286,15 @@ int olb_rs_adamw_blocks(long long n_elems);
 int olb_rs_adamw_mc(const void* const* peer_grad, void* const* peer_param, int n, long long shard_off, long long n_elems,
                     float* master, float* m, float* v, const olb_adamw_hparams* hp, const float* clip_coef_dev,
                     float* norm_partial, int mode, const void* mc_grad, void* mc_param, cudaStream_t stream);
+// The same with ranges of the flat buffer whose updated parameters stay on this GPU (`local_only`: device array of
+// n_local_only sorted, disjoint [start, end) pairs in elements of the flat buffer): their all-gather is left to the first
+// GEMM that consumes the weight (olb_gemm_desc.B_peers).  my_rank = this GPU's index in peer_param.
+int olb_rs_adamw_ex(const void* const* peer_grad, void* const* peer_param, int n, long long shard_off, long long n_elems,
+                    float* master, float* m, float* v, const olb_adamw_hparams* hp, const float* clip_coef_dev,
+                    float* norm_partial, int mode, const void* mc_grad, void* mc_param, const long long* local_only,
+                    int n_local_only, int my_rank, cudaStream_t stream);
+// dst <- src, `bytes` a multiple of 16; src may point into another GPU's memory.
+int olb_peer_copy(const void* src, void* dst, long long bytes, cudaStream_t stream);
 
 // ---------------------------------------------------------------- attention (attention.cu)
 // Causal flash attention forward, bf16, q/k/v as [B, S, H, D] with arbitrary token/head strides

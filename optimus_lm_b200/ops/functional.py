@@ -137,7 +137,15 @@ class _LinearFn(torch.autograd.Function):
         # the result is allocated in its final shape: a view made inside the function could not be modified in
         # place by a later op (the in-place RoPE kernel works on projection outputs)
         y = torch.empty((*x.shape[:-1], N), dtype=x.dtype, device=x.device)
-        gemm(x2, w, M, N, K, out=y.view(M, N))
+        lazy = getattr(w, "_olb_lazy", None)
+        if lazy is not None and lazy.stale:
+            # the other ranks' updated parts of this weight come in inside this launch (parameter all-gather fused
+            # into the first consuming GEMM), or by a plain copy when the shape is not one the fused launch takes
+            if not lazy.gather_gemm(x2, w, y.view(M, N)):
+                lazy.materialize(w)
+                gemm(x2, w, M, N, K, out=y.view(M, N))
+        else:
+            gemm(x2, w, M, N, K, out=y.view(M, N))
         ctx.save_for_backward(x2, w)
         ctx.x_shape = x.shape
         ctx.holder = holder
@@ -166,6 +174,9 @@ def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """``x @ w.T`` for a bias-free projection (reference: nn.Linear -> oneDNN)."""
     if _kernel_ok(x, w) and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0:
         return _LinearFn.apply(x, w, _holder(w))
+    lazy = getattr(w, "_olb_lazy", None)
+    if lazy is not None and lazy.stale:
+        lazy.materialize(w)
     return F.linear(x, w)
 
 

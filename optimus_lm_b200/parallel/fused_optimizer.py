@@ -7,7 +7,10 @@ gradient and parameter buffers are moved into symmetric memory.  One kernel
     load the shard of every peer's gradient buffer over NVLink -> sum in fp32 (reduce-scatter; with NVLS one
     ``multimem.ld_reduce`` per 16 bytes does the sum in the switch, and one ``multimem.st`` the all-gather below)
     -> scale by 1/N -> norm partial -> AdamW on the fp32 master / moments
-    -> store the updated bf16 parameters into every peer's parameter buffer (all-gather)
+    -> store the updated bf16 parameters into every peer's parameter buffer (all-gather); the attention
+       projections and the LM head are left out of this push: every rank fetches the other ranks' parts of such a
+       weight inside the first GEMM that consumes it in the next forward (``LazyWeight``), where the transfer
+       runs underneath the tiles
 
 which replaces ``reduce_scatter_tensor`` + division + ``get_total_norm`` + ~12 elementwise kernels
 + ``all_gather_into_tensor`` of the reference (optimus/optimizers.py:354-494, 704-928).  Two
@@ -22,7 +25,8 @@ fused pass follows with the coefficient, at the cost of reading the peers' gradi
 from __future__ import annotations
 
 import os
-from typing import Dict, Optional
+import re
+from typing import Dict, List, Optional
 
 import torch
 
@@ -37,6 +41,57 @@ def use_multimem(group_size: int) -> bool:
     one (measured 2.69 ms against 1.71 ms for 512 Mi parameters); with n ranks plain loads move n - 1 copies."""
     v = os.environ.get("OLB_MULTIMEM", "auto")
     return group_size >= 4 if v == "auto" else v != "0"
+
+
+_LAZY_NAME = re.compile(r"(^|\.)(q_proj|k_proj|v_proj|o_proj)\.weight$|^lm_head\.weight$")
+
+
+def lazy_gather_enabled() -> bool:
+    """``OLB_PARAM_AG`` = ``gemm`` (default): the all-gather of the attention projections' and the LM head's updated
+    weights is left to the first GEMM that consumes them; ``push``: the update kernel stores every parameter into every
+    rank's buffer."""
+    return os.environ.get("OLB_PARAM_AG", "gemm") == "gemm"
+
+
+class LazyWeight:
+    """A weight matrix whose all-gather after a sharded optimizer step happens inside the first GEMM that consumes it.
+
+    After the step only the owner of each shard holds the updated values of its part of ``w`` (``segments[r]`` = the
+    element range of ``w`` that is current only on rank ``r``).  ``ops.functional.linear`` asks ``gather_gemm`` for the
+    forward product while ``stale`` is set: extra warps of that launch copy the segments in over NVLink while tiles whose
+    rows of ``w`` are complete already run.  Any other reader calls ``materialize`` first (a plain peer copy)."""
+
+    __slots__ = ("w_ptrs", "segments", "rank", "stale", "numel")
+
+    def __init__(self, w_ptrs, segments, rank, numel):
+        self.w_ptrs, self.segments, self.rank, self.numel = list(w_ptrs), list(segments), rank, numel
+        self.stale = False
+
+    def _flat_segments(self):
+        out = []
+        for lo, hi in self.segments:
+            out += [lo, hi]
+        return out
+
+    def gather_gemm(self, x2, w, y2) -> bool:
+        """``y2 = x2 @ w.T`` with the gather inside; False when the shape is not one the fused launch takes."""
+        M, K = x2.shape
+        N = w.shape[0]
+        if not (w.is_contiguous() and M >= 256 and K % 64 == 0 and (N % 256 == 0 or N >= 2048)
+                and os.environ.get("OLB_GEMM_PAIR", "1") != "0"):
+            return False
+        extension().gemm_b_gather(x2, w, y2, M, N, K, self.w_ptrs, self._flat_segments(), self.rank,
+                                  OF.stage_flags(w.device, N), OF.status_word(w.device))
+        self.stale = False
+        return True
+
+    def materialize(self, w):
+        C = extension()
+        flat = w.view(-1)
+        for r, (lo, hi) in enumerate(self.segments):
+            if hi > lo:
+                C.peer_copy(self.w_ptrs[r] + 2 * lo, flat[lo:hi], 2 * (hi - lo))
+        self.stale = False
 
 
 def slices_aligned(families) -> bool:
@@ -74,7 +129,49 @@ class FusedShardedStep:
             opt._alias_single()
         else:
             opt._alias_pair()
+        self.lazy: Dict[int, List] = {}          # family -> [(param, LazyWeight)]
+        self.local_only: Dict[int, torch.Tensor] = {}
+        if lazy_gather_enabled():
+            self._setup_lazy(opt)
         torch.cuda.synchronize()
+
+    def _setup_lazy(self, opt):
+        """Pick the weights whose all-gather moves into their first consuming GEMM: 2D projections that
+        ``ops.functional.linear`` consumes (attention q / k / v / o, LM head) of families with one sharded slice."""
+        names = {id(p): n for n, p in opt.model.named_parameters()} if getattr(opt, "model", None) is not None else {}
+        for fi, fam in enumerate(opt.families):
+            if fi not in self.sym or len(fam.slices) != 1:
+                continue
+            sg = self.groups[fi]
+            n, part = sg.size, fam.slices[0].part
+            ranges, entries = [], []
+            for p, start, size in zip(fam.spec.params, fam.param_start_inds, fam.param_sizes):
+                name = names.get(id(p), "")
+                if p.dim() != 2 or not _LAZY_NAME.search(name) or start % 8 or size % 8 or p.shape[1] % 64:
+                    continue
+                if not (p.shape[0] % 256 == 0 or p.shape[0] >= 2048):
+                    continue
+                segs = []
+                for r in range(n):   # the part of [start, start + size) that rank r owns, relative to the weight
+                    lo, hi = max(start, r * part), min(start + size, (r + 1) * part)
+                    segs.append((lo - start, hi - start) if (hi > lo and r != sg.rank) else (0, 0))
+                if not any(hi > lo for lo, hi in segs):
+                    continue             # the whole weight is this rank's own
+                lw = LazyWeight(self.sym[fi]["param"].offset_ptrs(start), segs, sg.rank, size)
+                p._olb_lazy = lw
+                entries.append((p, lw))
+                ranges.append((start, start + size))
+            if entries:
+                self.lazy[fi] = entries
+                self.local_only[fi] = torch.tensor(sorted(ranges), dtype=torch.int64, device=self.device)
+
+    def materialize(self):
+        """Bring every weight whose gather is still pending up to date (before anything but a forward GEMM reads the
+        parameters: checkpoints, evaluation code that bypasses ``ops.functional.linear``)."""
+        for entries in self.lazy.values():
+            for p, lw in entries:
+                if lw.stale:
+                    lw.materialize(p.data)
 
     @staticmethod
     def try_create(opt) -> Optional["FusedShardedStep"]:
@@ -137,7 +234,8 @@ class FusedShardedStep:
                         mcg, mcp = self._multicast(fi)
                         C.rs_adamw(self.sym[fi]["grad"].ptrs, self.sym[fi]["param"].ptrs, lo, fam.master[s0:s1],
                                    fam.exp_avg[s0:s1], fam.exp_avg_sq[s0:s1], lr, beta1, beta2, eps, wd, step_no, scale,
-                                   clip_coef, partial, mode, opt.skip_optimizer_step_weight_update, mcg, mcp)
+                                   clip_coef, partial, mode, opt.skip_optimizer_step_weight_update, mcg, mcp,
+                                   self.local_only.get(fi), self.groups[fi].rank)
                         if clip_coef is None:
                             total_sq.add_(partial.sum())
                     else:
@@ -163,4 +261,8 @@ class FusedShardedStep:
 
         for sg in {id(g): g for g in self.groups.values()}.values():
             sg.barrier(9)  # parameters written everywhere, gradients consumed everywhere
+        if not opt.skip_optimizer_step_weight_update:
+            for entries in self.lazy.values():      # their other ranks' parts arrive with the next forward's GEMMs
+                for _p, lw in entries:
+                    lw.stale = True
         return grad_norm

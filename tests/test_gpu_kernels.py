@@ -439,6 +439,34 @@ def test_bounded_peer_wait_times_out_without_hanging():
     assert OF.check_status("cuda") == 0
 
 
+@pytest.mark.parametrize("M,N,K,n", [(512, 512, 256, 2), (1024, 2304, 512, 4), (256, 2048, 2048, 8)])
+def test_gemm_with_fused_parameter_all_gather(M, N, K, n):
+    """y = x w^T where only this rank's part of w is current locally: the other parts are fetched from their owners'
+    copies (standing in this GPU's memory) inside the launch, and w is complete afterwards."""
+    from optimus_lm_b200.ops import extension
+    me = 1 % n
+    x = bf(M, K, seed=1)
+    w_true = bf(N, K, seed=2, scale=0.05)
+    part = (N * K // n + 511) // 512 * 512            # shard boundaries like the flat optimizer's: multiples of 512 elements
+    copies, seg = [], []
+    w_local = torch.full((N, K), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for r in range(n):
+        lo, hi = min(r * part, N * K), min((r + 1) * part, N * K)
+        c = torch.full((N * K,), float("nan"), dtype=torch.bfloat16, device="cuda")
+        c[lo:hi] = w_true.view(-1)[lo:hi]             # rank r holds the current values of its own shard only
+        copies.append(c)
+        if r == me:
+            w_local.view(-1)[lo:hi] = w_true.view(-1)[lo:hi]
+            seg += [0, 0]
+        else:
+            seg += [lo, hi]
+    y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    extension().gemm_b_gather(x, w_local, y, M, N, K, [c.data_ptr() for c in copies], seg, me,
+                              OF.stage_flags(x.device, N), OF.status_word("cuda"))
+    assert torch.equal(w_local, w_true)
+    assert torch.equal(y, OF.gemm(x, w_true, M, N, K))
+
+
 def test_exact_row_count_sizes_the_expert_buffers():
     """With ``exact`` the activation buffers follow the routed count, not the worst case, and nothing is dropped."""
     n, T, E_loc, K = 8, 1024, 4, 2
