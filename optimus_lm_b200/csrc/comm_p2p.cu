@@ -291,10 +291,28 @@ rs_adamw_kernel(PeerPtrs peer_grad, PeerPtrsMut peer_param, int n, long long sha
   const float inv_bc1 = 1.f / hp.bias_correction1, inv_bc2 = 1.f / hp.bias_correction2;
   const float decay = -hp.lr * hp.weight_decay;
   float sq = 0.f;
-  for (long long i = begin + threadIdx.x * 8; i < end; i += 256 * 8) {
+  // NVLS: a reduced load makes a round trip through the switch, so four of them are issued ahead of their use
+  constexpr int MC_DEPTH = 4;
+  uint4 pre[MC_DEPTH];
+  if constexpr (MC) {
+#pragma unroll
+    for (int u = 0; u < MC_DEPTH; ++u) {
+      const long long j = begin + threadIdx.x * 8 + static_cast<long long>(u) * 256 * 8;
+      if (j < end) pre[u] = multimem_ld_reduce_bf16x8(mc_grad + shard_off + j);
+    }
+  }
+  int turn = 0;
+  for (long long i = begin + threadIdx.x * 8; i < end; i += 256 * 8, ++turn) {
     float g[8];
     if constexpr (MC) {
-      const uint4 t = multimem_ld_reduce_bf16x8(mc_grad + shard_off + i);
+      uint4 t = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < MC_DEPTH; ++u)
+        if ((turn % MC_DEPTH) == u) {
+          t = pre[u];
+          const long long j = i + static_cast<long long>(MC_DEPTH) * 256 * 8;   // refill this slot for a later turn
+          if (j < end) pre[u] = multimem_ld_reduce_bf16x8(mc_grad + shard_off + j);
+        }
       float2 a;
       a = unpack_bf16(t.x); g[0] = a.x; g[1] = a.y;
       a = unpack_bf16(t.y); g[2] = a.x; g[3] = a.y;

@@ -169,6 +169,8 @@ def w_fused_optimizer_vs_nccl(rank, world):
     from optimus_lm_b200.engine import EngineArgs, TrainEngine
     from optimus_lm_b200.ops import functional as OF
     losses = {}
+    os.environ["OLB_PARAM_AG"] = "gemm"      # also the parameter all-gather inside the consuming GEMM (off by default)
+    os.environ["OLB_MULTIMEM"] = "1" if world >= 4 else "0"     # and, from 4 ranks, the NVLS form of the update kernel
     for fused in (False, True):
         args = EngineArgs(model_choice="allenai/OLMoE-1B-7B-0924--L2-SH0.125-SA0.25-SE0.125-SC0.25-SI0.5",
                           batch_size=2, context_size=128, optimizer="pgshard", warmup_steps=2, expert_parallelism=world,
