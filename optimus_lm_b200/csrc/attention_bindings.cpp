@@ -16,7 +16,7 @@ void check4(const at::Tensor& t, const char* name) {
 }
 
 void attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at::Tensor& o, at::Tensor& lse,
-              double scale, const c10::optional<at::Tensor>& status) {
+              double scale, const c10::optional<at::Tensor>& status, int64_t variant) {
   check4(q, "q");
   check4(k, "k");
   check4(v, "v");
@@ -41,6 +41,7 @@ void attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at:
   d.Dv = static_cast<int>(v.size(3));
   d.scale = static_cast<float>(scale);
   d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
+  d.variant = static_cast<int>(variant);
   const int rc = olb_attn_fwd(&d, cur_stream());
   TORCH_CHECK(rc == 0, "olb_attn_fwd failed with code ", rc);
 }
@@ -50,6 +51,7 @@ void attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at:
 void register_attention_bwd(pybind11::module& m);
 
 void register_attention(pybind11::module& m) {
-  m.def("attn_fwd", &attn_fwd);
+  m.def("attn_fwd", &attn_fwd, pybind11::arg("q"), pybind11::arg("k"), pybind11::arg("v"), pybind11::arg("o"),
+        pybind11::arg("lse"), pybind11::arg("scale"), pybind11::arg("status"), pybind11::arg("variant") = 0);
   register_attention_bwd(m);
 }

@@ -310,6 +310,7 @@ typedef struct {
   int B, S, Hq, Hkv, D, Dv;
   float scale;
   int* status;
+  int variant;  // 0: the kernel the library prefers for the shape; 1: one query tile per CTA; 2: two (S % 256 == 0)
 } olb_attn_fwd_desc;
 int olb_attn_fwd(const olb_attn_fwd_desc* d, cudaStream_t stream);
 

@@ -334,6 +334,49 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Three-input maximum and the packed two-wide fp32 operations of sm_100 (one instruction, two results per lane).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  unsigned long long ra, rb, rc, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  unsigned long long ra, rb, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+// 2^t for a pair of arguments on the FMA pipe instead of the special-function unit: t = n + f with n the nearest
+// integer (magic-number rounding) and f in [-0.5, 0.5], 2^f by a cubic (relative error < 7e-4, below the rounding of
+// a bf16 result), n added into the exponent field.  Arguments below -126 are clamped (result ~1e-38).
+__device__ __forceinline__ float2 ex2_poly2(float2 t) {
+  const float2 magic = make_float2(12582912.f, 12582912.f);  // 1.5 * 2^23
+  t.x = fmaxf(t.x, -126.f);
+  t.y = fmaxf(t.y, -126.f);
+  const float2 z = add2(t, magic);
+  const float2 n = add2(z, make_float2(-12582912.f, -12582912.f));
+  const float2 f = fma2(n, make_float2(-1.f, -1.f), t);
+  float2 q = fma2(f, make_float2(0.0555041f, 0.0555041f), make_float2(0.2402265f, 0.2402265f));
+  q = fma2(q, f, make_float2(0.6931472f, 0.6931472f));
+  q = fma2(q, f, make_float2(1.f, 1.f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(z.x) << 23));
+  r.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(z.y) << 23));
+  return r;
+}
 __device__ __forceinline__ float2 unpack_bf16(uint32_t v) {
   __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&v);
   return __bfloat1622float2(b);

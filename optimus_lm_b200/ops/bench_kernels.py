@@ -109,6 +109,13 @@ def bench_attention():
         fl = 2.0 * B * Hh * S * S * (D + Dv) / 2
         t1 = _time(lambda: OA.flash_attention(q, k, v))
         msg = f"attention fwd B{B} S{S} H{Hh} D{D}/{Dv}: kernel {t1:.3f} ms ({fl / t1 * 1e-9:.0f} TFLOP/s)"
+        C = OF.extension()
+        o_ = torch.empty(B, S, Hh, Dv, dtype=torch.bfloat16, device="cuda")
+        lse_ = torch.empty(B, Hh, S, dtype=torch.float32, device="cuda")
+        st_ = OF.status_word(q.device)
+        for variant, label in ((1, "one query tile per CTA"), (2, "two query tiles per CTA")):
+            tv = _time(lambda: C.attn_fwd(q, k, v, o_, lse_, D ** -0.5, st_, variant))
+            msg += f" | {label} {tv:.3f} ms ({fl / tv * 1e-9:.0f} TFLOP/s)"
         if D == Dv:
             qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
             t2 = _time(lambda: F.scaled_dot_product_attention(qh, kh, vh, is_causal=True))

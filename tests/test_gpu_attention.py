@@ -32,6 +32,29 @@ def test_flash_attention_forward(B, S, Hq, Hkv, D, Dv):
     assert OF.check_status("cuda") == 0
 
 
+@pytest.mark.parametrize("B,S,Hq,Hkv,D,Dv", [(1, 256, 1, 1, 128, 128), (2, 2048, 4, 2, 128, 128), (1, 1280, 2, 2, 64, 64),
+                                             (1, 768, 2, 2, 192, 128)])
+def test_flash_attention_forward_two_tile_kernel(B, S, Hq, Hkv, D, Dv):
+    # the kernel with two query tiles per CTA against the fp32 oracle (element-wise as well as in norm) and against
+    # the single-tile kernel, output and log-sum-exp; long sequences wrap the K/V ring several times
+    q, k, v = _mk(B, S, Hq, Hkv, D, Dv, seed=7)
+    scale = D ** -0.5
+    C = OF.extension()
+    outs = []
+    for variant in (1, 2):
+        o = torch.empty(B, S, Hq, Dv, dtype=torch.bfloat16, device="cuda")
+        lse = torch.empty(B, Hq, S, dtype=torch.float32, device="cuda")
+        C.attn_fwd(q, k, v, o, lse, scale, OF.status_word("cuda"), variant)
+        outs.append((o, lse))
+    assert OF.check_status("cuda") == 0
+    ref = OF.attention_reference(q.float(), k.float(), v.float(), scale, True)
+    o2, lse2 = outs[1]
+    assert _rel(o2, ref) < 2e-2, _rel(o2, ref)
+    assert (o2.float() - ref).abs().max().item() < 4e-2
+    assert (o2.float() - outs[0][0].float()).abs().max().item() < 2e-2
+    assert (lse2 - outs[0][1]).abs().max().item() < 1e-3
+
+
 def test_flash_attention_strided_views_and_lse():
     # q/k/v as slices of wider tensors (the MLA layout) and the saved log-sum-exp
     B, S, H = 1, 256, 2
