@@ -1,13 +1,14 @@
 // Causal flash-attention backward for sm_100a (tcgen05 + TMEM), deterministic: every gradient element has
 // exactly one writer, no atomics.
 //
-//   delta kernel : delta[b,h,s] = sum_d dO*O  and  lse2 = lse * log2(e)            (one warp per row)
+//   delta kernel : delta[b,h,s] = sum_d dO*O  and  lse2 = lse * log2(e), both stored negated   (one warp per row)
 //   dK/dV kernel : one CTA per (batch, kv head, 128-row key tile); K and V tiles stay in shared memory,
 //                  64-row Q / dO tiles of every query head of the group stream through a TMA ring:
 //                    S^T = K Q^T, dP^T = V dO^T            (UMMA 128x64x16 into TMEM)
 //                    P^T = exp2(S^T*c - lse2[q]),  dS^T = P^T o (dP^T - delta[q])   (8 warps, two threads per key row)
-//                    dV += P^T dO,  dK += dS^T Q          (A = bf16 tiles written to swizzled shared memory,
-//                                                          B = the streamed tile read MN-major)
+//                    dV += P^T dO,  dK += dS^T Q          (A = packed bf16 written back over the start of each
+//                                                          thread's own score columns in TMEM, B = the streamed
+//                                                          tile read MN-major)
 //   dQ kernel    : one CTA per (batch, head, 128-row query tile); Q and dO stay, 64-row K / V tiles stream:
 //                    S = Q K^T, dP = dO V^T, dS = P o (dP - delta[q]), dQ += dS K
 // Both are one template: a resident pair R1/R2 (128 rows), a streamed pair T1/T2 (64 rows), X = R1 T1^T,
@@ -18,6 +19,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cfloat>
 #include <cstdint>
 
 #include "olb_api.h"
@@ -33,24 +35,25 @@ constexpr int BW_T = 64;   // streamed rows per step
 
 template <int D1, int D2, bool KV_MODE>
 struct BwdCfg {
-  static constexpr int NB = (KV_MODE && D1 > 128) ? 1 : 2;  // score / dS buffers
-  static constexpr int TS = (D1 > 128) ? 2 : 3;               // stages of the streamed-tile ring
+  static constexpr int NB = (KV_MODE && D1 > 128) ? 1 : 2;  // score / dS buffers (TMEM)
   // Recompute warps: NG warps share each group of 32 rows (TMEM lanes) and split the 64 columns of a tile.  The
-  // per-tile chain (wait, TMEM read, exp, shared-memory write, signal) is latency-bound, so more warps with less
+  // per-tile chain (wait, TMEM read, exp, TMEM write, signal) is latency-bound, so more warps with less
   // work each hide it better: four per lane group where the epilogue's 32-column pieces allow it.
   static constexpr int NG = (D1 == 128 && D2 == 128) ? 4 : 2;
   static constexpr int THREADS = 64 + 128 * NG;                // TMA warp, MMA warp, 4 * NG recompute warps
   static constexpr int R1_BYTES = BW_R * D1 * 2, R2_BYTES = BW_R * D2 * 2;
   static constexpr int T1_BYTES = BW_T * D1 * 2, T2_BYTES = BW_T * D2 * 2;
-  static constexpr int DS_BYTES = BW_R * BW_T * 2;
+  // P and dS live in TMEM, so all of shared memory beyond the resident pair is the ring of streamed tiles: a tile
+  // is requested one ring length ahead, and the load latency under load is more than one iteration
+  static constexpr int TS_FIT = (232448 - 256 - 1024 - R1_BYTES - R2_BYTES) / (T1_BYTES + T2_BYTES);
+  static constexpr int TS = TS_FIT > 6 ? 6 : TS_FIT;           // stages of the streamed-tile ring
   static constexpr int OFF_R1 = 0;
   static constexpr int OFF_R2 = OFF_R1 + R1_BYTES;
   static constexpr int OFF_T1 = OFF_R2 + R2_BYTES;
   static constexpr int OFF_T2 = OFF_T1 + TS * T1_BYTES;
-  static constexpr int OFF_DS = OFF_T2 + TS * T2_BYTES;
-  static constexpr int OFF_P = OFF_DS + NB * DS_BYTES;
-  static constexpr int OFF_BAR = OFF_P + (KV_MODE ? NB * DS_BYTES : 0);
+  static constexpr int OFF_BAR = OFF_T2 + TS * T2_BYTES;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+  static_assert(TS >= 2, "ring depth");
   static constexpr uint32_t TM_X = 0, TM_Y = BW_T * NB, TM_ACC1 = 2 * BW_T * NB;
   static constexpr uint32_t TM_ACC2 = KV_MODE ? TM_ACC1 + 128 : TM_ACC1;
   static_assert(TM_ACC2 + D1 <= 512 && D2 <= 128, "TMEM columns");
@@ -58,8 +61,8 @@ struct BwdCfg {
 };
 
 struct AttnBwdParams {
-  const float* lse2;   // [B, Hq, S] log-sum-exp in base 2
-  const float* delta;  // [B, Hq, S]
+  const float* lse2;   // [B, Hq, S] minus the log-sum-exp in base 2
+  const float* delta;  // [B, Hq, S] minus delta
   __nv_bfloat16 *out1, *out2;  // key mode: dV, dK; query mode: unused, dQ
   long long o1_bs, o1_ss, o1_hs, o2_bs, o2_ss, o2_hs;
   int B, S, Hq, Hkv;
@@ -67,8 +70,7 @@ struct AttnBwdParams {
   int* status;
 };
 
-enum { BB_R = 0, BB_T_FULL0 = 1, BB_T_EMPTY0 = 4, BB_XY_FULL0 = 7, BB_XY_EMPTY0 = 9, BB_DS_FULL0 = 11, BB_DS_EMPTY0 = 13,
-       BB_ACC = 15, BB_COUNT = 16 };
+enum { BB_R = 0, BB_T_FULL0 = 1, BB_T_EMPTY0 = 7, BB_XY_FULL0 = 13, BB_DS_FULL0 = 15, BB_ACC = 17, BB_COUNT = 18 };
 
 template <int D1, int D2, bool KV_MODE>
 __global__ void __launch_bounds__((BwdCfg<D1, D2, KV_MODE>::THREADS), 1)
@@ -99,15 +101,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
 
   if (threadIdx.x == 0) {
     mbar_init(bar(BB_R), 1);
-    for (int s = 0; s < 3; ++s) {
+    for (int s = 0; s < 6; ++s) {
       mbar_init(bar(BB_T_FULL0 + s), 1);
       mbar_init(bar(BB_T_EMPTY0 + s), 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(BB_XY_FULL0 + s), 1);
-      mbar_init(bar(BB_XY_EMPTY0 + s), 4 * L::NG);
       mbar_init(bar(BB_DS_FULL0 + s), 4 * L::NG);
-      mbar_init(bar(BB_DS_EMPTY0 + s), 1);
     }
     mbar_init(bar(BB_ACC), 1);
     *abort_flag = 0;
@@ -159,50 +159,52 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
       const uint32_t idesc_a2 = make_idesc_bf16(BW_R, D1, 0, 1);
       bool ok = mbar_wait(bar(BB_R), 0, p.status, ST_TIMEOUT_FULL, abort_flag);
       tc_fence_after();
-      // acc += (P | dS)(u) x streamed tile of iteration u, then release that tile and the dS buffer
+      // Descriptors: the fields other than the start address are constant, and shared memory ends below 256 KB, so
+      // moving a descriptor by a byte offset is one add on its low word.
+      auto desc_at = [](uint64_t d, uint32_t byte_off) { return d + (byte_off >> 4); };
+      const uint64_t dr1 = make_smem_desc(base + L::OFF_R1, 16, 1024), dr2 = make_smem_desc(base + L::OFF_R2, 16, 1024);
+      constexpr int CPT = BW_T / L::NG;  // columns per recompute thread
+      // column, inside a score buffer, of the packed bf16 of K step k (16 elements): the start of the owning
+      // thread's own columns
+      auto a_col = [](int k) { return static_cast<uint32_t>(((16 * k) / CPT) * CPT + ((16 * k) % CPT) / 2); };
+      // acc += (P | dS)(u) x streamed tile of iteration u (A read from TMEM), then release that tile
       auto issue_acc = [&](int u) -> bool {
         const int s = u % NB, st = u % TS;
         if (!mbar_wait(bar(BB_DS_FULL0 + s), (u / NB) & 1u, p.status, ST_TIMEOUT_FULL, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t t1 = base + L::OFF_T1 + st * L::T1_BYTES, t2 = base + L::OFF_T2 + st * L::T2_BYTES;
+        const uint64_t dt1 = make_smem_desc(base + L::OFF_T1 + st * L::T1_BYTES, BW_T * 128, 1024);
+        const uint64_t dt2 = make_smem_desc(base + L::OFF_T2 + st * L::T2_BYTES, BW_T * 128, 1024);
 #pragma unroll
         for (int k = 0; k < BW_T / 16; ++k) {
-          if (KV_MODE) {
-            const uint64_t da = make_smem_desc(base + L::OFF_P + s * L::DS_BYTES + k * 32, 16, 1024);
-            const uint64_t db = make_smem_desc(t2 + k * 2048, BW_T * 128, 1024);
-            umma_ss(tmem + L::TM_ACC1, da, db, idesc_a1, (u > 0 || k > 0) ? 1u : 0u);
-          }
-          const uint64_t da = make_smem_desc(base + L::OFF_DS + s * L::DS_BYTES + k * 32, 16, 1024);
-          const uint64_t db = make_smem_desc(t1 + k * 2048, BW_T * 128, 1024);
-          umma_ss(tmem + L::TM_ACC2, da, db, idesc_a2, (u > 0 || k > 0) ? 1u : 0u);
+          if (KV_MODE)
+            umma_ts(tmem + L::TM_ACC1, tmem + L::TM_X + s * BW_T + a_col(k), desc_at(dt2, k * 2048), idesc_a1,
+                    (u > 0 || k > 0) ? 1u : 0u);
+          umma_ts(tmem + L::TM_ACC2, tmem + L::TM_Y + s * BW_T + a_col(k), desc_at(dt1, k * 2048), idesc_a2,
+                  (u > 0 || k > 0) ? 1u : 0u);
         }
         umma_commit(bar(BB_T_EMPTY0 + st));
-        umma_commit(bar(BB_DS_EMPTY0 + s));
         return true;
       };
       for (int it = 0; ok && it < n_iter; ++it) {
         const int s = it % NB, st = it % TS;
+        // One score buffer: the products of the previous tile read P and dS from it, so they go first.  Two: the
+        // buffer of tile it held P and dS of tile it-2, whose products were issued in the previous turn, and the
+        // tcgen05.mma of one thread execute in issue order.
+        if (NB == 1 && it >= 1 && !issue_acc(it - 1)) { ok = false; break; }
         if (!mbar_wait(bar(BB_T_FULL0 + st), (it / TS) & 1u, p.status, ST_TIMEOUT_FULL, abort_flag)) { ok = false; break; }
-        if (it >= NB && !mbar_wait(bar(BB_XY_EMPTY0 + s), ((it / NB) - 1) & 1u, p.status, ST_TIMEOUT_ACC_EMPTY, abort_flag)) {
-          ok = false;
-          break;
-        }
         tc_fence_after();
-        const uint32_t t1 = base + L::OFF_T1 + st * L::T1_BYTES, t2 = base + L::OFF_T2 + st * L::T2_BYTES;
+        const uint64_t dt1 = make_smem_desc(base + L::OFF_T1 + st * L::T1_BYTES, 16, 1024);
+        const uint64_t dt2 = make_smem_desc(base + L::OFF_T2 + st * L::T2_BYTES, 16, 1024);
 #pragma unroll
-        for (int k = 0; k < D1 / 16; ++k) {
-          const uint64_t da = make_smem_desc(base + L::OFF_R1 + (k / 4) * (BW_R * 128) + (k % 4) * 32, 16, 1024);
-          const uint64_t db = make_smem_desc(t1 + (k / 4) * (BW_T * 128) + (k % 4) * 32, 16, 1024);
-          umma_ss(tmem + L::TM_X + s * BW_T, da, db, idesc_xy, k > 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < D1 / 16; ++k)
+          umma_ss(tmem + L::TM_X + s * BW_T, desc_at(dr1, (k / 4) * (BW_R * 128) + (k % 4) * 32),
+                  desc_at(dt1, (k / 4) * (BW_T * 128) + (k % 4) * 32), idesc_xy, k > 0 ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < D2 / 16; ++k) {
-          const uint64_t da = make_smem_desc(base + L::OFF_R2 + (k / 4) * (BW_R * 128) + (k % 4) * 32, 16, 1024);
-          const uint64_t db = make_smem_desc(t2 + (k / 4) * (BW_T * 128) + (k % 4) * 32, 16, 1024);
-          umma_ss(tmem + L::TM_Y + s * BW_T, da, db, idesc_xy, k > 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < D2 / 16; ++k)
+          umma_ss(tmem + L::TM_Y + s * BW_T, desc_at(dr2, (k / 4) * (BW_R * 128) + (k % 4) * 32),
+                  desc_at(dt2, (k / 4) * (BW_T * 128) + (k % 4) * 32), idesc_xy, k > 0 ? 1u : 0u);
         umma_commit(bar(BB_XY_FULL0 + s));
-        if (it >= 1 && !issue_acc(it - 1)) { ok = false; break; }
+        if (NB == 2 && it >= 1 && !issue_acc(it - 1)) { ok = false; break; }
       }
       if (ok && n_iter > 0 && issue_acc(n_iter - 1)) umma_commit(bar(BB_ACC));
     }
@@ -219,30 +221,36 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
     const int row = lg * 32 + lane;  // resident row == TMEM lane
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(lg * 32) << 16);
     bool ok = true;
-    float my_lse2 = 0.f, my_delta = 0.f;
+    float my_nlse2 = 0.f, my_ndelta = 0.f;
     if (!KV_MODE) {
       const long long o = (static_cast<long long>(b) * p.Hq + head_r) * p.S + r0 + row;
-      my_lse2 = p.lse2[o];
-      my_delta = p.delta[o];
+      my_nlse2 = p.lse2[o];
+      my_ndelta = p.delta[o];
     }
+    int tq = 0, hq = 0;  // key mode: tile inside the query head, query head inside the group (no division per tile)
     for (int it = 0; it < n_iter && ok; ++it) {
       const int s = it % NB;
-      const int tr = t_row0(it);
-      if (!mbar_wait(bar(BB_XY_FULL0 + s), (it / NB) & 1u, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) { ok = false; break; }
-      if (it >= NB && !mbar_wait(bar(BB_DS_EMPTY0 + s), ((it / NB) - 1) & 1u, p.status, ST_TIMEOUT_EMPTY, abort_flag)) {
-        ok = false;
-        break;
+      const int tr = (t_first + (KV_MODE ? tq : it)) * BW_T;
+      const int th = KV_MODE ? head_r * G + hq : 0;
+      if (KV_MODE && ++tq == t_count) {
+        tq = 0;
+        ++hq;
       }
-      tc_fence_after();
       // rows are keys and columns queries in key mode, the other way round in query mode
       const bool diag = KV_MODE ? (tr < r0 + BW_R) : (tr + BW_T > r0);
-      const float* lse_col = nullptr;
-      const float* dl_col = nullptr;
+      // key mode: the statistics of this tile's queries (negated log-sum-exp and delta), the same CPT values for every
+      // thread of the warp, fetched before the wait for the scores so that their latency falls into it
+      float4 nl4[CPT / 4], nd4[CPT / 4];
       if (KV_MODE) {
-        const long long o = (static_cast<long long>(b) * p.Hq + t_head(it)) * p.S + tr + c0;
-        lse_col = p.lse2 + o;
-        dl_col = p.delta + o;
+        const long long o = (static_cast<long long>(b) * p.Hq + th) * p.S + tr + c0;
+#pragma unroll
+        for (int i = 0; i < CPT / 4; ++i) {
+          nl4[i] = __ldg(reinterpret_cast<const float4*>(p.lse2 + o) + i);
+          nd4[i] = __ldg(reinterpret_cast<const float4*>(p.delta + o) + i);
+        }
       }
+      if (!mbar_wait(bar(BB_XY_FULL0 + s), (it / NB) & 1u, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) { ok = false; break; }
+      tc_fence_after();
       uint32_t x[CPT], y[CPT];
       if constexpr (CPT == 32) {
         tmem_ld_32x32b_x32(lane_addr + L::TM_X + s * BW_T + c0, x);
@@ -253,54 +261,55 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
       }
       tmem_ld_wait();
       uint32_t pp[CPT / 2], ds[CPT / 2];
+      // P = 2^(x c - lse2) and dS = P (y - delta), two elements per instruction (packed fp32); the statistics are stored
+      // negated so that both are one fused operation.  Tiles off the diagonal take the path without comparisons;
+      // on the diagonal a masked score is replaced by -FLT_MAX, which makes P and with it dS exactly zero.
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 my_nl2 = make_float2(my_nlse2, my_nlse2), my_nd2 = make_float2(my_ndelta, my_ndelta);
 #pragma unroll
       for (int i8 = 0; i8 < CPT / 8; ++i8) {
-        float l2[8], dl[8];
+        float2 nl2[4], nd2[4];
         if (KV_MODE) {
-          // all threads read the same 8 query statistics: two broadcast 16-byte loads each
-          const float4 a0 = __ldg(reinterpret_cast<const float4*>(lse_col + i8 * 8));
-          const float4 a1 = __ldg(reinterpret_cast<const float4*>(lse_col + i8 * 8 + 4));
-          const float4 b0 = __ldg(reinterpret_cast<const float4*>(dl_col + i8 * 8));
-          const float4 b1 = __ldg(reinterpret_cast<const float4*>(dl_col + i8 * 8 + 4));
-          l2[0] = a0.x; l2[1] = a0.y; l2[2] = a0.z; l2[3] = a0.w; l2[4] = a1.x; l2[5] = a1.y; l2[6] = a1.z; l2[7] = a1.w;
-          dl[0] = b0.x; dl[1] = b0.y; dl[2] = b0.z; dl[3] = b0.w; dl[4] = b1.x; dl[5] = b1.y; dl[6] = b1.z; dl[7] = b1.w;
-        }
-        float pv[8], dv[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int col = c0 + i8 * 8 + e;
-          const int kv = KV_MODE ? r0 + row : tr + col;
-          const int qi = KV_MODE ? tr + col : r0 + row;
-          const bool valid = !diag || kv <= qi;
-          const float pr = valid ? ex2_approx(__uint_as_float(x[i8 * 8 + e]) * p.scale_log2 - (KV_MODE ? l2[e] : my_lse2)) : 0.f;
-          pv[e] = pr;
-          dv[e] = pr * (__uint_as_float(y[i8 * 8 + e]) - (KV_MODE ? dl[e] : my_delta));
+          const float4 a0 = nl4[2 * i8], a1 = nl4[2 * i8 + 1], b0 = nd4[2 * i8], b1 = nd4[2 * i8 + 1];
+          nl2[0] = make_float2(a0.x, a0.y); nl2[1] = make_float2(a0.z, a0.w);
+          nl2[2] = make_float2(a1.x, a1.y); nl2[3] = make_float2(a1.z, a1.w);
+          nd2[0] = make_float2(b0.x, b0.y); nd2[1] = make_float2(b0.z, b0.w);
+          nd2[2] = make_float2(b1.x, b1.y); nd2[3] = make_float2(b1.z, b1.w);
         }
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          pp[i8 * 4 + e] = pack_bf16(pv[2 * e], pv[2 * e + 1]);
-          ds[i8 * 4 + e] = pack_bf16(dv[2 * e], dv[2 * e + 1]);
+          float x0 = __uint_as_float(x[i8 * 8 + 2 * e]), x1 = __uint_as_float(x[i8 * 8 + 2 * e + 1]);
+          if (diag) {
+            const int col = c0 + i8 * 8 + 2 * e;
+            const int kv = KV_MODE ? r0 + row : tr + col;       // of the first element of the pair
+            const int qi = KV_MODE ? tr + col : r0 + row;
+            if (kv > qi) x0 = -FLT_MAX;
+            if ((KV_MODE ? kv : kv + 1) > (KV_MODE ? qi + 1 : qi)) x1 = -FLT_MAX;
+          }
+          const float2 t2 = fma2(make_float2(x0, x1), sc2, KV_MODE ? nl2[e] : my_nl2);
+          float2 pr;
+          pr.x = ex2_approx(t2.x);
+          pr.y = ex2_approx(t2.y);
+          const float2 dd = add2(make_float2(__uint_as_float(y[i8 * 8 + 2 * e]), __uint_as_float(y[i8 * 8 + 2 * e + 1])),
+                                 KV_MODE ? nd2[e] : my_nd2);
+          const float2 dv = mul2(pr, dd);
+          pp[i8 * 4 + e] = pack_bf16(pr.x, pr.y);
+          ds[i8 * 4 + e] = pack_bf16(dv.x, dv.y);
         }
       }
-#pragma unroll
-      for (int q = 0; q < CPT / 8; ++q) {
-        const int chunk = grp * (CPT / 8) + q;  // 16-byte chunk of the 128-byte row
-        const uint32_t off = row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + L::OFF_DS + s * L::DS_BYTES + off),
-                     "r"(ds[4 * q]), "r"(ds[4 * q + 1]), "r"(ds[4 * q + 2]), "r"(ds[4 * q + 3])
-                     : "memory");
-        if (KV_MODE)
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + L::OFF_P + s * L::DS_BYTES + off),
-                       "r"(pp[4 * q]), "r"(pp[4 * q + 1]), "r"(pp[4 * q + 2]), "r"(pp[4 * q + 3])
-                       : "memory");
+      // dS (and in key mode P) as packed bf16 over the first half of this thread's own score columns: nobody else
+      // reads or writes those, and the products that consume them are issued only after every warp has signalled
+      if constexpr (CPT == 32) {
+        tmem_st_32x32b_x16(lane_addr + L::TM_Y + s * BW_T + c0, ds);
+        if (KV_MODE) tmem_st_32x32b_x16(lane_addr + L::TM_X + s * BW_T + c0, pp);
+      } else {
+        tmem_st_32x32b_x8(lane_addr + L::TM_Y + s * BW_T + c0, ds);
+        if (KV_MODE) tmem_st_32x32b_x8(lane_addr + L::TM_X + s * BW_T + c0, pp);
       }
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar(BB_XY_EMPTY0 + s));
-        mbar_arrive(bar(BB_DS_FULL0 + s));
-      }
+      if (lane == 0) mbar_arrive(bar(BB_DS_FULL0 + s));
     }
     if (ok && n_iter > 0 && mbar_wait(bar(BB_ACC), 0, p.status, ST_TIMEOUT_ACC_FULL, abort_flag)) {
       tc_fence_after();
@@ -339,7 +348,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
   }
 }
 
-// delta[b,h,s] = sum_d dO[b,s,h,d] * O[b,s,h,d];  lse2 = lse * log2(e).  One warp per (b, s, h) row.
+// delta[b,h,s] = -sum_d dO[b,s,h,d] * O[b,s,h,d];  lse2 = -lse * log2(e): both stored negated, which is how the
+// recompute warps add them.  One warp per (b, s, h) row.
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                                   const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2,
                                   long long o_bs, long long o_ss, long long o_hs, long long do_bs, long long do_ss,
@@ -366,8 +376,8 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
   acc = warp_sum(acc);
   if (lane == 0) {
     const long long idx = (static_cast<long long>(b) * H + h) * S + s;
-    delta[idx] = acc;
-    lse2[idx] = lse[idx] * 1.4426950408889634f;
+    delta[idx] = -acc;
+    lse2[idx] = -lse[idx] * 1.4426950408889634f;
   }
 }
 
