@@ -349,21 +349,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
 }
 
 // delta[b,h,s] = -sum_d dO[b,s,h,d] * O[b,s,h,d];  lse2 = -lse * log2(e): both stored negated, which is how the
-// recompute warps add them.  One warp per (b, s, h) row.
+// recompute warps add them.  Eight lanes per (b, s, h) row, four rows per warp: every lane has up to four 16-byte
+// loads in flight.
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                                   const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2,
                                   long long o_bs, long long o_ss, long long o_hs, long long do_bs, long long do_ss,
                                   long long do_hs, int B, int S, int H, int Dv) {
-  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (w >= static_cast<long long>(B) * S * H) return;
+  const long long n_rows = static_cast<long long>(B) * S * H;
+  const int lane = threadIdx.x & 31, sub = lane & 7;
+  long long w = ((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * 4 + (lane >> 3);
+  const bool live = w < n_rows;
+  if (!live) w = n_rows - 1;  // keep the lane in the shuffles
   const int h = static_cast<int>(w % H);
   const int s = static_cast<int>((w / H) % S);
   const int b = static_cast<int>(w / (static_cast<long long>(H) * S));
   const __nv_bfloat16* orow = o + b * o_bs + s * o_ss + h * o_hs;
   const __nv_bfloat16* drow = dout + b * do_bs + s * do_ss + h * do_hs;
   float acc = 0.f;
-  for (int c = lane * 8; c < Dv; c += 256) {
+  for (int c = sub * 8; c < Dv; c += 64) {
     const uint4 a = *reinterpret_cast<const uint4*>(orow + c);
     const uint4 g = *reinterpret_cast<const uint4*>(drow + c);
     const uint32_t av[4] = {a.x, a.y, a.z, a.w}, gv[4] = {g.x, g.y, g.z, g.w};
@@ -373,8 +376,9 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
       acc += x.x * y.x + x.y * y.y;
     }
   }
-  acc = warp_sum(acc);
-  if (lane == 0) {
+#pragma unroll
+  for (int m = 4; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+  if (live && sub == 0) {
     const long long idx = (static_cast<long long>(b) * H + h) * S + s;
     delta[idx] = -acc;
     lse2[idx] = -lse[idx] * 1.4426950408889634f;
@@ -395,7 +399,7 @@ static int launch_bwd(const olb_attn_bwd_desc* d, cudaStream_t stream) {
   const long long n_rows = static_cast<long long>(d->B) * d->S * d->Hq;
   float* delta = d->delta;
   float* lse2 = d->delta + n_rows;
-  attn_delta_kernel<<<static_cast<unsigned>((n_rows * 32 + 255) / 256), 256, 0, stream>>>(
+  attn_delta_kernel<<<static_cast<unsigned>((n_rows * 8 + 255) / 256), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(d->o), static_cast<const __nv_bfloat16*>(d->dout), d->lse, delta, lse2, d->o_bs,
       d->o_ss, d->o_hs, d->do_bs, d->do_ss, d->do_hs, d->B, d->S, d->Hq, d->Dv);
 

@@ -206,7 +206,10 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16
       vd[k] = *reinterpret_cast<const uint4*>(dy + row * cols + k * 256 + lane * 8);
     }
     const float r = rstd[row];
-    float dot = 0.f;
+    const float2 r2 = make_float2(r, r);
+    // two elements per instruction (packed fp32): the products and sums are the same fused operations as in the
+    // scalar form, so the results do not change
+    float2 dot2 = make_float2(0.f, 0.f);
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
       const uint32_t ux[4] = {vx[k].x, vx[k].y, vx[k].z, vx[k].w}, ud[4] = {vd[k].x, vd[k].y, vd[k].z, vd[k].w};
@@ -215,35 +218,38 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16
       const uint32_t uw[4] = {vw.x, vw.y, vw.z, vw.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float2 fx = unpack_bf16(ux[i]), fd = unpack_bf16(ud[i]), fw = unpack_bf16(uw[i]);
-        const float n0 = fx.x * r, n1 = fx.y * r;
-        dot += (w ? fd.x * fw.x : fd.x) * n0 + (w ? fd.y * fw.y : fd.y) * n1;
-        dw_acc[k][2 * i] += fd.x * round_bf16(n0);
-        dw_acc[k][2 * i + 1] += fd.y * round_bf16(n1);
+        const float2 fd = unpack_bf16(ud[i]);
+        const float2 n2 = mul2(unpack_bf16(ux[i]), r2);
+        const float2 d2 = w ? mul2(fd, unpack_bf16(uw[i])) : fd;
+        dot2 = fma2(d2, n2, dot2);
+        const float2 nr = unpack_bf16(pack_bf16(n2.x, n2.y));  // the normalised value as the forward rounded it
+        const float2 acc = fma2(fd, nr, make_float2(dw_acc[k][2 * i], dw_acc[k][2 * i + 1]));
+        dw_acc[k][2 * i] = acc.x;
+        dw_acc[k][2 * i + 1] = acc.y;
       }
     }
-    dot = warp_sum(dot) * inv_cols;
+    const float dot = warp_sum(dot2.x + dot2.y) * inv_cols;
+    const float2 ndot2 = make_float2(-dot, -dot);
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
       const uint32_t ux[4] = {vx[k].x, vx[k].y, vx[k].z, vx[k].w}, ud[4] = {vd[k].x, vd[k].y, vd[k].z, vd[k].w};
       uint4 vw = make_uint4(0, 0, 0, 0);
       if (w) vw = *reinterpret_cast<const uint4*>(s_w + k * 256 + lane * 8);
       const uint32_t uw[4] = {vw.x, vw.y, vw.z, vw.w};
+      uint4 vr = make_uint4(0, 0, 0, 0);
+      if (dres) vr = *reinterpret_cast<const uint4*>(dres + row * cols + k * 256 + lane * 8);
+      const uint32_t ur[4] = {vr.x, vr.y, vr.z, vr.w};
       uint32_t o[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float2 fx = unpack_bf16(ux[i]), fd = unpack_bf16(ud[i]), fw = unpack_bf16(uw[i]);
-        const float n0 = fx.x * r, n1 = fx.y * r;
-        const float d0 = w ? fd.x * fw.x : fd.x, d1 = w ? fd.y * fw.y : fd.y;
-        o[i] = pack_bf16(r * (d0 - n0 * dot), r * (d1 - n1 * dot));
-      }
-      if (dres) {
-        const uint4 vr = *reinterpret_cast<const uint4*>(dres + row * cols + k * 256 + lane * 8);
-        const uint32_t ur[4] = {vr.x, vr.y, vr.z, vr.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 a = unpack_bf16(o[i]), b = unpack_bf16(ur[i]);
-          o[i] = pack_bf16(a.x + b.x, a.y + b.y);
+        const float2 fd = unpack_bf16(ud[i]);
+        const float2 n2 = mul2(unpack_bf16(ux[i]), r2);
+        const float2 d2 = w ? mul2(fd, unpack_bf16(uw[i])) : fd;
+        const float2 g2 = mul2(r2, fma2(n2, ndot2, d2));
+        o[i] = pack_bf16(g2.x, g2.y);
+        if (dres) {
+          const float2 s2 = add2(unpack_bf16(o[i]), unpack_bf16(ur[i]));  // dx rounded first, as two kernels would
+          o[i] = pack_bf16(s2.x, s2.y);
         }
       }
       *reinterpret_cast<uint4*>(dx + row * cols + k * 256 + lane * 8) = make_uint4(o[0], o[1], o[2], o[3]);
