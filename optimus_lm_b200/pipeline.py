@@ -30,7 +30,7 @@ import torch.distributed as dist
 from .ops import aux_loss as AL
 from .ops import functional as OF
 from .profilers import record_pcl_function
-from .schedules import PipeOp, make_schedule
+from .schedules import Interleaved1f1bBufferManager, PipeOp, make_schedule
 
 
 class ParallelTrainerOutput:
@@ -122,6 +122,12 @@ class PipelineExecutor:
                 self.groups = _channel_groups(self.VPP > 1)
         self.last_virtual = self.PP * self.VPP - 1
         self._pending: List[Tuple[object, torch.Tensor]] = []
+        # slot plan of the activations in flight: bounded by the schedule's peak, checked on every step
+        self.buffers = Interleaved1f1bBufferManager(pmap, self.VPP, self.PP, self.NMB, reuse_buffers_in_1f1b=True,
+                                                    pp_scheme=pp_scheme)
+        if verbose and getattr(pmap, "dp_ind", 0) == 0 and getattr(pmap, "ep_ind", 0) == 0:
+            print(f"Rank {pmap.rank}: at most {self.buffers.num_act_buffers} micro-batch activations in flight "
+                  f"for {pp_scheme} pp_scheme (PP {self.PP}, VPP {self.VPP}, NMB {self.NMB})", flush=True)
 
     # ------------------------------------------------------------------ topology
     def _virtual(self, vp: int) -> int:
@@ -336,11 +342,15 @@ class PipelineExecutor:
         logits_list: List[Optional[torch.Tensor]] = [None] * NMB
         states: Dict[Tuple[int, int], _MicroState] = {}
 
+        self.buffers.reset()
         for op in self.schedule:
             if op.kind == "F":
+                if not only_forward:
+                    self.buffers.add_forward_to_flight(self.buffers.flat_index(op.mb, op.vp))
                 self._forward_op(op, states, input_list, labels_list, loss_list, logits_list, output_logits)
             elif not only_forward:
                 self._backward_op(op, states, output_grad_list)
+                self.buffers.drain_forward_from_flight(self.buffers.flat_index(op.mb, op.vp))
         for work, _keep in self._pending:
             work.wait()
         self._pending.clear()

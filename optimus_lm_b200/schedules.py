@@ -128,3 +128,90 @@ def simulate(scheme: str, PP: int, NMB: int, VPP: int = 1) -> int:
         if not progressed:
             raise RuntimeError(f"pipeline schedule dead-locks: scheme={scheme} PP={PP} NMB={NMB} VPP={VPP} pos={pos}")
     return rounds
+
+
+class Interleaved1f1bBufferManager:
+    """Slot plan for the activations a pipeline stage holds between a forward and its backward.
+
+    Same constructor and method names as the reference's bookkeeping class (optimus/trainer.py:89-182), built on
+    the schedule generators above instead of on fixed formulas: ``num_act_buffers`` is the largest number of
+    forwards in flight that this stage's schedule reaches (with ``reuse_buffers_in_1f1b``; ``VPP * NMB`` without),
+    a forward takes the lowest free slot and its backward gives the slot back.  The executor keeps its per-micro-batch
+    state in these slots and checks the bound on every step; code that sizes memory ahead of time reads
+    ``num_act_buffers`` / ``num_ograd_buffers``.  Indices are flat positions in forward order (micro-batch groups
+    of ``PP`` visit the chunks in turn), as in the reference.
+    """
+
+    def __init__(self, pmap, VPP, PP, NMB, reuse_buffers_in_1f1b=False, pp_scheme="1f1b"):
+        if pp_scheme == "1f1b" and VPP > 1:
+            assert NMB % PP == 0, "In Interleaved1f1b schedule, the number of micro batches should be a multiple of pipeline parallelism"
+        self.pmap, self.VPP, self.PP, self.NMB = pmap, VPP, PP, NMB
+        self.reuse_buffers_in_1f1b = reuse_buffers_in_1f1b
+        self.pp_scheme = pp_scheme
+        self.NMBG, self.NG = PP, max(NMB // PP, 1)
+        self.total = VPP * NMB
+        ops = make_schedule(pp_scheme, pmap.pp_ind, PP, NMB, VPP)
+        self.schedule_peak = max_in_flight(ops)
+        self.num_act_buffers = self.schedule_peak if reuse_buffers_in_1f1b else self.total
+        self.num_ograd_buffers = 1 if reuse_buffers_in_1f1b else self.total
+        self._slot_of = {}
+        self._free = list(range(self.num_act_buffers))  # kept sorted: the lowest free slot goes first
+        self.peak_used = 0
+
+    # ---- index arithmetic
+    def flat_index(self, mb: int, vp: int) -> int:
+        """Position of forward (micro-batch, chunk) in forward order; inverse of ``_virtual_forward`` (GPipe: chunk
+        by chunk)."""
+        if self.pp_scheme != "1f1b" or self.VPP == 1:
+            return vp * self.NMB + mb
+        group, lmb = divmod(mb, self.PP)
+        return group * self.PP * self.VPP + vp * self.PP + lmb
+
+    def _in_range(self, index) -> bool:
+        return index is not None and 0 <= index < self.total
+
+    def get_forward_index_from_backward_index(self, bwd_index):
+        """The k-th backward undoes the forward of the same micro-batch on the mirrored chunk."""
+        if not self._in_range(bwd_index):
+            return None
+        if self.pp_scheme != "1f1b" or self.VPP == 1:
+            vp, mb = divmod(bwd_index, self.NMB)
+            return self.flat_index(mb, self.VPP - 1 - vp)
+        mb, vp = _virtual_backward(bwd_index, self.PP, self.VPP)
+        return self.flat_index(mb, vp)
+
+    # ---- slots
+    def add_forward_to_flight(self, index):
+        if not self._in_range(index):
+            return None
+        assert index not in self._slot_of, f"forward {index} is already in flight"
+        assert self._free, (f"more than {self.num_act_buffers} forwards in flight on stage {self.pmap.pp_ind}: "
+                            f"{sorted(self._slot_of)} + {index}")
+        slot = self._free.pop(0)
+        self._slot_of[index] = slot
+        self.peak_used = max(self.peak_used, len(self._slot_of))
+        return slot
+
+    def get_forward_buffer_id(self, index):
+        if not self._in_range(index):
+            return None
+        assert index in self._slot_of, f"Forward index {index} is not in flight. (Forwards in flight {sorted(self._slot_of)})"
+        return self._slot_of[index]
+
+    def get_backward_buffer_id(self, index):
+        if not self._in_range(index):
+            return None
+        return 0 if self.reuse_buffers_in_1f1b else index
+
+    def drain_forward_from_flight(self, index):
+        """The backward of ``index`` has consumed its activations: the slot is free again."""
+        if not self._in_range(index) or index not in self._slot_of:
+            return None
+        slot = self._slot_of.pop(index)
+        import bisect
+        bisect.insort(self._free, slot)
+        return slot
+
+    def reset(self):
+        self._slot_of.clear()
+        self._free = list(range(self.num_act_buffers))

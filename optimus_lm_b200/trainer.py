@@ -10,7 +10,7 @@ import torch
 from torch import nn
 
 from .pipeline import ParallelTrainerOutput, PipelineExecutor  # noqa: F401
-from .schedules import _virtual_forward
+from .schedules import Interleaved1f1bBufferManager, _virtual_forward  # noqa: F401
 
 
 def get_coord_info_from_flat_index(i, NG, VPP, NMBG, backward=False):
@@ -19,27 +19,6 @@ def get_coord_info_from_flat_index(i, NG, VPP, NMBG, backward=False):
     mb, vp = _virtual_forward(i, NMBG, VPP)
     mg, lmb = divmod(mb, NMBG)
     return mg, (VPP - 1 - vp if backward else vp), lmb
-
-
-class Interleaved1f1bBufferManager:
-    """Slot allocator for activations in flight (reference trainer.py:89-182).  The executor
-    allocates from the caching allocator instead; this class keeps the bookkeeping API for code
-    that sizes buffers ahead of time."""
-
-    def __init__(self, num_buffers):
-        self.free = list(range(num_buffers))
-        self.in_flight = {}
-        self.drain = []
-
-    def add_forward_to_flight(self, key):
-        slot = self.free.pop(0)
-        self.in_flight[key] = slot
-        return slot
-
-    def drain_forward_from_flight(self, key):
-        slot = self.in_flight.pop(key)
-        self.free.append(slot)
-        return slot
 
 
 class ParallelTrainer(PipelineExecutor):
