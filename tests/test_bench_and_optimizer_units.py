@@ -92,3 +92,23 @@ def test_debug_shapes_do_not_carry_the_benchmark_metric_name():
     kw, mb, seq, vocab, metric, tag = b.named_config("olmoe_ep", 8)
     rec = b.result_config(opts, kw, 8 * mb * seq, tag)
     assert rec["model"] == "OLMoE-1B-7B" and rec["global_batch"] == 32 and rec["parallelism"] == "ep8"
+
+
+def test_step_profile_kernel_table_sums_device_events_only():
+    """The step profiler's table: device events are summed per kernel name, host events are left out, rows come longest
+    first and the total covers every kernel, also those below the cut."""
+    from types import SimpleNamespace
+
+    import torch
+
+    from optimus_lm_b200.utils.step_profile import kernel_table
+
+    cuda, cpu = torch.autograd.DeviceType.CUDA, torch.autograd.DeviceType.CPU
+    ev = [SimpleNamespace(device_type=cuda, name="gemm", device_time_total=100.0),
+          SimpleNamespace(device_type=cuda, name="gemm", device_time_total=50.0),
+          SimpleNamespace(device_type=cuda, name="adamw", device_time_total=400.0),
+          SimpleNamespace(device_type=cuda, name="rope", device_time_total=5.0),
+          SimpleNamespace(device_type=cpu, name="aten::mm", device_time_total=999.0)]
+    total, rows = kernel_table(ev, top=2)
+    assert total == 555.0
+    assert rows == [(400.0, 1, "adamw"), (150.0, 2, "gemm")]
