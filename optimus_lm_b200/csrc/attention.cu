@@ -665,7 +665,11 @@ int attn_tmap(CUtensorMap* map, const void* ptr, int Dh, int H, int S, int B, lo
 template <int D, int DV, int BKV>
 static int launch_fwd(const olb_attn_fwd_desc* d, cudaStream_t stream) {
   using L = AttnFwdSmem<D, DV, BKV>;
-  static bool configured = false;
+  // the attribute belongs to the function on one device: once per device, not once per process
+  static bool configured_on[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -3;
+  bool& configured = configured_on[dev];
   if (!configured) {
     if (cudaFuncSetAttribute(attn_fwd_kernel<D, DV, BKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
       return -3;
@@ -696,7 +700,11 @@ static int launch_fwd(const olb_attn_fwd_desc* d, cudaStream_t stream) {
 template <int D, int DV, int BKV, int EMU>
 static int launch_fwd2(const olb_attn_fwd_desc* d, cudaStream_t stream) {
   using L = AttnFwd2Smem<D, DV, BKV>;
-  static bool configured = false;
+  // the attribute belongs to the function on one device: once per device, not once per process
+  static bool configured_on[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -3;
+  bool& configured = configured_on[dev];
   if (!configured) {
     if (cudaFuncSetAttribute(attn_fwd2_kernel<D, DV, BKV, EMU>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
       return -3;

@@ -389,7 +389,11 @@ template <int D, int DV>
 static int launch_bwd(const olb_attn_bwd_desc* d, cudaStream_t stream) {
   using LK = BwdCfg<D, DV, true>;
   using LQ = BwdCfg<D, DV, false>;
-  static bool configured = false;
+  // the attribute belongs to the function on one device: once per device, not once per process
+  static bool configured_on[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -3;
+  bool& configured = configured_on[dev];
   if (!configured) {
     if (cudaFuncSetAttribute(attn_bwd_kernel<D, DV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, LK::TOTAL) != cudaSuccess ||
         cudaFuncSetAttribute(attn_bwd_kernel<D, DV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, LQ::TOTAL) != cudaSuccess)
