@@ -1,0 +1,143 @@
+"""Barrier protocol of the CTA-pair GEMM (csrc/gemm_tcgen05.cu: gemm_bf16_pair_kernel), replayed on the CPU.
+
+Two CTAs share a 256 x 256 tile.  Each CTA's producer refills its own half of a ring stage when its own "empty"
+barrier says so and reports the bytes to the even CTA's "full" barrier (the even CTA's producer announces the bytes
+of both, so the other CTA's bytes may land before the announcement); one thread of the even CTA issues the products
+and its commits arrive on both CTAs' "empty" and "accumulator full" barriers; the four epilogue warps of each CTA
+drain their half of one of two accumulators and arrive on the even CTA's "accumulator empty" barrier (count 8).
+The roles run under random interleavings and must not dead-lock, no wait may pass for another phase than the one it
+was written for, a stage half may only be refilled after the products that read it, and an accumulator may only be
+overwritten after all eight warps have drained it.
+"""
+import random
+
+import pytest
+
+
+class TxBarrier:
+    """mbarrier with an arrival count and a transaction-byte count; the phase ends when both reach zero."""
+
+    def __init__(self, count):
+        self.count, self.pending, self.tx, self.completions = count, count, 0, 0
+
+    def _check(self):
+        if self.pending == 0 and self.tx == 0:
+            self.pending = self.count
+            self.completions += 1
+
+    def arrive(self, expect=0):
+        self.tx += expect
+        self.pending -= 1
+        assert self.pending >= 0
+        self._check()
+
+    def complete_tx(self, nbytes):
+        self.tx -= nbytes
+        self._check()
+
+    def passes(self, parity):
+        return (self.completions & 1) != parity
+
+
+def run(roles, seed):
+    rng = random.Random(seed)
+    live = {i: iter(r) for i, r in enumerate(roles)}
+    blocked = {}
+    while live:
+        progressed = False
+        order = list(live)
+        rng.shuffle(order)
+        for i in order:
+            if i in blocked:
+                bar, gen = blocked[i]
+                if not bar.passes(gen & 1):
+                    continue
+                assert bar.completions == gen + 1, f"wait for completion {gen} passed at {bar.completions}"
+                del blocked[i]
+            try:
+                req = next(live[i])
+            except StopIteration:
+                del live[i]
+                progressed = True
+                continue
+            progressed = True
+            if req is not None:
+                blocked[i] = req
+        assert progressed, f"dead-lock with roles {sorted(live)} blocked"
+
+
+def pair_roles(tiles, k_blocks, STAGES, acc_empty_count=8):
+    HALF = 16384 + 16384  # bytes of one CTA's half of a stage (A and B)
+    full = [TxBarrier(1) for _ in range(STAGES)]                                     # the even CTA's
+    empty = [[TxBarrier(1) for _ in range(STAGES)] for _ in range(2)]                # per CTA
+    acc_full = [[TxBarrier(1) for _ in range(2)] for _ in range(2)]                  # per CTA, per accumulator
+    acc_empty = [TxBarrier(acc_empty_count) for _ in range(2)]                        # the even CTA's
+    holds = [[None] * STAGES for _ in range(2)]      # k-block index (global) a CTA's stage half holds
+    consumed = set()
+    acc_tile = [None, None]                          # tile an accumulator holds
+    drained = [8, 8]                                 # epilogue warps that have drained it
+
+    def producer(rank):
+        i = 0
+        for _t in range(tiles):
+            for _kb in range(k_blocks):
+                s = i % STAGES
+                if i >= STAGES:
+                    yield (empty[rank][s], i // STAGES - 1)
+                    assert holds[rank][s] in consumed, "stage half refilled before the products that read it"
+                if rank == 0:
+                    full[s].arrive(expect=2 * HALF)
+                    yield None
+                holds[rank][s] = i
+                full[s].complete_tx(HALF)   # the copy lands (here: at once)
+                i += 1
+                yield None
+
+    def issuer():
+        i = 0
+        for t in range(tiles):
+            a = t & 1
+            if t >= 2:
+                yield (acc_empty[a], t // 2 - 1)
+                assert drained[a] == 8, "accumulator overwritten before every warp had drained it"
+            acc_tile[a], drained[a] = t, 0
+            for _kb in range(k_blocks):
+                s = i % STAGES
+                yield (full[s], i // STAGES)
+                assert holds[0][s] == i and holds[1][s] == i, "products issued on a stage that is not complete"
+                consumed.add(i)
+                empty[0][s].arrive(); empty[1][s].arrive()    # one commit, arrives in both CTAs
+                i += 1
+                yield None
+            acc_full[0][a].arrive(); acc_full[1][a].arrive()
+            yield None
+
+    def epilogue(rank):
+        for t in range(tiles):
+            a = t & 1
+            yield (acc_full[rank][a], t // 2)
+            assert acc_tile[a] == t
+            drained[a] += 1
+            acc_empty[a].arrive()
+            yield None
+
+    return [producer(0), producer(1), issuer()] + [epilogue(r) for r in (0, 1) for _ in range(4)]
+
+
+@pytest.mark.parametrize("tiles,k_blocks", [(1, 1), (1, 7), (2, 3), (3, 32), (9, 2), (5, 13)])
+@pytest.mark.parametrize("STAGES", [2, 4, 6])
+def test_pair_gemm_protocol(tiles, k_blocks, STAGES):
+    for seed in range(10):
+        run(pair_roles(tiles, k_blocks, STAGES), seed)
+
+
+def test_replay_catches_a_barrier_that_is_one_arrival_short():
+    """The checker itself: with the accumulator barrier initialised for seven arrivals instead of eight, some
+    interleaving lets the issuer overwrite an accumulator that a warp is still reading (or trips the arrival count)."""
+    failures = 0
+    for seed in range(10):
+        try:
+            run(pair_roles(6, 2, 4, acc_empty_count=7), seed)
+        except AssertionError:
+            failures += 1
+    assert failures > 0
